@@ -1,0 +1,315 @@
+#!/usr/bin/env python
+"""Headline benchmark: int8-KV-cache decode attention at B=64, ctx 4096 (per GPU).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
+
+A step is one decode pass of the attention path over a stack of LAYERS distinct layer caches
+(28, as in Qwen3-1.7B): per layer, quantize-on-write of the B new tokens (fused QK-RMSNorm +
+RoPE + int8) then split-K paged decode attention over ctx tokens.  The whole step is one CUDA
+graph replay, as in the reference engine.  Metric: algorithmic HBM bytes of the step / time.
+
+With N > 1 (torchrun) every rank holds its own B sequences (sequence sharding, no collective
+on the data path: weak scaling); the reported value is all ranks' bytes over the slowest
+rank's device time.  Prints ONE JSON line on rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+HQ, HKV, D, PAGE = 16, 8, 128, 16
+CACHE_BYTES_PER_TOKEN = HKV * (2 * D + 8)  # int8 K+V codes and fp32 K+V scales of one token, one layer = 2112
+WRITE_BYTES_PER_TOKEN = 14656  # q,k,v,cos,sin read (8448) + q', codes, scales written (6208)
+
+
+def attn_bytes(B: int, n: int) -> int:
+    """Algorithmic bytes of one decode_attention call: cache stream + q read + out write."""
+    return B * n * CACHE_BYTES_PER_TOKEN + 2 * (B * HQ * D * 2)
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-i", str(self.index), "-lms", "100"], stdout=subprocess.PIPE, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()
+            self.thread.join(timeout=2)
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[0]))
+                mx.append(float(r[1]))
+            except (ValueError, IndexError):
+                continue
+            for name, val in zip(names, r[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ----------------------------------------------------------------------------- CPU arm
+class CpuSample:
+    """The CPU port of decode attention (the oracle) on `seqs` of the workload's sequences of one
+    layer; `run()` returns seconds for one pass."""
+
+    def __init__(self, B: int, n: int, seqs: int, seed: int = 2):
+        from oracle import oracle as O
+
+        self.O, self.n, self.seqs = O, n, seqs
+        rng = np.random.default_rng(seed)
+        pages_per_seq = (n + PAGE - 1) // PAGE
+        num_pages = seqs * pages_per_seq
+        self.cache = O.make_cache(num_pages, HKV, PAGE, D)
+        self.cache.k[...] = rng.integers(-127, 128, self.cache.k.shape, dtype=np.int8)
+        self.cache.v[...] = rng.integers(-127, 128, self.cache.v.shape, dtype=np.int8)
+        self.cache.k_scale[...] = 0.02
+        self.cache.v_scale[...] = 0.02
+        self.table = rng.permutation(num_pages).astype(np.int32).reshape(seqs, pages_per_seq)
+        self.q = O.bf16_round(rng.standard_normal((seqs, HQ, D)).astype(np.float32))
+        self.cached = np.full(seqs, n - 1, np.int32)
+        self.bytes = attn_bytes(seqs, n)
+        self.sample = (f"decode attention, {seqs} of {B} sequences x ctx {n}, 1 layer "
+                       f"(numpy port of the reference math; the reference itself is Triton-only)")
+
+    def run(self, threads: int) -> float:
+        try:
+            from threadpoolctl import threadpool_limits
+        except ImportError:  # pragma: no cover
+            threadpool_limits = None
+        ctx = threadpool_limits(limits=threads) if threadpool_limits is not None else None
+        if ctx is not None:
+            ctx.__enter__()
+        try:
+            t0 = time.perf_counter()
+            self.O.decode_attention(self.q, self.cache, self.cached, self.table, self.seqs, D ** -0.5)
+            return time.perf_counter() - t0
+        finally:
+            if ctx is not None:
+                ctx.__exit__(None, None, None)
+
+
+def run_reference(args):
+    """--impl reference: the reference publishes no CPU implementation of this path (it is
+    Triton-only), so the CPU arm is the oracle port of its math, timed on the host cores."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    cs = CpuSample(args.batch, args.ctx, max(1, min(args.batch, args.cpu_seqs)))
+    secs = [cs.run(threads) for _ in range(args.warmup + args.steps)][args.warmup:]
+    dt = float(np.mean(secs))
+    v = cs.bytes / dt / 1e9
+    print(json.dumps({
+        "impl": "reference", "metric": "decode_attention_hbm_gbs", "value": round(v, 4), "unit": "GB/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(1e3 * dt, 3),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp32", "data": "synthetic",
+        "config": workload_config(args, l2="n/a (CPU)"),
+        "cpu_baseline": {"value": round(v, 4), "unit": "GB/s", "cores": threads, "kind": "port", "sample": cs.sample},
+        "e2e": {"value": round(v, 4), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "tokens_per_s": round(cs.seqs / dt, 3),
+    }))
+
+
+def workload_config(args, l2):
+    return {"workload": f"split-K paged int8 decode attention sweep cell B={args.batch} ctx={args.ctx} "
+                        f"(16 Q / 8 KV heads, head_dim 128, 16-token pages, random page table), "
+                        f"{args.layers} distinct layer caches per step, quantize-on-write of the new token included",
+            "batch_per_gpu": args.batch, "ctx": args.ctx, "layers": args.layers, "page_size": PAGE,
+            "sharding": "sequences across GPUs, no collective", "l2": l2}
+
+
+# ----------------------------------------------------------------------------- GPU arm
+def run_b200(args):
+    import torch
+    import torch.distributed as dist
+
+    from inference_engine_b200 import kernels as K
+    from inference_engine_b200.host_step import HostDecodeStep
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the kernels have no CPU path")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    B, n, L = args.batch, args.ctx, args.layers
+    gen = torch.Generator(device=dev).manual_seed(2 + rank)
+    pages_per_seq = (n + PAGE - 1) // PAGE
+    num_pages = B * pages_per_seq + 1
+    caches = []
+    for _ in range(L):
+        c = K.make_layer_cache(num_pages, HKV, PAGE, D, device=dev)
+        c.k.copy_(torch.randint(-127, 128, c.k.shape, generator=gen, device=dev, dtype=torch.int8))
+        c.v.copy_(torch.randint(-127, 128, c.v.shape, generator=gen, device=dev, dtype=torch.int8))
+        c.k_scale.copy_(0.01 + 0.03 * torch.rand(c.k_scale.shape, generator=gen, device=dev))
+        c.v_scale.copy_(0.01 + 0.03 * torch.rand(c.v_scale.shape, generator=gen, device=dev))
+        caches.append(c)
+    table_h = torch.randperm(num_pages - 1, generator=torch.Generator().manual_seed(2 + rank)).to(torch.int32)
+    table_h = table_h.reshape(B, pages_per_seq).contiguous().pin_memory()
+    W = (HQ + 2 * HKV) * D
+    g_cpu = torch.Generator().manual_seed(12 + rank)
+    qkv_h = torch.randn(L, B, W, generator=g_cpu).to(torch.bfloat16).pin_memory()
+    pos = torch.full((B,), n - 1, dtype=torch.int32)  # the new token is token n-1: ctx counts it
+    inv_freq = 1e6 ** (-torch.arange(0, D, 2, dtype=torch.float32) / D)
+    ang = pos[:, None, None] * inv_freq[None, None, :]
+    cos_h, sin_h = ang.cos().to(torch.bfloat16).pin_memory(), ang.sin().to(torch.bfloat16).pin_memory()
+    cached_h = pos.clone().pin_memory()
+    nd_h = torch.tensor([B], dtype=torch.int32).pin_memory()
+    out_h = torch.empty(L, B, HQ, D, dtype=torch.bfloat16).pin_memory()
+
+    step = HostDecodeStep(caches, B, HQ, HKV, D, tuple(table_h.shape))
+    step.run_host(qkv_h, cos_h, sin_h, cached_h, table_h, nd_h, out_h)  # fills the device inputs
+    torch.cuda.synchronize()
+    if K.check_status(dev):
+        raise SystemExit("device status word reports an inconsistent page table")
+    step.capture()
+
+    # a graph of decode_attention calls only (dominant kernel + its reduction), one per layer cache
+    q_dev = torch.randn(L, B, HQ, D, generator=gen, device=dev).to(torch.bfloat16)
+    attn_out = torch.empty_like(q_dev)
+
+    def attn_only():
+        for l in range(L):
+            K.decode_attention(q_dev[l], caches[l], step.dev_cached, step.dev_table, step.dev_nd, D ** -0.5, out=attn_out[l])
+
+    attn_only()
+    torch.cuda.synchronize()
+    attn_graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(attn_graph):
+        attn_only()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    for _ in range(max(args.warmup, 3)):
+        step.run_device()
+        attn_graph.replay()
+    with ClockSampler(local) as clocks:
+        ms_dev = timed(step.run_device, args.steps)
+        ms_attn = timed(attn_graph.replay, args.steps)
+        ms_e2e = timed(lambda: step.run_host(qkv_h, cos_h, sin_h, cached_h, table_h, nd_h, out_h), args.steps)
+    if K.check_status(dev):
+        raise SystemExit("device status word set during the timed region")
+
+    step_bytes = L * (attn_bytes(B, n) + B * WRITE_BYTES_PER_TOKEN)
+    peak, peak_kind = peaks()
+    value = world * step_bytes * args.steps / (ms_dev * 1e-3) / 1e9
+    e2e = world * step_bytes * args.steps / (ms_e2e * 1e-3) / 1e9
+    per_call_s = ms_attn * 1e-3 / (args.steps * L)
+    achieved = attn_bytes(B, n) / per_call_s / 1e9
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        threads = os.cpu_count() or 1
+        cs = CpuSample(B, n, max(1, min(B, args.cpu_seqs)))
+        dt = cs.run(threads)
+        cpu = {"value": round(cs.bytes / dt / 1e9, 4), "unit": "GB/s", "cores": threads, "kind": "port",
+               "sample": cs.sample, "seconds": round(dt, 2)}
+    if rank == 0:
+        print(json.dumps({
+            "metric": "decode_attention_hbm_gbs", "value": round(value, 1), "unit": "GB/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms_dev / args.steps, 4),
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8 codes, fp16 MMA operands, fp32 accumulate",
+            "data": "synthetic", "config": workload_config(args, l2=f"step streams {step_bytes / 1e9:.1f} GB per GPU, far above the 126 MB L2"),
+            "pct_of_8TBs": round(100 * value / world / 8000.0, 2),
+            "tokens_per_s": round(world * B * args.steps / (ms_dev * 1e-3), 1),
+            "roofline": {"bound": "hbm", "kernel": "decode_attn_kernel<mma> + decode_combine_kernel (one decode_attention call)",
+                         "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 4),
+                         "peak_kind": peak_kind, "us_per_call": round(per_call_s * 1e6, 2),
+                         "algorithmic_bytes_per_call": attn_bytes(B, n), "traffic": args.traffic},
+            "e2e": {"value": round(e2e, 1), "unit": "GB/s", "ms_per_step": round(ms_e2e / args.steps, 4),
+                    "h2d_bytes_per_step": step.h2d_bytes, "d2h_bytes_per_step": step.d2h_bytes},
+            "gpu_launches": args.steps * L * 3,
+            "cpu_baseline": cpu, "clocks": clocks.summary(),
+        }))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--batch", type=int, default=64, help="sequences per GPU")
+    ap.add_argument("--ctx", type=int, default=4096, help="tokens attended per sequence, the new one included")
+    ap.add_argument("--layers", type=int, default=28)
+    ap.add_argument("--cpu-seqs", type=int, default=16, help="sequences in the CPU baseline sample")
+    ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--traffic", type=float, default=None, help="ncu DRAM bytes per decode_attention call, if known")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_b200(args)
+
+
+if __name__ == "__main__":
+    main()

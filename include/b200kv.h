@@ -1,0 +1,170 @@
+/*
+ * b200kv.h — C ABI of the B200 (sm_100a) int8-KV-cache attention kernels.
+ *
+ * Drop-in boundary for the attention half of kbwal/inference-engine's Qwen3-1.7B engine:
+ * each entry point replaces one host wrapper + Triton kernel pair of the reference file
+ * qwen3-1.7b/kernels.py (cited per function).  A Python binding (ctypes) calls these with
+ * raw device pointers taken from torch tensors; nothing here knows about torch.
+ *
+ * Conventions
+ *   - Every pointer is a DEVICE pointer unless the name ends in _host.
+ *   - Strides are in ELEMENTS of the pointed-to type.  The innermost (head_dim) stride is 1.
+ *   - bf16 tensors are passed as `const void*` / `void*` (2-byte elements).
+ *   - `stream` is a cudaStream_t passed as void* (0 = legacy default stream).  All work is
+ *     enqueued on it; no entry point synchronises, allocates, frees or keeps a pointer after
+ *     it returns, and every grid is a function of the shape arguments only, so calls may be
+ *     captured in a CUDA graph (the reference engine does: engine.py:376-449).
+ *   - Return value: B200KV_OK, or a negative B200KV_E_* code, in which case NOTHING was
+ *     launched.  `status` (optional, may be NULL) is a device int32 the kernels OR error bits
+ *     into when device-side data is inconsistent (a page id or token position out of range):
+ *     the offending access is skipped, never performed.
+ *
+ * Cache layout (reference: LayerKVCache, kernels.py:11-17; allocation engine.py:472-492)
+ *   k, v          int8  [num_pages, Hkv, page_size, D]
+ *   k_scale, v_scale fp32 [num_pages, Hkv, page_size]
+ *   k_calibration fp32  [num_pages, Hkv, 1, D]
+ *   The reference's layout is the special case page_size = max_len, one page per sequence
+ *   slot, table = slot_ids.  Token t of entry b lives in page table[b*table_stride + t/page_size]
+ *   at row t % page_size; an entry's calibration row is that of its first page.
+ */
+#ifndef B200KV_H
+#define B200KV_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200KV_VERSION 1
+
+enum {
+  B200KV_OK = 0,
+  B200KV_E_NULL = -1,      /* a required pointer is NULL */
+  B200KV_E_SHAPE = -2,     /* unsupported geometry (head_dim, head counts, page size) */
+  B200KV_E_ALIGN = -3,     /* pointer or stride not aligned as the kernels need */
+  B200KV_E_WORKSPACE = -4, /* caller-provided workspace too small */
+  B200KV_E_LAUNCH = -5,    /* the CUDA runtime rejected a launch (see cudaGetLastError) */
+  B200KV_E_RANGE = -6      /* a size argument is out of the supported range */
+};
+
+/* Bits OR-ed into the optional device status word. */
+enum {
+  B200KV_S_BAD_PAGE = 1,    /* block-table entry outside [0, num_pages) */
+  B200KV_S_BAD_POSITION = 2 /* token position outside the entry's table (>= max_pages*page_size) */
+};
+
+/* One layer's cache, by value.  Mirrors LayerKVCache (kernels.py:11-17). */
+typedef struct b200kv_cache {
+  int8_t* k;
+  int8_t* v;
+  float* k_scale;
+  float* v_scale;
+  float* k_calibration;
+  int64_t stride_page;  /* codes: elements between pages (k and v share strides, kernels.py:284-287) */
+  int64_t stride_head;  /* codes: elements between kv heads */
+  int64_t stride_tok;   /* codes: elements between token rows (>= D) */
+  int64_t sstride_page; /* scales: elements between pages */
+  int64_t sstride_head; /* scales: elements between kv heads */
+  int64_t cstride_page; /* calibration: elements between pages */
+  int64_t cstride_head; /* calibration: elements between kv heads */
+  int32_t num_pages;
+  int32_t num_kv_heads;
+  int32_t page_size;
+  int32_t head_dim;
+} b200kv_cache;
+
+/* Page table of a batch: `ids` int32 [num_entries, max_pages] with row stride `stride`.
+ * The reference's `slot_ids [B]` is {ids = slot_ids, stride = 1, max_pages = 1}. */
+typedef struct b200kv_table {
+  const int32_t* ids;
+  int32_t stride;
+  int32_t max_pages;
+} b200kv_table;
+
+int b200kv_version(void);
+const char* b200kv_error_string(int code);
+
+/* Replaces fused_rope_kv_decode (kernels.py:364-544).
+ * For every entry b < *num_decoding: per-head RMSNorm + half-split RoPE of q[b] and k[b] in
+ * fp32; q_out[b] = bf16(q * calibration); k / calibration and v are quantized per head to int8
+ * with scale = max(absmax,1e-6)/127 and written at token position cached_lens[b].
+ * q [B,Hq,D], k,v [B,Hkv,D] bf16 with the given entry/head strides (views of the fused QKV
+ * row are fine); cos,sin bf16 [B, D/2] with row stride; q_out bf16 [B,Hq,D].
+ * Codes, scales and q_out are bit-identical to the reference arithmetic evaluated in IEEE fp32
+ * without FMA (sum of squares in numpy pairwise order). */
+int b200kv_write_decode(const void* q, int64_t q_stride_b, int64_t q_stride_h,
+                        const void* k, int64_t k_stride_b, int64_t k_stride_h,
+                        const void* v, int64_t v_stride_b, int64_t v_stride_h,
+                        const void* q_norm_w, const void* k_norm_w,
+                        const void* cos, int64_t cos_stride_b, const void* sin, int64_t sin_stride_b,
+                        const b200kv_cache* cache, const b200kv_table* table,
+                        const int32_t* cached_lens, const int32_t* num_decoding,
+                        void* q_out, int64_t o_stride_b, int64_t o_stride_h,
+                        int32_t B, int32_t Hq, float eps, int32_t* status, void* stream);
+
+/* Replaces fused_norm_rope_prefill (kernels.py:547-714): norm + rope of all N packed rows,
+ * bf16 outputs q_out [N,Hq,D], k_out [N,Hkv,D] (strides given). */
+int b200kv_norm_rope_prefill(const void* q, int64_t q_stride_n, int64_t q_stride_h,
+                             const void* k, int64_t k_stride_n, int64_t k_stride_h,
+                             const void* q_norm_w, const void* k_norm_w,
+                             const void* cos, int64_t cos_stride_n, const void* sin, int64_t sin_stride_n,
+                             void* q_out, int64_t qo_stride_n, int64_t qo_stride_h,
+                             void* k_out, int64_t ko_stride_n, int64_t ko_stride_h,
+                             int32_t N, int32_t Hq, int32_t Hkv, int32_t D, float eps, void* stream);
+
+/* Replaces quantize_kv_prefill (kernels.py:717-865).  k (bf16, output of norm_rope_prefill)
+ * and v [N,Hkv,D] packed rows; entry b >= *num_decoding owns rows [cu_seqlens[b], cu_seqlens[b+1]).
+ * First chunk (cached_lens[b] == 0): calibration = max(1e-3, max_t |k[t,d]|) is computed and
+ * stored; otherwise loaded.  Rows are written at token positions cached_lens[b] + t. */
+int b200kv_quantize_prefill(const void* k, int64_t k_stride_n, int64_t k_stride_h,
+                            const void* v, int64_t v_stride_n, int64_t v_stride_h,
+                            const int32_t* cu_seqlens, int32_t num_entries,
+                            const b200kv_cache* cache, const b200kv_table* table,
+                            const int32_t* cached_lens, const int32_t* num_decoding,
+                            int32_t N, int32_t* status, void* stream);
+
+/* Replaces dequantize_kv_prefix (kernels.py:868-970): rows [cu_cached[b], cu_cached[b+1]) of
+ * k_out/v_out bf16 [Hkv, capacity, D] receive bf16(code*k_scale*calibration) / bf16(code*v_scale)
+ * of entry b's first cached tokens. */
+int b200kv_dequant_prefix(const b200kv_cache* cache, const b200kv_table* table,
+                          const int32_t* cu_cached, int32_t num_entries,
+                          void* k_out, void* v_out, int64_t o_stride_h, int64_t o_stride_n,
+                          int32_t capacity, int32_t* status, void* stream);
+
+/* Replaces prefill_attention (kernels.py:973-1175): packed varlen causal attention of the
+ * prefilling entries over [dequantized prefix | own chunk].  tile_start [num_tiles] gives the
+ * first packed row of each block_m-row query tile (-1 = idle), seq_ids [N] the entry of each row. */
+int b200kv_prefill_attn(const void* q, int64_t q_stride_n, int64_t q_stride_h,
+                        const void* k, int64_t k_stride_n, int64_t k_stride_h,
+                        const void* v, int64_t v_stride_n, int64_t v_stride_h,
+                        const int32_t* seq_ids, const int32_t* cu_seqlens, const int32_t* tile_start,
+                        int32_t num_tiles, int32_t block_m,
+                        const void* k_prefix, const void* v_prefix, int64_t p_stride_h, int64_t p_stride_n,
+                        const int32_t* cu_cached,
+                        void* out, int64_t o_stride_n, int64_t o_stride_h,
+                        int32_t N, int32_t Hq, int32_t Hkv, int32_t D, void* stream);
+
+/* Bytes of fp32 workspace b200kv_decode_attn needs for a batch of B entries on a device with
+ * `sm_count` SMs (replaces the three partial buffers of kernels.py:305-311). */
+size_t b200kv_decode_attn_workspace_bytes(int32_t B, int32_t Hq, int32_t Hkv, int32_t D, int32_t sm_count);
+
+/* Replaces decode_attention (kernels.py:272-361): split-K GQA decode attention over the int8
+ * cache with in-kernel dequantization, one new token per entry, followed by the cross-split
+ * log-sum-exp reduction.  Entry b < *num_decoding attends tokens [0, cached_lens[b]] and its
+ * result is written to out[b] (bf16 [>=B,Hq,D]); other rows of `out` are not touched.
+ * q bf16 [B,Hq,D] is the q_out of b200kv_write_decode.  `variant`: 0 = tensor-core kernel
+ * (the product path), 1 = scalar CUDA-core kernel kept for cross-checking. */
+int b200kv_decode_attn(const void* q, int64_t q_stride_b, int64_t q_stride_h,
+                       const b200kv_cache* cache, const b200kv_table* table,
+                       const int32_t* cached_lens, const int32_t* num_decoding, float scale,
+                       void* out, int64_t o_stride_b, int64_t o_stride_h,
+                       void* workspace, size_t workspace_bytes,
+                       int32_t B, int32_t Hq, int32_t sm_count, int32_t variant,
+                       int32_t* status, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200KV_H */

@@ -1,0 +1,17 @@
+// Version and error-string entry points of the b200kv C ABI.
+#include "b200kv.h"
+
+extern "C" int b200kv_version(void) { return B200KV_VERSION; }
+
+extern "C" const char* b200kv_error_string(int code) {
+  switch (code) {
+    case B200KV_OK: return "ok";
+    case B200KV_E_NULL: return "a required pointer is NULL";
+    case B200KV_E_SHAPE: return "unsupported geometry (head_dim must be 128, Hq a multiple of Hkv with ratio <= 8, page_size a multiple of 16 when paged)";
+    case B200KV_E_ALIGN: return "pointer or stride not aligned (bf16 rows need 8-byte, q/out of decode attention 16-byte alignment)";
+    case B200KV_E_WORKSPACE: return "workspace too small (see b200kv_decode_attn_workspace_bytes)";
+    case B200KV_E_LAUNCH: return "CUDA launch failed";
+    case B200KV_E_RANGE: return "size argument out of range";
+    default: return "unknown b200kv error";
+  }
+}

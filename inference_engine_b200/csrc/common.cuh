@@ -1,0 +1,79 @@
+// Shared device/host helpers for the b200kv kernels (sm_100a).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "b200kv.h"
+
+namespace b200kv {
+
+constexpr int kD = 128;       // head_dim the kernels are specialised for
+constexpr int kHalfD = 64;
+
+// Device-side view of the cache + page table, passed to kernels by value.
+struct CacheView {
+  int8_t* k;
+  int8_t* v;
+  float* k_scale;
+  float* v_scale;
+  float* k_cal;
+  long long stride_page, stride_head, stride_tok;
+  long long sstride_page, sstride_head;
+  long long cstride_page, cstride_head;
+  int num_pages, Hkv, page_size;
+  const int32_t* table;
+  int table_stride, max_pages;
+};
+
+inline CacheView make_view(const b200kv_cache* c, const b200kv_table* t) {
+  CacheView w;
+  w.k = c->k; w.v = c->v; w.k_scale = c->k_scale; w.v_scale = c->v_scale; w.k_cal = c->k_calibration;
+  w.stride_page = c->stride_page; w.stride_head = c->stride_head; w.stride_tok = c->stride_tok;
+  w.sstride_page = c->sstride_page; w.sstride_head = c->sstride_head;
+  w.cstride_page = c->cstride_page; w.cstride_head = c->cstride_head;
+  w.num_pages = c->num_pages; w.Hkv = c->num_kv_heads; w.page_size = c->page_size;
+  w.table = t->ids; w.table_stride = t->stride; w.max_pages = t->max_pages;
+  return w;
+}
+
+inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+
+// Host-side validation shared by the entry points.  Returns B200KV_OK or an error code.
+inline int check_cache(const b200kv_cache* c, const b200kv_table* t) {
+  if (!c || !t || !c->k || !c->v || !c->k_scale || !c->v_scale || !c->k_calibration || !t->ids) return B200KV_E_NULL;
+  if (c->head_dim != kD || c->num_kv_heads < 1 || c->page_size < 1 || c->num_pages < 1) return B200KV_E_SHAPE;
+  if (t->max_pages < 1 || t->stride < 0) return B200KV_E_SHAPE;
+  // a 16-token tile must not straddle pages; a single page per entry may have any length
+  if (t->max_pages > 1 && (c->page_size % 16) != 0) return B200KV_E_SHAPE;
+  if (!aligned(c->k, 16) || !aligned(c->v, 16) || !aligned(c->k_scale, 16) || !aligned(c->v_scale, 16) ||
+      !aligned(c->k_calibration, 16))
+    return B200KV_E_ALIGN;
+  if (c->stride_tok < kD || (c->stride_tok % 16) || (c->stride_head % 16) || (c->stride_page % 16)) return B200KV_E_ALIGN;
+  if ((c->sstride_head % 4) || (c->sstride_page % 4) || (c->cstride_head % 4) || (c->cstride_page % 4)) return B200KV_E_ALIGN;
+  return B200KV_OK;
+}
+
+__device__ __forceinline__ float bf16_bits_to_float(uint32_t bits16) { return __uint_as_float(bits16 << 16); }
+
+__device__ __forceinline__ uint32_t float_to_bf16_bits(float x) {
+  return static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(x)));
+}
+
+// Page id of token position `pos` of entry b, or -1 (and a status bit) when out of range.
+__device__ __forceinline__ int lookup_page(const CacheView& c, int b, int pos, int32_t* status) {
+  int slot = pos / c.page_size;
+  if (pos < 0 || slot >= c.max_pages) {
+    if (status) atomicOr(status, B200KV_S_BAD_POSITION);
+    return -1;
+  }
+  int page = c.table[(long long)b * c.table_stride + slot];
+  if (page < 0 || page >= c.num_pages) {
+    if (status) atomicOr(status, B200KV_S_BAD_PAGE);
+    return -1;
+  }
+  return page;
+}
+
+}  // namespace b200kv

@@ -1,0 +1,713 @@
+// Split-K GQA decode attention over the paged int8 KV cache (sm_100a), with in-kernel
+// dequantization and a cross-split log-sum-exp reduction.  Replaces the reference's
+// decode_attention_kernel + decode_attention_combine_kernel (qwen3-1.7b/kernels.py:83-264).
+//
+// Work decomposition (device side, from cached_lens/num_decoding only, so the grid is a
+// function of shapes and the call is graph-capturable):
+//   * the unit of work is a TILE of 16 tokens of one (entry, kv head);
+//   * all tiles of the batch are laid end to end in (entry, kv head, tile) order and cut into
+//     equal contiguous ranges, one per WARP of a persistent grid (sm_count * kCtasPerSm CTAs of
+//     kWarps warps).  Every warp therefore streams the same number of bytes (+-1 tile);
+//   * a warp walks its range; whenever it finishes its part of an (entry, head) it either
+//     writes the final bf16 output (it saw the whole sequence) or an fp32 partial
+//     (acc, m, l) into one of its two workspace slots;
+//   * a second small kernel merges the partials of every split (entry, head).
+//
+// Data movement: every warp owns a private ring of kStages tiles in shared memory, filled
+// with 16-byte cp.async copies (K tile 2 KB, V tile 2 KB, 2 x 16 scales) that complete in the
+// background; no block-level barrier exists anywhere in the main loop.  Each token row is
+// 128 contiguous bytes, a (page, head) tile is 2 KB contiguous, so every copy is coalesced.
+//
+// Arithmetic (variant 0, the product path): int8 codes are widened to fp16 with byte
+// permutes (0x6400 | (code ^ 0x80) == 1152 + code, exact), and both contractions run on the
+// tensor cores as mma.m16n8k16 with the 16 tokens of a tile as one MMA dimension and the
+// G <= 8 query heads of the GQA group as the 8-wide one:
+//     S^T[tok, head] = K[tok, :] . q[head, :]          (K offset by 1152, corrected with sum(q))
+//     O^T[d, head]  += V^T[d, tok] . P'[tok, head]     (V converted exactly; P' = p * v_scale)
+// Softmax state is fp32 in registers; scores use exp2 with log2(e) folded into the scale.
+// Variant 1 does the same with fp32 FMAs on the CUDA cores and exists for cross-checking.
+#include <type_traits>
+
+#include "common.cuh"
+
+namespace b200kv {
+
+constexpr int kTile = 16;                 // tokens per tile
+constexpr int kWarps = 4;                 // warps per CTA
+constexpr int kCtasPerSm = 3;
+constexpr int kStages = 4;                // tiles in flight per warp
+constexpr int kTileBytes = 2 * kTile * kD + 2 * kTile * 4;  // K, V codes + K, V scales = 4224
+constexpr int kMaxG = 8;                  // query heads per kv head the MMA n-dimension can hold
+constexpr int kMaxB = 1 << 20;
+
+struct Partition {
+  int U;        // total tiles over all (entry, head)
+  int per;      // tiles per worker
+  int W;        // workers (warps in the grid)
+};
+
+// ------------------------------------------------------------------ small PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async4(uint32_t dst, const void* src, int src_bytes) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;\n" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+  uint32_t r;
+  asm("prmt.b32 %0, %1, %2, %3;\n" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
+  return r;
+}
+__device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
+  __half2 h = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+__device__ __forceinline__ uint32_t hsub2_u32(uint32_t a, uint32_t b) {
+  __half2 r = __hsub2(*reinterpret_cast<__half2*>(&a), *reinterpret_cast<__half2*>(&b));
+  return *reinterpret_cast<uint32_t*>(&r);
+}
+// D += A(16x16, row) * B(16x8, col), fp16 inputs, fp32 accumulate.
+__device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// ------------------------------------------------------------------ partition (all CTAs agree)
+__device__ __forceinline__ int tiles_of(const int32_t* __restrict__ cached_lens, int b, int nd) {
+  return b < nd ? (cached_lens[b] + 1 + kTile - 1) / kTile : 0;
+}
+
+// Tiles per kv head of entries [0,B), scanned by the whole CTA.  Thread i owns the `chunk`
+// consecutive entries starting at i*chunk; chunk_prefix[i] (shared, blockDim.x+1 ints) is the
+// number of tiles before that chunk, chunk_prefix[blockDim.x] the total.  When `gprefix` is
+// given (one CTA does this) the per-entry exclusive prefix [B+1] is also written to global
+// memory for the reduction kernel.
+__device__ void scan_tiles(const int32_t* __restrict__ cached_lens, int B, int nd, int chunk, int* chunk_prefix,
+                           int* __restrict__ gprefix) {
+  const int tid = threadIdx.x, nt = blockDim.x;
+  const int lo = min(tid * chunk, B), hi = min(lo + chunk, B);
+  int sum = 0;
+  for (int b = lo; b < hi; ++b) sum += tiles_of(cached_lens, b, nd);
+  chunk_prefix[tid] = sum;
+  __syncthreads();
+  if (tid < 32) {  // exclusive scan of the nt chunk sums by one warp
+    int carry = 0;
+    for (int base = 0; base < nt; base += 32) {
+      int v = (base + tid < nt) ? chunk_prefix[base + tid] : 0;
+      int incl = v;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        int y = __shfl_up_sync(0xffffffffu, incl, o);
+        if (tid >= o) incl += y;
+      }
+      if (base + tid < nt) chunk_prefix[base + tid] = carry + incl - v;
+      carry += __shfl_sync(0xffffffffu, incl, 31);
+    }
+    if (tid == 0) chunk_prefix[nt] = carry;
+  }
+  __syncthreads();
+  if (gprefix) {
+    int run = chunk_prefix[tid];
+    for (int b = lo; b < hi; ++b) {
+      gprefix[b] = run;
+      run += tiles_of(cached_lens, b, nd);
+    }
+    if (tid == 0) gprefix[B] = chunk_prefix[nt];
+  }
+}
+
+__host__ __device__ __forceinline__ Partition make_partition(int total_tiles_one_head, int Hkv, int W, int min_tiles) {
+  Partition p;
+  p.U = total_tiles_one_head * Hkv;
+  p.W = W;
+  int per = (p.U + W - 1) / W;
+  p.per = per > min_tiles ? per : min_tiles;
+  return p;
+}
+
+// Position of a warp in the flattened (entry, head, tile) list.  `base` is the flat index of
+// (entry b, head 0, tile 0).
+struct Cursor {
+  int b, h, tile, T, n, base;
+  __device__ __forceinline__ void seek(const int* chunk_prefix, int nchunks, int chunk, const int32_t* cached_lens,
+                                       int nd, int Hkv, int u) {
+    int lo = 0, hi = nchunks;  // largest chunk whose first flat index is <= u
+    while (hi - lo > 1) {
+      int mid = (lo + hi) >> 1;
+      if (Hkv * chunk_prefix[mid] <= u) lo = mid; else hi = mid;
+    }
+    b = lo * chunk;
+    int run = chunk_prefix[lo];
+    while (true) {
+      T = tiles_of(cached_lens, b, nd);
+      if (Hkv * (run + T) > u) break;
+      run += T;
+      ++b;
+    }
+    base = Hkv * run;
+    n = cached_lens[b] + 1;
+    int r = u - base;
+    h = r / T;
+    tile = r - h * T;
+  }
+  // Only called while another tile exists, so a following entry with tiles exists.
+  __device__ __forceinline__ void next(const int32_t* cached_lens, int nd, int Hkv) {
+    if (++tile < T) return;
+    tile = 0;
+    if (++h < Hkv) return;
+    h = 0;
+    base += Hkv * T;
+    do { ++b; T = tiles_of(cached_lens, b, nd); } while (T == 0);
+    n = cached_lens[b] + 1;
+  }
+};
+
+// ------------------------------------------------------------------ producer: one tile -> smem
+// Shared-memory tile: K codes [16][128] with 16-byte chunk c of row r stored at chunk
+// c ^ (4*(r&1)); V codes [16][128] with chunk c of row r at c ^ ((2*r)&7); then k_scale[16],
+// v_scale[16].  The two swizzles make the consumer's 16-byte fragment reads conflict-free.
+struct PageWindow {
+  int b, base, reg;  // `reg` of lane i holds table[b][base + i]
+};
+
+__device__ __forceinline__ void issue_tile(const CacheView& c, const Cursor& cur, PageWindow& win, uint8_t* stage,
+                                           int lane, int32_t* status) {
+  const int tok0 = cur.tile * kTile;
+  const int nvalid = min(kTile, cur.n - tok0);
+  const int slot = tok0 / c.page_size;
+  const int row0 = tok0 - slot * c.page_size;
+  if (cur.b != win.b || slot < win.base || slot >= win.base + 32) {
+    win.b = cur.b;
+    win.base = slot & ~31;
+    const int idx = win.base + lane;
+    win.reg = (idx < c.max_pages) ? c.table[(long long)cur.b * c.table_stride + idx] : -1;
+  }
+  int page = __shfl_sync(0xffffffffu, win.reg, slot - win.base);
+  bool ok = slot < c.max_pages && page >= 0 && page < c.num_pages;
+  if (!ok) {
+    if (lane == 0 && status) atomicOr(status, slot < c.max_pages ? B200KV_S_BAD_PAGE : B200KV_S_BAD_POSITION);
+    page = 0;
+  }
+  const long long code_off = page * c.stride_page + cur.h * c.stride_head + row0 * c.stride_tok;
+  const int8_t* kbase = c.k + code_off;
+  const int8_t* vbase = c.v + code_off;
+  const uint32_t sK = smem_u32(stage), sV = sK + kTile * kD, sS = sV + kTile * kD;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int chunk = lane + 32 * i, r = chunk >> 3, col = chunk & 7;
+    const bool valid = ok && r < nvalid;
+    const long long off = valid ? (r * c.stride_tok + col * 16) : 0;
+    cp_async16(sK + r * kD + ((col ^ ((r & 1) << 2)) << 4), kbase + off, valid ? 16 : 0);
+    cp_async16(sV + r * kD + ((col ^ ((2 * r) & 7)) << 4), vbase + off, valid ? 16 : 0);
+  }
+  {
+    const int r = lane & 15;
+    const bool valid = ok && r < nvalid;
+    const float* sbase = (lane < 16 ? c.k_scale : c.v_scale) + page * c.sstride_page + cur.h * c.sstride_head + row0;
+    cp_async4(sS + lane * 4, sbase + (valid ? r : 0), valid ? 4 : 0);
+  }
+}
+
+// ------------------------------------------------------------------ consumer state (tensor-core variant)
+// Lane (g = lane>>2, t = lane&3) owns query-head columns 2t and 2t+1 of every accumulator.
+struct MmaState {
+  uint32_t qb[8][2];  // q fragments (B operand of S^T = K.q), fp16, pre-scaled by 2^-e per head
+  float sfac[2];      // per column: softmax_scale * log2(e) * 2^e
+  float corr[2];      // per column: 1152 * sum_d q_fp16[d]
+  float m[2], l[2];   // running max (log2 domain) and this lane's share of the running sum
+  float o[8][4];      // O^T accumulators: m-tile j, rows d = 16g+2j (+1), columns 2t, 2t+1
+};
+
+__device__ __forceinline__ void mma_begin(MmaState& st, const uint16_t* __restrict__ q, long long q_sb, long long q_sh,
+                                          int b, int h, int G, float scale_log2, int lane) {
+  const int g = lane >> 2, t = lane & 3;
+  float f[32];
+  float amax = 0.f;
+  if (g < G) {
+    const uint16_t* row = q + b * q_sb + (long long)(h * G + g) * q_sh;
+#pragma unroll
+    for (int c = 0; c < 2; ++c)
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint4 raw = *reinterpret_cast<const uint4*>(row + 64 * c + 16 * t + 8 * half);
+        uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          f[16 * c + 8 * half + 2 * i] = bf16_bits_to_float(w[i] & 0xFFFFu);
+          f[16 * c + 8 * half + 2 * i + 1] = bf16_bits_to_float(w[i] >> 16);
+        }
+      }
+#pragma unroll
+    for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(f[i]));
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) f[i] = 0.f;
+  }
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+  // exact power-of-two pre-scale so that |q| < 2 in fp16 whatever the calibration folded into q
+  int e = (int)((__float_as_uint(amax) >> 23) & 0xFFu) - 127;
+  if (amax == 0.f || e < -100) e = 0;
+  if (e > 100) e = 100;
+  const float down = __uint_as_float((uint32_t)(127 - e) << 23), up = __uint_as_float((uint32_t)(127 + e) << 23);
+  float qsum = 0.f;
+#pragma unroll
+  for (int s = 0; s < 8; ++s) {  // k-step s = 4c + j covers d = 64c + 16t + 4j + {0,1,2,3}
+    __half2 lo = __floats2half2_rn(f[4 * s] * down, f[4 * s + 1] * down);
+    __half2 hi = __floats2half2_rn(f[4 * s + 2] * down, f[4 * s + 3] * down);
+    st.qb[s][0] = *reinterpret_cast<uint32_t*>(&lo);
+    st.qb[s][1] = *reinterpret_cast<uint32_t*>(&hi);
+    float2 a = __half22float2(lo), c2 = __half22float2(hi);
+    qsum += (a.x + a.y) + (c2.x + c2.y);
+  }
+  qsum += __shfl_xor_sync(0xffffffffu, qsum, 1);
+  qsum += __shfl_xor_sync(0xffffffffu, qsum, 2);
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    const int col = 2 * t + j;  // owned by lanes with g == col
+    float up_c = __shfl_sync(0xffffffffu, up, 4 * col);
+    float qs_c = __shfl_sync(0xffffffffu, qsum, 4 * col);
+    st.sfac[j] = col < G ? scale_log2 * up_c : 0.f;
+    st.corr[j] = col < G ? 1152.f * qs_c : 0.f;
+    st.m[j] = -INFINITY;
+    st.l[j] = 0.f;
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) st.o[j][i] = 0.f;
+}
+
+__device__ __forceinline__ void mma_tile(MmaState& st, const uint8_t* stage, int nvalid, int lane) {
+  const int g = lane >> 2, t = lane & 3;
+  const uint8_t* sK = stage;
+  const uint8_t* sV = stage + kTile * kD;
+  const float* sS = reinterpret_cast<const float*>(stage + 2 * kTile * kD);
+  constexpr uint32_t kMagic = 0x64646464u, kFlip = 0x80808080u;
+
+  // ---- S^T = K . q : rows g and g+8 of the tile, 8 k-steps of 16 channels
+  float s[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+  for (int c = 0; c < 2; ++c) {
+    const int chunk = t + 4 * c;
+    uint4 r0 = *reinterpret_cast<const uint4*>(sK + g * kD + ((chunk ^ ((g & 1) << 2)) << 4));
+    uint4 r1 = *reinterpret_cast<const uint4*>(sK + (g + 8) * kD + ((chunk ^ ((g & 1) << 2)) << 4));
+    uint32_t w0[4] = {r0.x, r0.y, r0.z, r0.w}, w1[4] = {r1.x, r1.y, r1.z, r1.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      uint32_t x0 = w0[j] ^ kFlip, x1 = w1[j] ^ kFlip;
+      mma16816(s, prmt(x0, kMagic, 0x5140u), prmt(x1, kMagic, 0x5140u), prmt(x0, kMagic, 0x7362u),
+               prmt(x1, kMagic, 0x7362u), st.qb[4 * c + j][0], st.qb[4 * c + j][1]);
+    }
+  }
+  const float ks0 = sS[g], ks1 = sS[g + 8], vs0 = sS[16 + g], vs1 = sS[24 + g];
+  const bool v0 = g < nvalid, v1 = g + 8 < nvalid;
+  // s[0]: (tok g, col 2t)  s[1]: (tok g, col 2t+1)  s[2]: (tok g+8, col 2t)  s[3]: (tok g+8, col 2t+1)
+  float p[4];
+  float alpha[2];
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    float a = v0 ? (s[j] - st.corr[j]) * (ks0 * st.sfac[j]) : -INFINITY;
+    float b = v1 ? (s[2 + j] - st.corr[j]) * (ks1 * st.sfac[j]) : -INFINITY;
+    float mx = fmaxf(a, b);
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+    const float m_new = fmaxf(st.m[j], mx);
+    alpha[j] = fast_exp2(st.m[j] - m_new);
+    const float pa = fast_exp2(a - m_new), pb = fast_exp2(b - m_new);
+    st.l[j] = st.l[j] * alpha[j] + (pa + pb);
+    st.m[j] = m_new;
+    p[j] = v0 ? pa * vs0 : 0.f;
+    p[2 + j] = v1 ? pb * vs1 : 0.f;
+  }
+  // ---- P' fragments: lane (g,t) needs, for head column g, tokens (t, t+8) and (t+4, t+12)
+  const uint32_t y0 = pack_half2(p[0], p[2]), y1 = pack_half2(p[1], p[3]);  // (tok g, tok g+8) of col 2t / 2t+1
+  const int src = 4 * t + (g >> 1);
+  const uint32_t a0 = __shfl_sync(0xffffffffu, y0, src), a1 = __shfl_sync(0xffffffffu, y1, src);
+  const uint32_t c0 = __shfl_sync(0xffffffffu, y0, src + 16), c1 = __shfl_sync(0xffffffffu, y1, src + 16);
+  const uint32_t pb0 = (g & 1) ? a1 : a0, pb1 = (g & 1) ? c1 : c0;
+
+  // ---- rescale O only when some running max moved (warp-uniform test)
+  const bool moved = (alpha[0] != 1.f) || (alpha[1] != 1.f);
+  if (__any_sync(0xffffffffu, moved)) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      st.o[j][0] *= alpha[0]; st.o[j][1] *= alpha[1];
+      st.o[j][2] *= alpha[0]; st.o[j][3] *= alpha[1];
+    }
+  }
+  // ---- O^T += V^T . P' : lane reads channels 16g..16g+15 of tokens t, t+4, t+8, t+12
+  uint32_t vw[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int r = t + 4 * i;
+    uint4 raw = *reinterpret_cast<const uint4*>(sV + r * kD + ((g ^ ((2 * r) & 7)) << 4));
+    vw[i][0] = raw.x ^ kFlip; vw[i][1] = raw.y ^ kFlip; vw[i][2] = raw.z ^ kFlip; vw[i][3] = raw.w ^ kFlip;
+  }
+  constexpr uint32_t kBias = 0x64806480u;  // half2(1152, 1152)
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const uint32_t sel = (j & 1) ? 0x7362u : 0x5140u;
+    const uint32_t xa = prmt(vw[0][j >> 1], vw[2][j >> 1], sel);  // tokens t, t+8: (d0,d0',d1,d1')
+    const uint32_t xb = prmt(vw[1][j >> 1], vw[3][j >> 1], sel);  // tokens t+4, t+12
+    mma16816(st.o[j], hsub2_u32(prmt(xa, kMagic, 0x5140u), kBias), hsub2_u32(prmt(xa, kMagic, 0x7362u), kBias),
+             hsub2_u32(prmt(xb, kMagic, 0x5140u), kBias), hsub2_u32(prmt(xb, kMagic, 0x7362u), kBias), pb0, pb1);
+  }
+}
+
+// Finish an (entry, head) segment: final bf16 rows when the warp saw every tile, otherwise an
+// fp32 partial (acc[G][128], m[G], l[G]) in workspace slot `slot`.
+__device__ __forceinline__ void mma_end(MmaState& st, bool whole, uint16_t* __restrict__ out, long long o_sb,
+                                        long long o_sh, int b, int h, int G, float* __restrict__ part_o,
+                                        float* __restrict__ part_ml, int lane) {
+  const int g = lane >> 2, t = lane & 3;
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    float l = st.l[j];
+    l += __shfl_xor_sync(0xffffffffu, l, 4);
+    l += __shfl_xor_sync(0xffffffffu, l, 8);
+    l += __shfl_xor_sync(0xffffffffu, l, 16);
+    st.l[j] = l;
+  }
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    const int col = 2 * t + j;
+    if (col >= G) continue;
+    if (whole) {
+      const float inv = 1.f / st.l[j];
+      uint32_t w[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i)  // channels 16g + 2i, 16g + 2i + 1
+        w[i] = float_to_bf16_bits(st.o[i][j] * inv) | (float_to_bf16_bits(st.o[i][2 + j] * inv) << 16);
+      uint16_t* dst = out + b * o_sb + (long long)(h * G + col) * o_sh + 16 * g;
+      *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+      *reinterpret_cast<uint4*>(dst + 8) = make_uint4(w[4], w[5], w[6], w[7]);
+    } else {
+      float* dst = part_o + col * kD + 16 * g;
+#pragma unroll
+      for (int i = 0; i < 8; i += 2)
+        *reinterpret_cast<float4*>(dst + 2 * i) = make_float4(st.o[i][j], st.o[i][2 + j], st.o[i + 1][j], st.o[i + 1][2 + j]);
+      if (g == 0) {
+        part_ml[col * 2] = st.m[j];
+        part_ml[col * 2 + 1] = st.l[j];
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------ consumer state (scalar variant)
+// Lane l: scores of token l>>1 over channels 64*(l&1).., output channels 4l..4l+3.
+struct ScalarState {
+  float m[kMaxG], l[kMaxG];
+  float o[kMaxG][4];
+  float scale_log2;
+};
+
+__device__ __forceinline__ void scalar_begin(ScalarState& st, float* qs, const uint16_t* __restrict__ q, long long q_sb,
+                                             long long q_sh, int b, int h, int G, float scale_log2, int lane) {
+  __syncwarp();
+  for (int i = lane; i < G * kD; i += 32) {
+    const int gq = i / kD, d = i - gq * kD;
+    qs[i] = bf16_bits_to_float(q[b * q_sb + (long long)(h * G + gq) * q_sh + d]);
+  }
+  __syncwarp();
+#pragma unroll
+  for (int gq = 0; gq < kMaxG; ++gq) {
+    st.m[gq] = -INFINITY; st.l[gq] = 0.f;
+    st.o[gq][0] = st.o[gq][1] = st.o[gq][2] = st.o[gq][3] = 0.f;
+  }
+  st.scale_log2 = scale_log2;
+}
+
+__device__ __forceinline__ void scalar_tile(ScalarState& st, const float* qs, float* ps, const uint8_t* stage, int nvalid,
+                                            int G, int lane) {
+  const uint8_t* sK = stage;
+  const uint8_t* sV = stage + kTile * kD;
+  const float* sS = reinterpret_cast<const float*>(stage + 2 * kTile * kD);
+  const int tok = lane >> 1, half = lane & 1;
+  float dot[kMaxG];
+#pragma unroll
+  for (int gq = 0; gq < kMaxG; ++gq) dot[gq] = 0.f;
+  for (int cc = 0; cc < 4; ++cc) {
+    const int chunk = 4 * half + cc;
+    uint4 raw = *reinterpret_cast<const uint4*>(sK + tok * kD + ((chunk ^ ((tok & 1) << 2)) << 4));
+    uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const float kf = (float)(int)(int8_t)((w[i >> 2] >> (8 * (i & 3))) & 0xFFu);
+#pragma unroll
+      for (int gq = 0; gq < kMaxG; ++gq)
+        if (gq < G) dot[gq] = fmaf(qs[gq * kD + 16 * chunk + i], kf, dot[gq]);
+    }
+  }
+  const bool valid = tok < nvalid;
+  const float ks = sS[tok], vs = sS[16 + tok];
+  float alpha[kMaxG];
+  __syncwarp();
+#pragma unroll
+  for (int gq = 0; gq < kMaxG; ++gq) {
+    if (gq >= G) continue;
+    float d = dot[gq] + __shfl_xor_sync(0xffffffffu, dot[gq], 1);
+    float sc = valid ? d * (ks * st.scale_log2) : -INFINITY;
+    float mx = sc;
+#pragma unroll
+    for (int o = 2; o < 32; o <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    const float m_new = fmaxf(st.m[gq], mx);
+    alpha[gq] = fast_exp2(st.m[gq] - m_new);
+    const float p = fast_exp2(sc - m_new);
+    float psum = half == 0 ? p : 0.f;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) psum += __shfl_xor_sync(0xffffffffu, psum, o);
+    st.l[gq] = st.l[gq] * alpha[gq] + psum;
+    st.m[gq] = m_new;
+    if (half == 0) ps[gq * kTile + tok] = valid ? p * vs : 0.f;
+  }
+  __syncwarp();
+#pragma unroll
+  for (int gq = 0; gq < kMaxG; ++gq)
+    if (gq < G) { st.o[gq][0] *= alpha[gq]; st.o[gq][1] *= alpha[gq]; st.o[gq][2] *= alpha[gq]; st.o[gq][3] *= alpha[gq]; }
+  for (int r = 0; r < kTile; ++r) {
+    const uint32_t w = *reinterpret_cast<const uint32_t*>(sV + r * kD + (((lane >> 2) ^ ((2 * r) & 7)) << 4) + 4 * (lane & 3));
+    float vf[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) vf[i] = (float)(int)(int8_t)((w >> (8 * i)) & 0xFFu);
+#pragma unroll
+    for (int gq = 0; gq < kMaxG; ++gq) {
+      if (gq >= G) continue;
+      const float pv = ps[gq * kTile + r];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) st.o[gq][i] = fmaf(pv, vf[i], st.o[gq][i]);
+    }
+  }
+}
+
+__device__ __forceinline__ void scalar_end(ScalarState& st, bool whole, uint16_t* __restrict__ out, long long o_sb,
+                                           long long o_sh, int b, int h, int G, float* __restrict__ part_o,
+                                           float* __restrict__ part_ml, int lane) {
+#pragma unroll
+  for (int gq = 0; gq < kMaxG; ++gq) {
+    if (gq >= G) continue;
+    if (whole) {
+      const float inv = 1.f / st.l[gq];
+      uint2 w;
+      w.x = float_to_bf16_bits(st.o[gq][0] * inv) | (float_to_bf16_bits(st.o[gq][1] * inv) << 16);
+      w.y = float_to_bf16_bits(st.o[gq][2] * inv) | (float_to_bf16_bits(st.o[gq][3] * inv) << 16);
+      *reinterpret_cast<uint2*>(out + b * o_sb + (long long)(h * G + gq) * o_sh + 4 * lane) = w;
+    } else {
+      *reinterpret_cast<float4*>(part_o + gq * kD + 4 * lane) = make_float4(st.o[gq][0], st.o[gq][1], st.o[gq][2], st.o[gq][3]);
+      if (lane == 0) {
+        part_ml[gq * 2] = st.m[gq];
+        part_ml[gq * 2 + 1] = st.l[gq];
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------ main kernel
+// Workspace: int32 prefix[B+1] (padded to 256 B) | float ml[W][2][G][2] | float acc[W][2][G][128]
+__host__ __device__ inline size_t ws_prefix_bytes(int B) { return (((size_t)(B + 1) * 4 + 255) / 256) * 256; }
+__host__ __device__ inline size_t ws_ml_bytes(int W, int G) { return (((size_t)W * 2 * G * 2 * 4 + 255) / 256) * 256; }
+
+template <bool kScalar>
+__global__ void __launch_bounds__(kWarps * 32, kCtasPerSm)
+decode_attn_kernel(const uint16_t* __restrict__ q, long long q_sb, long long q_sh, CacheView c,
+                   const int32_t* __restrict__ cached_lens, const int32_t* __restrict__ num_decoding, float scale_log2,
+                   uint16_t* __restrict__ out, long long o_sb, long long o_sh, uint8_t* __restrict__ workspace, int B,
+                   int G, int min_tiles, int32_t* status) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  uint8_t* ring = smem;                                                       // kWarps * kStages * kTileBytes
+  float* q_s = reinterpret_cast<float*>(ring + kWarps * kStages * kTileBytes);  // scalar variant: kWarps * (G*128 + G*16)
+  int* chunk_prefix = reinterpret_cast<int*>(q_s + (kScalar ? kWarps * (kMaxG * kD + kMaxG * kTile) : 0));
+
+  const int nd = min(*num_decoding, B);
+  const int nchunks = blockDim.x, chunk = (B + nchunks - 1) / nchunks;
+  scan_tiles(cached_lens, B, nd, chunk, chunk_prefix, blockIdx.x == 0 ? reinterpret_cast<int*>(workspace) : nullptr);
+  const int W = gridDim.x * kWarps;
+  const Partition part = make_partition(chunk_prefix[nchunks], c.Hkv, W, min_tiles);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int w = blockIdx.x * kWarps + warp;
+  const long long u_begin = (long long)w * part.per;
+  if (u_begin >= part.U) return;
+  const int u0 = (int)u_begin, u1 = min(u0 + part.per, part.U);
+  const int ntiles = u1 - u0;
+
+  float* ws_ml = reinterpret_cast<float*>(workspace + ws_prefix_bytes(B));
+  float* ws_o = reinterpret_cast<float*>(workspace + ws_prefix_bytes(B) + ws_ml_bytes(W, G));
+  uint8_t* my_ring = ring + warp * kStages * kTileBytes;
+  float* my_q = q_s + warp * (kMaxG * kD + kMaxG * kTile);
+
+  Cursor load_cur, cur;
+  load_cur.seek(chunk_prefix, nchunks, chunk, cached_lens, nd, c.Hkv, u0);
+  cur = load_cur;
+  PageWindow win{-1, 0, -1};
+
+  // prologue: kStages-1 tiles in flight
+#pragma unroll
+  for (int i = 0; i < kStages - 1; ++i) {
+    if (i < ntiles) {
+      issue_tile(c, load_cur, win, my_ring + i * kTileBytes, lane, status);
+      if (i + 1 < ntiles) load_cur.next(cached_lens, nd, c.Hkv);
+    }
+    cp_async_commit();
+  }
+
+  typename std::conditional<kScalar, ScalarState, MmaState>::type st;
+  bool fresh = true;       // next tile starts an (entry, head) segment
+  bool first_seg = true;   // that segment is the first of this warp's range
+  for (int i = 0; i < ntiles; ++i) {
+    const int ahead = i + kStages - 1;
+    if (ahead < ntiles) {
+      issue_tile(c, load_cur, win, my_ring + (ahead % kStages) * kTileBytes, lane, status);
+      if (ahead + 1 < ntiles) load_cur.next(cached_lens, nd, c.Hkv);
+    }
+    cp_async_commit();
+    cp_async_wait<kStages - 1>();
+    __syncwarp();
+
+    if (fresh) {
+      if constexpr (kScalar) scalar_begin(st, my_q, q, q_sb, q_sh, cur.b, cur.h, G, scale_log2, lane);
+      else mma_begin(st, q, q_sb, q_sh, cur.b, cur.h, G, scale_log2, lane);
+      fresh = false;
+    }
+    const uint8_t* stage = my_ring + (i % kStages) * kTileBytes;
+    const int nvalid = min(kTile, cur.n - cur.tile * kTile);
+    if constexpr (kScalar) scalar_tile(st, my_q, my_q + kMaxG * kD, stage, nvalid, G, lane);
+    else mma_tile(st, stage, nvalid, lane);
+    __syncwarp();
+
+    const bool seg_last = (cur.tile + 1 == cur.T) || (i + 1 == ntiles);
+    if (seg_last) {
+      // tiles of this (entry, head) seen by this warp end at cur.tile; they began at tile
+      // max(0, cur.tile - i_since_seg_start).  The segment is whole iff it began at tile 0 and
+      // ends at T-1; it began at tile 0 unless it is the first segment and the range started inside it.
+      const int seg_first_unit = cur.base + cur.h * cur.T;   // flat index of tile 0
+      const bool began_at_zero = seg_first_unit >= u0;
+      const bool whole = began_at_zero && (cur.tile + 1 == cur.T);
+      const int slot = first_seg ? 0 : 1;
+      float* po = ws_o + ((size_t)w * 2 + slot) * G * kD;
+      float* pml = ws_ml + ((size_t)w * 2 + slot) * G * 2;
+      if constexpr (kScalar) scalar_end(st, whole, out, o_sb, o_sh, cur.b, cur.h, G, po, pml, lane);
+      else mma_end(st, whole, out, o_sb, o_sh, cur.b, cur.h, G, po, pml, lane);
+      fresh = true;
+      first_seg = false;
+    }
+    if (i + 1 < ntiles) cur.next(cached_lens, nd, c.Hkv);
+  }
+  cp_async_wait<0>();
+}
+
+// ------------------------------------------------------------------ cross-split reduction
+// grid (B, Hkv), 128 threads (one per channel).  kernels.py:216-264, with exp2 because the
+// running maxima are kept in the log2 domain.
+__global__ void __launch_bounds__(kD)
+decode_combine_kernel(const uint8_t* __restrict__ workspace, const int32_t* __restrict__ num_decoding,
+                      uint16_t* __restrict__ out, long long o_sb, long long o_sh, int B, int Hkv, int G, int W,
+                      int min_tiles) {
+  const int b = blockIdx.x, h = blockIdx.y, d = threadIdx.x;
+  if (b >= min(*num_decoding, B)) return;
+  const int* prefix = reinterpret_cast<const int*>(workspace);
+  const int T = prefix[b + 1] - prefix[b];
+  if (T == 0) return;
+  const Partition part = make_partition(prefix[B], Hkv, W, min_tiles);
+  const int s = Hkv * prefix[b] + h * T, e = s + T;
+  const int w_first = s / part.per, w_last = (e - 1) / part.per;
+  if (w_first == w_last) return;  // one warp saw the whole sequence and wrote the output itself
+  const float* ws_ml = reinterpret_cast<const float*>(workspace + ws_prefix_bytes(B));
+  const float* ws_o = reinterpret_cast<const float*>(workspace + ws_prefix_bytes(B) + ws_ml_bytes(W, G));
+  for (int col = 0; col < G; ++col) {
+    float M = -INFINITY;
+    for (int w = w_first; w <= w_last; ++w) {
+      const int slot = (w == w_first && s > w * part.per) ? 1 : 0;
+      M = fmaxf(M, ws_ml[(((size_t)w * 2 + slot) * G + col) * 2]);
+    }
+    float acc = 0.f, L = 0.f;
+    for (int w = w_first; w <= w_last; ++w) {
+      const int slot = (w == w_first && s > w * part.per) ? 1 : 0;
+      const size_t base = ((size_t)w * 2 + slot) * G + col;
+      const float wgt = fast_exp2(ws_ml[base * 2] - M);
+      L = fmaf(ws_ml[base * 2 + 1], wgt, L);
+      acc = fmaf(ws_o[base * kD + d], wgt, acc);
+    }
+    out[b * o_sb + (long long)(h * G + col) * o_sh + d] = (uint16_t)float_to_bf16_bits(acc / L);
+  }
+}
+
+static size_t main_smem_bytes(int B, bool scalar) {
+  size_t s = (size_t)kWarps * kStages * kTileBytes;
+  if (scalar) s += (size_t)kWarps * (kMaxG * kD + kMaxG * kTile) * 4;
+  s += (size_t)(kWarps * 32 + 1) * 4;
+  (void)B;
+  return s;
+}
+
+}  // namespace b200kv
+
+using namespace b200kv;
+
+extern "C" size_t b200kv_decode_attn_workspace_bytes(int32_t B, int32_t Hq, int32_t Hkv, int32_t D, int32_t sm_count) {
+  if (B < 0 || Hq < 1 || Hkv < 1 || Hq % Hkv || D != kD || sm_count < 1) return 0;
+  const int G = Hq / Hkv;
+  const int W = sm_count * kCtasPerSm * kWarps;
+  return ws_prefix_bytes(B) + ws_ml_bytes(W, G) + (size_t)W * 2 * G * kD * 4;
+}
+
+extern "C" int b200kv_decode_attn(const void* q, int64_t q_sb, int64_t q_sh, const b200kv_cache* cache,
+                                  const b200kv_table* table, const int32_t* cached_lens, const int32_t* num_decoding,
+                                  float scale, void* out, int64_t o_sb, int64_t o_sh, void* workspace,
+                                  size_t workspace_bytes, int32_t B, int32_t Hq, int32_t sm_count, int32_t variant,
+                                  int32_t* status, void* stream) {
+  if (!q || !cached_lens || !num_decoding || !out || !workspace) return B200KV_E_NULL;
+  int rc = check_cache(cache, table);
+  if (rc) return rc;
+  const int Hkv = cache->num_kv_heads;
+  if (B < 0 || Hq < 1 || Hq % Hkv || Hq / Hkv > kMaxG || sm_count < 1 || (variant != 0 && variant != 1)) return B200KV_E_SHAPE;
+  if (B > kMaxB) return B200KV_E_RANGE;
+  if (!aligned(q, 16) || !aligned(out, 16) || !aligned(workspace, 256) || (q_sb % 8) || (q_sh % 8) || (o_sb % 8) || (o_sh % 8))
+    return B200KV_E_ALIGN;
+  if (workspace_bytes < b200kv_decode_attn_workspace_bytes(B, Hq, Hkv, kD, sm_count)) return B200KV_E_WORKSPACE;
+  if (B == 0) return B200KV_OK;
+  const int G = Hq / Hkv;
+  const int grid = sm_count * kCtasPerSm;
+  const int W = grid * kWarps;
+  const int min_tiles = 4;  // at least 64 tokens per partial, like the reference's MIN_PIECE (kernels.py:295)
+  const float scale_log2 = scale * 1.4426950408889634f;
+  cudaStream_t s = (cudaStream_t)stream;
+  const bool scalar = variant == 1;
+  const size_t smem = main_smem_bytes(B, scalar);
+  static bool attr_set[2] = {false, false};  // the opt-in to > 48 KB of dynamic shared memory is per function
+  if (!attr_set[variant]) {
+    cudaError_t e = scalar ? cudaFuncSetAttribute(decode_attn_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
+                           : cudaFuncSetAttribute(decode_attn_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return B200KV_E_LAUNCH;
+    attr_set[variant] = true;
+  }
+  CacheView view = make_view(cache, table);
+  if (scalar)
+    decode_attn_kernel<true><<<grid, kWarps * 32, smem, s>>>((const uint16_t*)q, q_sb, q_sh, view, cached_lens, num_decoding,
+                                                            scale_log2, (uint16_t*)out, o_sb, o_sh, (uint8_t*)workspace, B,
+                                                            G, min_tiles, status);
+  else
+    decode_attn_kernel<false><<<grid, kWarps * 32, smem, s>>>((const uint16_t*)q, q_sb, q_sh, view, cached_lens,
+                                                             num_decoding, scale_log2, (uint16_t*)out, o_sb, o_sh,
+                                                             (uint8_t*)workspace, B, G, min_tiles, status);
+  if (cudaGetLastError() != cudaSuccess) return B200KV_E_LAUNCH;
+  decode_combine_kernel<<<dim3(B, Hkv), kD, 0, s>>>((const uint8_t*)workspace, num_decoding, (uint16_t*)out, o_sb, o_sh, B,
+                                                    Hkv, G, W, min_tiles);
+  return cudaGetLastError() == cudaSuccess ? B200KV_OK : B200KV_E_LAUNCH;
+}

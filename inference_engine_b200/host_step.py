@@ -1,0 +1,87 @@
+"""Decode step of the attention path driven from HOST buffers.
+
+What a caller outside the GPU process boundary sees of one decode step of one layer stack:
+it hands over this step's projections (the fused QKV rows of the B new tokens, per layer),
+the rope rows and the batch metadata in pinned host memory, and reads the attention output
+back.  The int8 KV cache itself is device-resident state that persists across steps, exactly
+as in the reference engine (engine.py:472-492); it is not a per-step input.
+
+Per step and per layer this runs the two calls `AttentionLayer.forward` makes for a pure
+decode step (architecture.py:98-123): fused_rope_kv_decode, then decode_attention."""
+from __future__ import annotations
+
+import torch
+
+from . import kernels as K
+
+
+class HostDecodeStep:
+    def __init__(self, caches: list[K.LayerKVCache], B: int, Hq: int, Hkv: int, D: int, table_shape, eps: float = 1e-6):
+        dev = caches[0].k.device
+        L = len(caches)
+        self.caches, self.B, self.Hq, self.Hkv, self.D, self.eps = caches, B, Hq, Hkv, D, eps
+        W = (Hq + 2 * Hkv) * D
+        self.dev_qkv = torch.empty(L, B, W, dtype=torch.bfloat16, device=dev)
+        self.dev_cos = torch.empty(B, 1, D // 2, dtype=torch.bfloat16, device=dev)
+        self.dev_sin = torch.empty_like(self.dev_cos)
+        self.dev_cached = torch.empty(B, dtype=torch.int32, device=dev)
+        self.dev_table = torch.empty(table_shape, dtype=torch.int32, device=dev)
+        self.dev_nd = torch.empty(1, dtype=torch.int32, device=dev)
+        self.dev_out = torch.empty(L, B, Hq, D, dtype=torch.bfloat16, device=dev)
+        self.q_w = [torch.ones(D, dtype=torch.bfloat16, device=dev) for _ in range(L)]
+        self.k_w = [torch.ones(D, dtype=torch.bfloat16, device=dev) for _ in range(L)]
+        self.graph = None
+
+    def set_norm_weights(self, q_w, k_w):
+        self.q_w, self.k_w = q_w, k_w
+
+    @property
+    def h2d_bytes(self) -> int:
+        ts = (self.dev_qkv, self.dev_cos, self.dev_sin, self.dev_cached, self.dev_table, self.dev_nd)
+        return sum(t.numel() * t.element_size() for t in ts)
+
+    @property
+    def d2h_bytes(self) -> int:
+        return self.dev_out.numel() * self.dev_out.element_size()
+
+    def device_step(self):
+        """The device part: per layer, quantize-on-write of the new tokens then attention."""
+        Hq, Hkv, D = self.Hq, self.Hkv, self.D
+        for l, cache in enumerate(self.caches):
+            q, k, v = self.dev_qkv[l].split([Hq * D, Hkv * D, Hkv * D], dim=-1)
+            q = q.view(self.B, Hq, D)
+            k = k.view(self.B, Hkv, D)
+            v = v.view(self.B, Hkv, D)
+            qr = K.fused_rope_kv_decode(q, k, v, self.q_w[l], self.k_w[l], self.dev_cos, self.dev_sin, self.dev_table,
+                                        cache, self.dev_cached, self.dev_nd, self.eps)
+            K.decode_attention(qr, cache, self.dev_cached, self.dev_table, self.dev_nd, D ** -0.5, out=self.dev_out[l])
+
+    def capture(self):
+        """Record device_step into a CUDA graph (two eager warm-up runs first, like engine.py:432-449)."""
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            for _ in range(2):
+                self.device_step()
+        torch.cuda.current_stream().wait_stream(s)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.device_step()
+
+    def run_device(self):
+        if self.graph is not None:
+            self.graph.replay()
+        else:
+            self.device_step()
+
+    def run_host(self, qkv, cos, sin, cached_lens, table, num_decoding, out):
+        """All arguments are pinned host tensors; `out` receives [L, B, Hq, D] bf16.  Enqueues
+        H2D copies, the device step and the D2H copy on the current stream (no sync)."""
+        self.dev_qkv.copy_(qkv, non_blocking=True)
+        self.dev_cos.copy_(cos, non_blocking=True)
+        self.dev_sin.copy_(sin, non_blocking=True)
+        self.dev_cached.copy_(cached_lens, non_blocking=True)
+        self.dev_table.copy_(table, non_blocking=True)
+        self.dev_nd.copy_(num_decoding, non_blocking=True)
+        self.run_device()
+        out.copy_(self.dev_out, non_blocking=True)

@@ -1,0 +1,300 @@
+"""Drop-in replacement for the attention ops of the reference engine's `kernels.py`.
+
+Same names, positional signatures and semantics as kbwal/inference-engine
+qwen3-1.7b/kernels.py (LayerKVCache :11-17, decode_attention :272-361, fused_rope_kv_decode
+:483-544, fused_norm_rope_prefill :673-714, quantize_kv_prefill :826-865,
+dequantize_kv_prefix :935-970, prefill_attention :1129-1175), backed by hand-written sm_100a
+CUDA kernels reached through the C ABI in include/b200kv.h.  There is no Triton, no other
+backend and no CPU fallback: without a CUDA device and the built library every op raises.
+
+One generalisation: wherever the reference takes `slot_ids [B]` (one contiguous cache row per
+sequence), a 2-D int32 block table `[B, max_pages]` is accepted as well, in which case the
+cache tensors are read as pages `[num_pages, Hkv, page_size, D]` (page_size a multiple of 16).
+The reference layout is the one-page-per-sequence case of the same kernels.
+"""
+from __future__ import annotations
+
+import ctypes
+import functools
+from dataclasses import dataclass
+
+import torch
+import torch.nn.functional as F
+
+from . import _lib
+
+
+@dataclass
+class LayerKVCache:
+    k: torch.Tensor  # int8  [pool, Hkv, max_len, D]   (paged: [num_pages, Hkv, page_size, D])
+    v: torch.Tensor  # int8  [pool, Hkv, max_len, D]
+    k_scale: torch.Tensor  # fp32  [pool, Hkv, max_len]
+    v_scale: torch.Tensor  # fp32  [pool, Hkv, max_len]
+    k_calibration: torch.Tensor  # fp32  [pool, Hkv, 1, D]
+
+
+def make_layer_cache(num_pages: int, num_kv_heads: int, page_size: int, head_dim: int, device="cuda") -> LayerKVCache:
+    """engine.py:472-492: zeroed codes and scales, calibration of ones."""
+    return LayerKVCache(
+        k=torch.zeros(num_pages, num_kv_heads, page_size, head_dim, device=device, dtype=torch.int8),
+        v=torch.zeros(num_pages, num_kv_heads, page_size, head_dim, device=device, dtype=torch.int8),
+        k_scale=torch.zeros(num_pages, num_kv_heads, page_size, device=device, dtype=torch.float32),
+        v_scale=torch.zeros(num_pages, num_kv_heads, page_size, device=device, dtype=torch.float32),
+        k_calibration=torch.ones(num_pages, num_kv_heads, 1, head_dim, device=device, dtype=torch.float32),
+    )
+
+
+# ----------------------------------------------------------------------------- plumbing
+@functools.cache
+def num_sms(device: torch.device) -> int:
+    return torch.cuda.get_device_properties(device).multi_processor_count
+
+
+_status: dict[int, torch.Tensor] = {}
+
+
+def status_word(device: torch.device) -> torch.Tensor:
+    """Device int32 the kernels OR error bits into (bad page id / token position).  Created on
+    first use per device, so call any op once before capturing a CUDA graph."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    t = _status.get(idx)
+    if t is None:
+        t = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
+        _status[idx] = t
+    return t
+
+
+def check_status(device=None) -> int:
+    """Read and clear the status word (synchronises).  0 means no device-side error was seen."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    t = status_word(dev)
+    val = int(t.item())
+    if val:
+        t.zero_()
+    return val
+
+
+def _require_cuda(*tensors: torch.Tensor) -> None:
+    for t in tensors:
+        if not t.is_cuda:
+            raise RuntimeError("b200kv ops need CUDA tensors: there is no CPU path")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _cache_struct(cache: LayerKVCache) -> _lib.Cache:
+    k, v, ks, vs, cal = cache.k, cache.v, cache.k_scale, cache.v_scale, cache.k_calibration
+    assert k.stride() == v.stride(), "kernel uses one set of strides for k and v"
+    assert ks.stride() == vs.stride()
+    assert k.dtype == torch.int8 and v.dtype == torch.int8 and ks.dtype == torch.float32 and cal.dtype == torch.float32
+    assert k.stride(3) == 1 and ks.stride(2) == 1 and cal.stride(3) == 1
+    return _lib.Cache(
+        k.data_ptr(), v.data_ptr(), ks.data_ptr(), vs.data_ptr(), cal.data_ptr(),
+        k.stride(0), k.stride(1), k.stride(2), ks.stride(0), ks.stride(1), cal.stride(0), cal.stride(1),
+        k.shape[0], k.shape[1], k.shape[2], k.shape[3])
+
+
+def _table_struct(slot_ids: torch.Tensor) -> _lib.Table:
+    assert slot_ids.dtype == torch.int32, "slot ids / block table must be int32"
+    if slot_ids.ndim == 1:
+        assert slot_ids.numel() <= 1 or slot_ids.stride(0) >= 1
+        return _lib.Table(slot_ids.data_ptr(), slot_ids.stride(0) if slot_ids.numel() > 1 else 1, 1)
+    assert slot_ids.ndim == 2 and slot_ids.stride(1) == 1
+    return _lib.Table(slot_ids.data_ptr(), slot_ids.stride(0), slot_ids.shape[1])
+
+
+def _i32(t: torch.Tensor) -> int:
+    assert t.dtype == torch.int32 and (t.numel() <= 1 or t.stride(-1) == 1)
+    return t.data_ptr()
+
+
+def _row_stride(t: torch.Tensor) -> int:
+    """Entry stride of a [N, 1, D/2] or [N, D/2] rope table."""
+    assert t.stride(-1) == 1
+    return t.stride(0)
+
+
+# ----------------------------------------------------------------------------- ops
+def decode_attention(
+    q: torch.Tensor,  # [B, Hq, D], one new token per sequence
+    kv_cache: LayerKVCache,
+    cached_lens: torch.Tensor,  # [B], tokens already cached per sequence
+    slot_ids: torch.Tensor,  # [B] cache row per sequence, or [B, max_pages] block table
+    num_decoding: torch.Tensor,  # int32 [1]
+    scale,
+    out: torch.Tensor | None = None,  # [>= B, Hq, D]
+    variant: int = 0,
+):
+    _require_cuda(q, kv_cache.k, cached_lens, slot_ids, num_decoding)
+    lib = _lib.load()
+    B, Hq, D = q.shape
+    Hkv = kv_cache.k.shape[1]
+    assert q.dtype == torch.bfloat16 and q.stride(-1) == 1
+    if out is None:
+        out = torch.empty(B, Hq, D, device=q.device, dtype=q.dtype)
+    assert out.shape[0] >= B and out.shape[1:] == (Hq, D) and out.stride(-1) == 1
+    sms = num_sms(q.device)
+    nbytes = lib.b200kv_decode_attn_workspace_bytes(B, Hq, Hkv, D, sms)
+    if nbytes == 0:
+        raise ValueError("decode_attention: unsupported geometry")
+    workspace = torch.empty(nbytes, device=q.device, dtype=torch.uint8)
+    cs, ts = _cache_struct(kv_cache), _table_struct(slot_ids)
+    rc = lib.b200kv_decode_attn(
+        q.data_ptr(), q.stride(0), q.stride(1), ctypes.byref(cs), ctypes.byref(ts), _i32(cached_lens),
+        _i32(num_decoding), float(scale), out.data_ptr(), out.stride(0), out.stride(1), workspace.data_ptr(), nbytes,
+        B, Hq, sms, variant, status_word(q.device).data_ptr(), _stream())
+    _lib.check(rc, "decode_attention")
+    return out
+
+
+def fused_rope_kv_decode(
+    q: torch.Tensor,  # (B, Hq, D), one new token per sequence
+    k: torch.Tensor,  # (B, Hkv, D)
+    v: torch.Tensor,
+    q_norm_weight: torch.Tensor,  # (D,)
+    k_norm_weight: torch.Tensor,
+    cos: torch.Tensor,  # (B, 1, D // 2)
+    sin: torch.Tensor,
+    slot_ids: torch.Tensor,
+    kv_cache: LayerKVCache,
+    cached_lens: torch.Tensor,
+    num_decoding: torch.Tensor,
+    eps: float,
+):
+    """Returns normed + roped q (times calibration) and writes the new K/V token into the cache."""
+    _require_cuda(q, k, v, kv_cache.k)
+    lib = _lib.load()
+    B, Hq, D = q.shape
+    assert q.dtype == torch.bfloat16 and q.stride(-1) == 1 and k.stride(-1) == 1 and v.stride(-1) == 1
+    out = torch.empty(B, Hq, D, device=q.device, dtype=q.dtype)
+    cs, ts = _cache_struct(kv_cache), _table_struct(slot_ids)
+    rc = lib.b200kv_write_decode(
+        q.data_ptr(), q.stride(0), q.stride(1), k.data_ptr(), k.stride(0), k.stride(1), v.data_ptr(), v.stride(0),
+        v.stride(1), q_norm_weight.data_ptr(), k_norm_weight.data_ptr(), cos.data_ptr(), _row_stride(cos),
+        sin.data_ptr(), _row_stride(sin), ctypes.byref(cs), ctypes.byref(ts), _i32(cached_lens), _i32(num_decoding),
+        out.data_ptr(), out.stride(0), out.stride(1), B, Hq, float(eps), status_word(q.device).data_ptr(), _stream())
+    _lib.check(rc, "fused_rope_kv_decode")
+    return out
+
+
+def fused_norm_rope_prefill(
+    q: torch.Tensor,  # bf16 [N, Hq, D]
+    k: torch.Tensor,  # bf16 [N, Hkv, D]
+    q_norm_weight: torch.Tensor,
+    k_norm_weight: torch.Tensor,
+    cos: torch.Tensor,  # [N, 1, D // 2]
+    sin: torch.Tensor,
+    eps: float,
+) -> tuple[torch.Tensor, torch.Tensor]:
+    _require_cuda(q, k)
+    lib = _lib.load()
+    N, Hq, D = q.shape
+    Hkv = k.shape[1]
+    assert q.stride(-1) == 1 and k.stride(-1) == 1, "kernel assumes contiguous head_dim"
+    assert cos.stride(-1) == 1 and sin.stride(-1) == 1
+    q_out = torch.empty(N, Hq, D, device=q.device, dtype=q.dtype)
+    k_out = torch.empty(N, Hkv, D, device=k.device, dtype=k.dtype)
+    rc = lib.b200kv_norm_rope_prefill(
+        q.data_ptr(), q.stride(0), q.stride(1), k.data_ptr(), k.stride(0), k.stride(1), q_norm_weight.data_ptr(),
+        k_norm_weight.data_ptr(), cos.data_ptr(), _row_stride(cos), sin.data_ptr(), _row_stride(sin), q_out.data_ptr(),
+        q_out.stride(0), q_out.stride(1), k_out.data_ptr(), k_out.stride(0), k_out.stride(1), N, Hq, Hkv, D, float(eps),
+        _stream())
+    _lib.check(rc, "fused_norm_rope_prefill")
+    return q_out, k_out
+
+
+def quantize_kv_prefill(
+    k: torch.Tensor,  # bf16 [N, Hkv, D], all sequences packed along N
+    v: torch.Tensor,
+    cu_seqlens: torch.Tensor,  # int32 [B + 1]
+    slot_ids: torch.Tensor,
+    cached_lens: torch.Tensor,
+    num_decoding: torch.Tensor,
+    cache: LayerKVCache,
+):
+    _require_cuda(k, v, cache.k)
+    lib = _lib.load()
+    N = k.shape[0]
+    assert k.stride(-1) == 1 and v.stride(-1) == 1, "kernel assumes contiguous head_dim"
+    cs, ts = _cache_struct(cache), _table_struct(slot_ids)
+    rc = lib.b200kv_quantize_prefill(
+        k.data_ptr(), k.stride(0), k.stride(1), v.data_ptr(), v.stride(0), v.stride(1), _i32(cu_seqlens),
+        cu_seqlens.shape[0] - 1, ctypes.byref(cs), ctypes.byref(ts), _i32(cached_lens), _i32(num_decoding), N,
+        status_word(k.device).data_ptr(), _stream())
+    _lib.check(rc, "quantize_kv_prefill")
+
+
+def dequantize_kv_prefix(
+    cache: LayerKVCache,
+    cu_cached: torch.Tensor,  # int32 [B + 1]
+    slot_ids: torch.Tensor,
+    k_out: torch.Tensor,  # bf16 [Hkv, >= total_cached, D]
+    v_out: torch.Tensor,
+):
+    _require_cuda(cache.k, k_out, v_out)
+    lib = _lib.load()
+    assert k_out.stride() == v_out.stride() and k_out.stride(-1) == 1
+    cs, ts = _cache_struct(cache), _table_struct(slot_ids)
+    rc = lib.b200kv_dequant_prefix(
+        ctypes.byref(cs), ctypes.byref(ts), _i32(cu_cached), cu_cached.shape[0] - 1, k_out.data_ptr(), v_out.data_ptr(),
+        k_out.stride(0), k_out.stride(1), k_out.shape[1], status_word(k_out.device).data_ptr(), _stream())
+    _lib.check(rc, "dequantize_kv_prefix")
+
+
+def prefill_attention(
+    q: torch.Tensor,  # bf16 [N, Hq, D]
+    k: torch.Tensor,  # bf16 [N, Hkv, D]
+    v: torch.Tensor,
+    seq_ids: torch.Tensor,  # [N]
+    cu_seqlens: torch.Tensor,  # [B + 1] int32
+    tile_start: torch.Tensor,  # [num_tiles] int32
+    k_prefix: torch.Tensor,  # bf16 [Hkv, total_cached, D]
+    v_prefix: torch.Tensor,
+    cu_cached: torch.Tensor,  # [B + 1] int32
+    PREFILL_BLOCK_M: int,
+) -> torch.Tensor:
+    _require_cuda(q, k, v)
+    lib = _lib.load()
+    N, Hq, D = q.shape
+    Hkv = k.shape[1]
+    assert q.stride(-1) == 1 and k.stride(-1) == 1 and v.stride(-1) == 1
+    assert k_prefix.stride() == v_prefix.stride() and k_prefix.stride(-1) == 1
+    out = torch.empty(N, Hq, D, device=q.device, dtype=q.dtype)
+    rc = lib.b200kv_prefill_attn(
+        q.data_ptr(), q.stride(0), q.stride(1), k.data_ptr(), k.stride(0), k.stride(1), v.data_ptr(), v.stride(0),
+        v.stride(1), _i32(seq_ids), _i32(cu_seqlens), _i32(tile_start), tile_start.shape[0], int(PREFILL_BLOCK_M),
+        k_prefix.data_ptr(), v_prefix.data_ptr(), k_prefix.stride(0), k_prefix.stride(1), _i32(cu_cached),
+        out.data_ptr(), out.stride(0), out.stride(1), N, Hq, Hkv, D, _stream())
+    _lib.check(rc, "prefill_attention")
+    return out
+
+
+# ----------------------------------------------------------------------------- scaffold ops
+# The remaining names the reference's architecture.py / engine.py import from kernels.py.  They
+# are outside the attention path; plain PyTorch keeps a model built on this module runnable.
+def silu_mul(x: torch.Tensor) -> torch.Tensor:  # kernels.py:1204: [N, 2D] -> silu(gate) * up
+    gate, up = x.chunk(2, dim=-1)
+    return F.silu(gate) * up
+
+
+def add_rms_norm(residual, x, weight, eps):  # kernels.py:1261: residual += x; return (residual, rmsnorm(residual) * w)
+    residual = x if residual is None else residual + x
+    r = residual.float()
+    y = r * torch.rsqrt(r.pow(2).mean(-1, keepdim=True) + eps)
+    return residual, (y * weight.float()).to(x.dtype)
+
+
+def sample(logits: torch.Tensor, tau: float, seed: torch.Tensor) -> torch.Tensor:  # kernels.py:1341, tau = 0 only
+    if tau != 0:
+        raise NotImplementedError("only greedy sampling (tau = 0) is provided by this scaffold")
+    return logits.argmax(dim=-1, keepdim=True)
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:  # kernels.py:1465
+    return F.linear(x, weight)
+
+
+def tune_linear(weights, row_counts) -> None:  # kernels.py:1473: nothing to tune for F.linear
+    return None
