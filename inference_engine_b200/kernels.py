@@ -101,7 +101,7 @@ def _table_struct(slot_ids: torch.Tensor) -> _lib.Table:
     if slot_ids.ndim == 1:
         assert slot_ids.numel() <= 1 or slot_ids.stride(0) >= 1
         return _lib.Table(slot_ids.data_ptr(), slot_ids.stride(0) if slot_ids.numel() > 1 else 1, 1)
-    assert slot_ids.ndim == 2 and slot_ids.stride(1) == 1
+    assert slot_ids.ndim == 2 and (slot_ids.stride(1) == 1 or slot_ids.shape[1] == 1)
     return _lib.Table(slot_ids.data_ptr(), slot_ids.stride(0), slot_ids.shape[1])
 
 

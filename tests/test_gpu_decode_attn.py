@@ -94,7 +94,8 @@ def test_split_shapes(K, B, n):
     rng = np.random.default_rng(B * 100003 + n)
     got, want = run_case(K, rng, [n] * B, 16, True, 0, gauss=True)
     err = np.abs(got - want)
-    assert err.max() <= 2e-3 and err.mean() <= 2e-4, (err.max(), err.mean())
+    # outputs are below 1 in magnitude: 4e-3 is one bf16 ulp there (a rounding flip), the mean is the real gate
+    assert err.max() <= 4e-3 and err.mean() <= 1e-4, (err.max(), err.mean())
 
 
 def test_ragged_batch_and_page_sizes(K):
