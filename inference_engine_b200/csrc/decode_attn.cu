@@ -18,12 +18,14 @@
 // background; no block-level barrier exists anywhere in the main loop.  Each token row is
 // 128 contiguous bytes, a (page, head) tile is 2 KB contiguous, so every copy is coalesced.
 //
-// Arithmetic (variant 0, the product path): int8 codes are widened to fp16 with byte
-// permutes (0x6400 | (code ^ 0x80) == 1152 + code, exact), and both contractions run on the
-// tensor cores as mma.m16n8k16 with the 16 tokens of a tile as one MMA dimension and the
-// G <= 8 query heads of the GQA group as the 8-wide one:
-//     S^T[tok, head] = K[tok, :] . q[head, :]          (K offset by 1152, corrected with sum(q))
-//     O^T[d, head]  += V^T[d, tok] . P'[tok, head]     (V converted exactly; P' = p * v_scale)
+// Arithmetic (variant 0, the product path): both contractions run on the tensor cores with the
+// 16 tokens of a tile as one MMA dimension and the G <= 8 query heads of the GQA group as the
+// 8-wide one:
+//     S^T[tok, head] = K[tok, :] . q[head, :]   int8 x int8 -> int32 (mma.m16n8k32): the raw code
+//                      words are the A fragments, q is split once per segment into two int8 terms;
+//     O^T[d, head]  += V^T[d, tok] . P'[tok, head]   fp16 x fp16 -> fp32 (mma.m16n8k16): codes are
+//                      widened exactly with byte permutes (0x6400 | (code ^ 0x80) == 1152 + code,
+//                      minus 1152), P' = p * v_scale.
 // Softmax state is fp32 in registers; scores use exp2 with log2(e) folded into the scale.
 // Variant 1 does the same with fp32 FMAs on the CUDA cores and exists for cross-checking.
 #include <type_traits>
@@ -140,11 +142,12 @@ __host__ __device__ __forceinline__ Partition make_partition(int total_tiles_one
 }
 
 // Position of a warp in the flattened (entry, head, tile) list.  `base` is the flat index of
-// (entry b, head 0, tile 0).
+// (entry b, head 0, tile 0); (slot, row0) locate the tile in the entry's page table (table column
+// and first row inside that page), advanced incrementally so the hot loop never divides.
 struct Cursor {
-  int b, h, tile, T, n, base;
+  int b, h, tile, T, n, base, slot, row0;
   __device__ __forceinline__ void seek(const int* chunk_prefix, int nchunks, int chunk, const int32_t* cached_lens,
-                                       int nd, int Hkv, int u) {
+                                       int nd, int Hkv, int page_size, int u) {
     int lo = 0, hi = nchunks;  // largest chunk whose first flat index is <= u
     while (hi - lo > 1) {
       int mid = (lo + hi) >> 1;
@@ -163,11 +166,17 @@ struct Cursor {
     int r = u - base;
     h = r / T;
     tile = r - h * T;
+    slot = (tile * kTile) / page_size;
+    row0 = tile * kTile - slot * page_size;
   }
   // Only called while another tile exists, so a following entry with tiles exists.
-  __device__ __forceinline__ void next(const int32_t* cached_lens, int nd, int Hkv) {
-    if (++tile < T) return;
-    tile = 0;
+  __device__ __forceinline__ void next(const int32_t* cached_lens, int nd, int Hkv, int page_size) {
+    if (++tile < T) {
+      row0 += kTile;
+      if (row0 >= page_size) { row0 = 0; ++slot; }
+      return;
+    }
+    tile = 0; slot = 0; row0 = 0;
     if (++h < Hkv) return;
     h = 0;
     base += Hkv * T;
@@ -184,12 +193,32 @@ struct PageWindow {
   int b, base, reg;  // `reg` of lane i holds table[b][base + i]
 };
 
-__device__ __forceinline__ void issue_tile(const CacheView& c, const Cursor& cur, PageWindow& win, uint8_t* stage,
-                                           int lane, int32_t* status) {
-  const int tok0 = cur.tile * kTile;
-  const int nvalid = min(kTile, cur.n - tok0);
-  const int slot = tok0 / c.page_size;
-  const int row0 = tok0 - slot * c.page_size;
+// Per-lane constants of the copy pattern: a lane moves 16-byte chunk (lane & 7) of rows
+// (lane >> 3) + 4i, i = 0..3; both swizzles are invariant under row += 4, so chunk i lands
+// 512 bytes after chunk 0 and starts 4 * stride_tok bytes after it in global memory.
+struct LaneCopy {
+  uint32_t k_dst, v_dst, s_dst;  // shared-memory byte offsets inside a stage
+  long long g_off, g_step;       // global byte offsets inside a (page, head) tile
+  int r0, srow;
+};
+
+__device__ __forceinline__ LaneCopy make_lane_copy(const CacheView& c, int lane) {
+  LaneCopy lc;
+  lc.r0 = lane >> 3;
+  const int col = lane & 7;
+  lc.k_dst = lc.r0 * kD + ((col ^ ((lc.r0 & 1) << 2)) << 4);
+  lc.v_dst = kTile * kD + lc.r0 * kD + ((col ^ ((2 * lc.r0) & 7)) << 4);
+  lc.s_dst = 2 * kTile * kD + lane * 4;
+  lc.g_off = lc.r0 * c.stride_tok + col * 16;
+  lc.g_step = 4 * c.stride_tok;
+  lc.srow = lane & 15;
+  return lc;
+}
+
+__device__ __forceinline__ void issue_tile(const CacheView& c, const Cursor& cur, PageWindow& win, const LaneCopy& lc,
+                                           uint8_t* stage, int lane, int32_t* status) {
+  const int nvalid = min(kTile, cur.n - cur.tile * kTile);
+  const int slot = cur.slot;
   if (cur.b != win.b || slot < win.base || slot >= win.base + 32) {
     win.b = cur.b;
     win.base = slot & ~31;
@@ -197,41 +226,56 @@ __device__ __forceinline__ void issue_tile(const CacheView& c, const Cursor& cur
     win.reg = (idx < c.max_pages) ? c.table[(long long)cur.b * c.table_stride + idx] : -1;
   }
   int page = __shfl_sync(0xffffffffu, win.reg, slot - win.base);
-  bool ok = slot < c.max_pages && page >= 0 && page < c.num_pages;
+  const bool ok = slot < c.max_pages && page >= 0 && page < c.num_pages;
   if (!ok) {
     if (lane == 0 && status) atomicOr(status, slot < c.max_pages ? B200KV_S_BAD_PAGE : B200KV_S_BAD_POSITION);
     page = 0;
   }
-  const long long code_off = page * c.stride_page + cur.h * c.stride_head + row0 * c.stride_tok;
-  const int8_t* kbase = c.k + code_off;
-  const int8_t* vbase = c.v + code_off;
-  const uint32_t sK = smem_u32(stage), sV = sK + kTile * kD, sS = sV + kTile * kD;
+  const long long code_off = page * c.stride_page + cur.h * c.stride_head + cur.row0 * c.stride_tok;
+  const int8_t* ksrc = c.k + code_off + lc.g_off;
+  const int8_t* vsrc = c.v + code_off + lc.g_off;
+  const float* ssrc = (lane < 16 ? c.k_scale : c.v_scale) + page * c.sstride_page + cur.h * c.sstride_head + cur.row0;
+  const uint32_t sbase = smem_u32(stage);
+  if (ok && nvalid == kTile) {  // the common case: a full tile, no predicates
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const int chunk = lane + 32 * i, r = chunk >> 3, col = chunk & 7;
-    const bool valid = ok && r < nvalid;
-    const long long off = valid ? (r * c.stride_tok + col * 16) : 0;
-    cp_async16(sK + r * kD + ((col ^ ((r & 1) << 2)) << 4), kbase + off, valid ? 16 : 0);
-    cp_async16(sV + r * kD + ((col ^ ((2 * r) & 7)) << 4), vbase + off, valid ? 16 : 0);
-  }
-  {
-    const int r = lane & 15;
-    const bool valid = ok && r < nvalid;
-    const float* sbase = (lane < 16 ? c.k_scale : c.v_scale) + page * c.sstride_page + cur.h * c.sstride_head + row0;
-    cp_async4(sS + lane * 4, sbase + (valid ? r : 0), valid ? 4 : 0);
+    for (int i = 0; i < 4; ++i) {
+      cp_async16(sbase + lc.k_dst + 512 * i, ksrc + i * lc.g_step, 16);
+      cp_async16(sbase + lc.v_dst + 512 * i, vsrc + i * lc.g_step, 16);
+    }
+    cp_async4(sbase + lc.s_dst, ssrc + lc.srow, 4);
+  } else {  // last tile of a sequence (rows past the end are zero-filled, never read) or a bad page
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const bool valid = ok && (lc.r0 + 4 * i) < nvalid;
+      cp_async16(sbase + lc.k_dst + 512 * i, valid ? ksrc + i * lc.g_step : c.k, valid ? 16 : 0);
+      cp_async16(sbase + lc.v_dst + 512 * i, valid ? vsrc + i * lc.g_step : c.v, valid ? 16 : 0);
+    }
+    const bool valid = ok && lc.srow < nvalid;
+    cp_async4(sbase + lc.s_dst, valid ? ssrc + lc.srow : c.k_scale, valid ? 4 : 0);
   }
 }
 
 // ------------------------------------------------------------------ consumer state (tensor-core variant)
 // Lane (g = lane>>2, t = lane&3) owns query-head columns 2t and 2t+1 of every accumulator.
 struct MmaState {
-  uint32_t qb[8][2];  // q fragments (B operand of S^T = K.q), fp16, pre-scaled by 2^-e per head
-  float sfac[2];      // per column: softmax_scale * log2(e) * 2^e
-  float corr[2];      // per column: 1152 * sum_d q_fp16[d]
-  float m[2], l[2];   // running max (log2 domain) and this lane's share of the running sum
-  float o[8][4];      // O^T accumulators: m-tile j, rows d = 16g+2j (+1), columns 2t, 2t+1
+  uint32_t qh[8], ql[8];  // q as two int8 terms, q ~ s1 * (hi + lo/128); word w = channels 64c+16t+4(w&3).., c = w>>2
+  float sfac[2];          // per column: softmax_scale * log2(e) * s1 / 128
+  float m[2], l[2];       // running max (log2 domain) and this lane's share of the running sum
+  float o[8][4];          // O^T accumulators: m-tile j, rows d = 16g+2j (+1), columns 2t, 2t+1
 };
 
+// D += A(16x32, row, s8) * B(32x8, col, s8), s32 accumulate.
+__device__ __forceinline__ void imma16832(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                          uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// Start of an (entry, head) segment: load the G query heads, split each into two int8 terms
+// (per-head scale s1 = absmax/127; hi = rint(q/s1), lo = rint((q - hi*s1) * 128/s1), so the
+// representation error is below absmax * 2^-15), and reset the softmax state.
 __device__ __forceinline__ void mma_begin(MmaState& st, const uint16_t* __restrict__ q, long long q_sb, long long q_sh,
                                           int b, int h, int G, float scale_log2, int lane) {
   const int g = lane >> 2, t = lane & 3;
@@ -259,30 +303,27 @@ __device__ __forceinline__ void mma_begin(MmaState& st, const uint16_t* __restri
   }
   amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
   amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-  // exact power-of-two pre-scale so that |q| < 2 in fp16 whatever the calibration folded into q
-  int e = (int)((__float_as_uint(amax) >> 23) & 0xFFu) - 127;
-  if (amax == 0.f || e < -100) e = 0;
-  if (e > 100) e = 100;
-  const float down = __uint_as_float((uint32_t)(127 - e) << 23), up = __uint_as_float((uint32_t)(127 + e) << 23);
-  float qsum = 0.f;
+  const float s1 = amax > 0.f ? amax * (1.f / 127.f) : 1.f;
+  const float inv = 1.f / s1;
 #pragma unroll
-  for (int s = 0; s < 8; ++s) {  // k-step s = 4c + j covers d = 64c + 16t + 4j + {0,1,2,3}
-    __half2 lo = __floats2half2_rn(f[4 * s] * down, f[4 * s + 1] * down);
-    __half2 hi = __floats2half2_rn(f[4 * s + 2] * down, f[4 * s + 3] * down);
-    st.qb[s][0] = *reinterpret_cast<uint32_t*>(&lo);
-    st.qb[s][1] = *reinterpret_cast<uint32_t*>(&hi);
-    float2 a = __half22float2(lo), c2 = __half22float2(hi);
-    qsum += (a.x + a.y) + (c2.x + c2.y);
+  for (int w = 0; w < 8; ++w) {
+    uint32_t hi_w = 0, lo_w = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float x = f[4 * w + i];
+      const float hi = fminf(fmaxf(rintf(x * inv), -127.f), 127.f);
+      const float lo = fminf(fmaxf(rintf((x - hi * s1) * (128.f * inv)), -127.f), 127.f);
+      hi_w |= ((uint32_t)(int)hi & 0xFFu) << (8 * i);
+      lo_w |= ((uint32_t)(int)lo & 0xFFu) << (8 * i);
+    }
+    st.qh[w] = hi_w;
+    st.ql[w] = lo_w;
   }
-  qsum += __shfl_xor_sync(0xffffffffu, qsum, 1);
-  qsum += __shfl_xor_sync(0xffffffffu, qsum, 2);
 #pragma unroll
   for (int j = 0; j < 2; ++j) {
     const int col = 2 * t + j;  // owned by lanes with g == col
-    float up_c = __shfl_sync(0xffffffffu, up, 4 * col);
-    float qs_c = __shfl_sync(0xffffffffu, qsum, 4 * col);
-    st.sfac[j] = col < G ? scale_log2 * up_c : 0.f;
-    st.corr[j] = col < G ? 1152.f * qs_c : 0.f;
+    const float s1_c = __shfl_sync(0xffffffffu, s1, 4 * col);
+    st.sfac[j] = col < G ? scale_log2 * s1_c * (1.f / 128.f) : 0.f;
     st.m[j] = -INFINITY;
     st.l[j] = 0.f;
   }
@@ -299,41 +340,42 @@ __device__ __forceinline__ void mma_tile(MmaState& st, const uint8_t* stage, int
   const float* sS = reinterpret_cast<const float*>(stage + 2 * kTile * kD);
   constexpr uint32_t kMagic = 0x64646464u, kFlip = 0x80808080u;
 
-  // ---- S^T = K . q : rows g and g+8 of the tile, 8 k-steps of 16 channels
-  float s[4] = {0.f, 0.f, 0.f, 0.f};
+  // ---- S^T = K . q on the int8 tensor cores: raw code words are the A fragments (rows g, g+8),
+  // 4 k-steps of 32 channels, one accumulator chain per q term
+  int dh[4] = {0, 0, 0, 0}, dl[4] = {0, 0, 0, 0};
 #pragma unroll
   for (int c = 0; c < 2; ++c) {
     const int chunk = t + 4 * c;
-    uint4 r0 = *reinterpret_cast<const uint4*>(sK + g * kD + ((chunk ^ ((g & 1) << 2)) << 4));
-    uint4 r1 = *reinterpret_cast<const uint4*>(sK + (g + 8) * kD + ((chunk ^ ((g & 1) << 2)) << 4));
-    uint32_t w0[4] = {r0.x, r0.y, r0.z, r0.w}, w1[4] = {r1.x, r1.y, r1.z, r1.w};
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      uint32_t x0 = w0[j] ^ kFlip, x1 = w1[j] ^ kFlip;
-      mma16816(s, prmt(x0, kMagic, 0x5140u), prmt(x1, kMagic, 0x5140u), prmt(x0, kMagic, 0x7362u),
-               prmt(x1, kMagic, 0x7362u), st.qb[4 * c + j][0], st.qb[4 * c + j][1]);
-    }
+    const uint4 r0 = *reinterpret_cast<const uint4*>(sK + g * kD + ((chunk ^ ((g & 1) << 2)) << 4));
+    const uint4 r1 = *reinterpret_cast<const uint4*>(sK + (g + 8) * kD + ((chunk ^ ((g & 1) << 2)) << 4));
+    imma16832(dh, r0.x, r1.x, r0.y, r1.y, st.qh[4 * c], st.qh[4 * c + 1]);
+    imma16832(dl, r0.x, r1.x, r0.y, r1.y, st.ql[4 * c], st.ql[4 * c + 1]);
+    imma16832(dh, r0.z, r1.z, r0.w, r1.w, st.qh[4 * c + 2], st.qh[4 * c + 3]);
+    imma16832(dl, r0.z, r1.z, r0.w, r1.w, st.ql[4 * c + 2], st.ql[4 * c + 3]);
   }
+  float s[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) s[i] = (float)(dh[i] * 128 + dl[i]);  // |dh| <= 128*127*127, so no overflow
   const float ks0 = sS[g], ks1 = sS[g + 8], vs0 = sS[16 + g], vs1 = sS[24 + g];
-  const bool v0 = g < nvalid, v1 = g + 8 < nvalid;
+  const bool v0 = g < nvalid, v1 = g + 8 < nvalid;  // both true except in a sequence's last tile
   // s[0]: (tok g, col 2t)  s[1]: (tok g, col 2t+1)  s[2]: (tok g+8, col 2t)  s[3]: (tok g+8, col 2t+1)
   float p[4];
   float alpha[2];
 #pragma unroll
   for (int j = 0; j < 2; ++j) {
-    float a = v0 ? (s[j] - st.corr[j]) * (ks0 * st.sfac[j]) : -INFINITY;
-    float b = v1 ? (s[2 + j] - st.corr[j]) * (ks1 * st.sfac[j]) : -INFINITY;
+    const float a = v0 ? s[j] * (ks0 * st.sfac[j]) : -INFINITY;
+    const float b = v1 ? s[2 + j] * (ks1 * st.sfac[j]) : -INFINITY;
     float mx = fmaxf(a, b);
     mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
     mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
     mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
     const float m_new = fmaxf(st.m[j], mx);
     alpha[j] = fast_exp2(st.m[j] - m_new);
-    const float pa = fast_exp2(a - m_new), pb = fast_exp2(b - m_new);
+    const float pa = fast_exp2(a - m_new), pb = fast_exp2(b - m_new);  // exp2(-inf) = 0 for masked rows
     st.l[j] = st.l[j] * alpha[j] + (pa + pb);
     st.m[j] = m_new;
-    p[j] = v0 ? pa * vs0 : 0.f;
-    p[2 + j] = v1 ? pb * vs1 : 0.f;
+    p[j] = pa * vs0;      // v_scale of masked rows was zero-filled
+    p[2 + j] = pb * vs1;
   }
   // ---- P' fragments: lane (g,t) needs, for head column g, tokens (t, t+8) and (t+4, t+12)
   const uint32_t y0 = pack_half2(p[0], p[2]), y1 = pack_half2(p[1], p[3]);  // (tok g, tok g+8) of col 2t / 2t+1
@@ -553,16 +595,17 @@ decode_attn_kernel(const uint16_t* __restrict__ q, long long q_sb, long long q_s
   float* my_q = q_s + warp * (kMaxG * kD + kMaxG * kTile);
 
   Cursor load_cur, cur;
-  load_cur.seek(chunk_prefix, nchunks, chunk, cached_lens, nd, c.Hkv, u0);
+  load_cur.seek(chunk_prefix, nchunks, chunk, cached_lens, nd, c.Hkv, c.page_size, u0);
   cur = load_cur;
   PageWindow win{-1, 0, -1};
+  const LaneCopy lc = make_lane_copy(c, lane);
 
   // prologue: kStages-1 tiles in flight
 #pragma unroll
   for (int i = 0; i < kStages - 1; ++i) {
     if (i < ntiles) {
-      issue_tile(c, load_cur, win, my_ring + i * kTileBytes, lane, status);
-      if (i + 1 < ntiles) load_cur.next(cached_lens, nd, c.Hkv);
+      issue_tile(c, load_cur, win, lc, my_ring + i * kTileBytes, lane, status);
+      if (i + 1 < ntiles) load_cur.next(cached_lens, nd, c.Hkv, c.page_size);
     }
     cp_async_commit();
   }
@@ -573,8 +616,8 @@ decode_attn_kernel(const uint16_t* __restrict__ q, long long q_sb, long long q_s
   for (int i = 0; i < ntiles; ++i) {
     const int ahead = i + kStages - 1;
     if (ahead < ntiles) {
-      issue_tile(c, load_cur, win, my_ring + (ahead % kStages) * kTileBytes, lane, status);
-      if (ahead + 1 < ntiles) load_cur.next(cached_lens, nd, c.Hkv);
+      issue_tile(c, load_cur, win, lc, my_ring + (ahead % kStages) * kTileBytes, lane, status);
+      if (ahead + 1 < ntiles) load_cur.next(cached_lens, nd, c.Hkv, c.page_size);
     }
     cp_async_commit();
     cp_async_wait<kStages - 1>();
@@ -607,7 +650,7 @@ decode_attn_kernel(const uint16_t* __restrict__ q, long long q_sb, long long q_s
       fresh = true;
       first_seg = false;
     }
-    if (i + 1 < ntiles) cur.next(cached_lens, nd, c.Hkv);
+    if (i + 1 < ntiles) cur.next(cached_lens, nd, c.Hkv, c.page_size);
   }
   cp_async_wait<0>();
 }
