@@ -18,14 +18,16 @@
 // background; no block-level barrier exists anywhere in the main loop.  Each token row is
 // 128 contiguous bytes, a (page, head) tile is 2 KB contiguous, so every copy is coalesced.
 //
-// Arithmetic (variant 0, the product path): both contractions run on the tensor cores with the
-// 16 tokens of a tile as one MMA dimension and the G <= 8 query heads of the GQA group as the
-// 8-wide one:
-//     S^T[tok, head] = K[tok, :] . q[head, :]   int8 x int8 -> int32 (mma.m16n8k32): the raw code
-//                      words are the A fragments, q is split once per segment into two int8 terms;
-//     O^T[d, head]  += V^T[d, tok] . P'[tok, head]   fp16 x fp16 -> fp32 (mma.m16n8k16): codes are
-//                      widened exactly with byte permutes (0x6400 | (code ^ 0x80) == 1152 + code,
-//                      minus 1152), P' = p * v_scale.
+// Arithmetic (variant 0, the product path): both contractions run on the tensor cores.
+//     S[head, tok] = q[head, :] . K[tok, :]   int8 x int8 -> int32, mma.m16n8k32.  q is split once
+//                    per segment into two int8 terms (rows 0-7: high term of heads 0-7, rows 8-15:
+//                    low term), the RAW code words of 8 tokens are the B fragment, straight from one
+//                    16-byte shared-memory read, with no conversion at all.  Lane (g,t) ends up with
+//                    the scores of head g for tokens 2t, 2t+1, 2t+8, 2t+9 - exactly the P' fragment
+//                    the second contraction wants, so no shuffles sit between the two.
+//     O^T[d, head] += V^T[d, tok] . P'[tok, head]   fp16 x fp16 -> fp32, mma.m16n8k16.  Codes are
+//                    widened exactly with byte permutes (0x6400 | (code ^ 0x80) == 1152 + code, then
+//                    minus 1152); P' = p * v_scale.
 // Softmax state is fp32 in registers; scores use exp2 with log2(e) folded into the scale.
 // Variant 1 does the same with fp32 FMAs on the CUDA cores and exists for cross-checking.
 #include <type_traits>
@@ -41,6 +43,7 @@ constexpr int kStages = 4;                // tiles in flight per warp
 constexpr int kTileBytes = 2 * kTile * kD + 2 * kTile * 4;  // K, V codes + K, V scales = 4224
 constexpr int kMaxG = 8;                  // query heads per kv head the MMA n-dimension can hold
 constexpr int kMaxB = 1 << 20;
+static_assert((kStages & (kStages - 1)) == 0, "ring indices are masked");
 
 struct Partition {
   int U;        // total tiles over all (entry, head)
@@ -78,6 +81,17 @@ __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
 __device__ __forceinline__ uint32_t hsub2_u32(uint32_t a, uint32_t b) {
   __half2 r = __hsub2(*reinterpret_cast<__half2*>(&a), *reinterpret_cast<__half2*>(&b));
   return *reinterpret_cast<uint32_t*>(&r);
+}
+template <int kOff>
+__device__ __forceinline__ void cp_async16_imm(uint32_t dst, const void* src) {  // both addresses + kOff bytes
+  asm volatile("cp.async.cg.shared.global [%0+%2], [%1+%2], 16;\n" ::"r"(dst), "l"(src), "n"(kOff) : "memory");
+}
+// D += A(16x32, row, s8) * B(32x8, col, s8), s32 accumulate.
+__device__ __forceinline__ void imma16832(int (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 // D += A(16x16, row) * B(16x8, col), fp16 inputs, fp32 accumulate.
 __device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
@@ -141,11 +155,11 @@ __host__ __device__ __forceinline__ Partition make_partition(int total_tiles_one
   return p;
 }
 
-// Position of a warp in the flattened (entry, head, tile) list.  `base` is the flat index of
-// (entry b, head 0, tile 0); (slot, row0) locate the tile in the entry's page table (table column
-// and first row inside that page), advanced incrementally so the hot loop never divides.
+// Position in the flattened (entry, head, tile) list.  (slot, row0) locate the tile in the
+// entry's page table (table column and first row inside that page); they advance incrementally
+// so the hot loop never divides.
 struct Cursor {
-  int b, h, tile, T, n, base, slot, row0;
+  int b, h, tile, T, n, slot, row0;
   __device__ __forceinline__ void seek(const int* chunk_prefix, int nchunks, int chunk, const int32_t* cached_lens,
                                        int nd, int Hkv, int page_size, int u) {
     int lo = 0, hi = nchunks;  // largest chunk whose first flat index is <= u
@@ -161,44 +175,48 @@ struct Cursor {
       run += T;
       ++b;
     }
-    base = Hkv * run;
     n = cached_lens[b] + 1;
-    int r = u - base;
+    int r = u - Hkv * run;
     h = r / T;
     tile = r - h * T;
     slot = (tile * kTile) / page_size;
     row0 = tile * kTile - slot * page_size;
   }
-  // Only called while another tile exists, so a following entry with tiles exists.
-  __device__ __forceinline__ void next(const int32_t* cached_lens, int nd, int Hkv, int page_size) {
-    if (++tile < T) {
-      row0 += kTile;
-      if (row0 >= page_size) { row0 = 0; ++slot; }
-      return;
-    }
+  // First tile of the next (entry, head); only called while one exists.
+  __device__ __forceinline__ void next_segment(const int32_t* cached_lens, int nd, int Hkv) {
     tile = 0; slot = 0; row0 = 0;
     if (++h < Hkv) return;
     h = 0;
-    base += Hkv * T;
     do { ++b; T = tiles_of(cached_lens, b, nd); } while (T == 0);
     n = cached_lens[b] + 1;
+  }
+  // Next tile in flat order; only called while one exists.
+  __device__ __forceinline__ void next(const int32_t* cached_lens, int nd, int Hkv, int page_size) {
+    if (++tile < T) {
+      row0 += kTile;
+      const bool wrap = row0 >= page_size;
+      row0 = wrap ? 0 : row0;
+      slot += wrap ? 1 : 0;
+      return;
+    }
+    next_segment(cached_lens, nd, Hkv);
   }
 };
 
 // ------------------------------------------------------------------ producer: one tile -> smem
-// Shared-memory tile: K codes [16][128] with 16-byte chunk c of row r stored at chunk
-// c ^ (4*(r&1)); V codes [16][128] with chunk c of row r at c ^ ((2*r)&7); then k_scale[16],
-// v_scale[16].  The two swizzles make the consumer's 16-byte fragment reads conflict-free.
+// Shared-memory tile (4224 B): K codes [16][128] with 16-byte chunk c of row r stored at chunk
+// c ^ (4*(r&1)); V codes [16][128] with chunk c of row r at c ^ (r&6); then k_scale[16],
+// v_scale[16].  The swizzles make the consumer's 16-byte fragment reads conflict-free.
 struct PageWindow {
   int b, base, reg;  // `reg` of lane i holds table[b][base + i]
 };
 
 // Per-lane constants of the copy pattern: a lane moves 16-byte chunk (lane & 7) of rows
-// (lane >> 3) + 4i, i = 0..3; both swizzles are invariant under row += 4, so chunk i lands
-// 512 bytes after chunk 0 and starts 4 * stride_tok bytes after it in global memory.
+// (lane >> 3) + 4i, i = 0..3.  The K swizzle is invariant under row += 4; the V swizzle flips
+// chunk bit 2, hence two V offsets (even / odd i).
 struct LaneCopy {
-  uint32_t k_dst, v_dst, s_dst;  // shared-memory byte offsets inside a stage
-  long long g_off, g_step;       // global byte offsets inside a (page, head) tile
+  uint32_t k_dst, v_dst[2], s_dst;  // shared-memory byte offsets inside a stage (for i = 0 / 1)
+  long long g_off, g_step;          // global byte offsets inside a (page, head) tile
   int r0, srow;
 };
 
@@ -207,7 +225,8 @@ __device__ __forceinline__ LaneCopy make_lane_copy(const CacheView& c, int lane)
   lc.r0 = lane >> 3;
   const int col = lane & 7;
   lc.k_dst = lc.r0 * kD + ((col ^ ((lc.r0 & 1) << 2)) << 4);
-  lc.v_dst = kTile * kD + lc.r0 * kD + ((col ^ ((2 * lc.r0) & 7)) << 4);
+  lc.v_dst[0] = kTile * kD + lc.r0 * kD + ((col ^ (lc.r0 & 6)) << 4);
+  lc.v_dst[1] = kTile * kD + lc.r0 * kD + ((col ^ ((lc.r0 + 4) & 6)) << 4);
   lc.s_dst = 2 * kTile * kD + lane * 4;
   lc.g_off = lc.r0 * c.stride_tok + col * 16;
   lc.g_step = 4 * c.stride_tok;
@@ -216,8 +235,8 @@ __device__ __forceinline__ LaneCopy make_lane_copy(const CacheView& c, int lane)
 }
 
 __device__ __forceinline__ void issue_tile(const CacheView& c, const Cursor& cur, PageWindow& win, const LaneCopy& lc,
-                                           uint8_t* stage, int lane, int32_t* status) {
-  const int nvalid = min(kTile, cur.n - cur.tile * kTile);
+                                           uint32_t sbase, int lane, int32_t* status) {
+  const int nvalid = cur.n - cur.tile * kTile;  // >= 1; >= 16 for every tile but a sequence's last
   const int slot = cur.slot;
   if (cur.b != win.b || slot < win.base || slot >= win.base + 32) {
     win.b = cur.b;
@@ -231,16 +250,26 @@ __device__ __forceinline__ void issue_tile(const CacheView& c, const Cursor& cur
     if (lane == 0 && status) atomicOr(status, slot < c.max_pages ? B200KV_S_BAD_PAGE : B200KV_S_BAD_POSITION);
     page = 0;
   }
-  const long long code_off = page * c.stride_page + cur.h * c.stride_head + cur.row0 * c.stride_tok;
-  const int8_t* ksrc = c.k + code_off + lc.g_off;
-  const int8_t* vsrc = c.v + code_off + lc.g_off;
+  const long long code_off = page * c.stride_page + cur.h * c.stride_head + cur.row0 * c.stride_tok + lc.g_off;
+  const int8_t* ksrc = c.k + code_off;
+  const int8_t* vsrc = c.v + code_off;
   const float* ssrc = (lane < 16 ? c.k_scale : c.v_scale) + page * c.sstride_page + cur.h * c.sstride_head + cur.row0;
-  const uint32_t sbase = smem_u32(stage);
-  if (ok && nvalid == kTile) {  // the common case: a full tile, no predicates
+  if (ok && nvalid >= kTile) {  // the common case: a full tile, no predicates
+    if (c.stride_tok == kD) {   // rows are contiguous: 4 rows further is +512 bytes on both sides
+      cp_async16_imm<0>(sbase + lc.k_dst, ksrc);
+      cp_async16_imm<512>(sbase + lc.k_dst, ksrc);
+      cp_async16_imm<1024>(sbase + lc.k_dst, ksrc);
+      cp_async16_imm<1536>(sbase + lc.k_dst, ksrc);
+      cp_async16_imm<0>(sbase + lc.v_dst[0], vsrc);
+      cp_async16_imm<512>(sbase + lc.v_dst[1], vsrc);
+      cp_async16_imm<1024>(sbase + lc.v_dst[0], vsrc);
+      cp_async16_imm<1536>(sbase + lc.v_dst[1], vsrc);
+    } else {
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      cp_async16(sbase + lc.k_dst + 512 * i, ksrc + i * lc.g_step, 16);
-      cp_async16(sbase + lc.v_dst + 512 * i, vsrc + i * lc.g_step, 16);
+      for (int i = 0; i < 4; ++i) {
+        cp_async16(sbase + lc.k_dst + 512 * i, ksrc + i * lc.g_step, 16);
+        cp_async16(sbase + lc.v_dst[i & 1] + 512 * i, vsrc + i * lc.g_step, 16);
+      }
     }
     cp_async4(sbase + lc.s_dst, ssrc + lc.srow, 4);
   } else {  // last tile of a sequence (rows past the end are zero-filled, never read) or a bad page
@@ -248,7 +277,7 @@ __device__ __forceinline__ void issue_tile(const CacheView& c, const Cursor& cur
     for (int i = 0; i < 4; ++i) {
       const bool valid = ok && (lc.r0 + 4 * i) < nvalid;
       cp_async16(sbase + lc.k_dst + 512 * i, valid ? ksrc + i * lc.g_step : c.k, valid ? 16 : 0);
-      cp_async16(sbase + lc.v_dst + 512 * i, valid ? vsrc + i * lc.g_step : c.v, valid ? 16 : 0);
+      cp_async16(sbase + lc.v_dst[i & 1] + 512 * i, valid ? vsrc + i * lc.g_step : c.v, valid ? 16 : 0);
     }
     const bool valid = ok && lc.srow < nvalid;
     cp_async4(sbase + lc.s_dst, valid ? ssrc + lc.srow : c.k_scale, valid ? 4 : 0);
@@ -256,26 +285,20 @@ __device__ __forceinline__ void issue_tile(const CacheView& c, const Cursor& cur
 }
 
 // ------------------------------------------------------------------ consumer state (tensor-core variant)
-// Lane (g = lane>>2, t = lane&3) owns query-head columns 2t and 2t+1 of every accumulator.
+// Lane (g = lane>>2, t = lane&3).  Scores: head g, tokens 2t, 2t+1, 2t+8, 2t+9 of the tile.
+// Output accumulators: channels 16g+2j (+1), head columns 2t, 2t+1.
 struct MmaState {
-  uint32_t qh[8], ql[8];  // q as two int8 terms, q ~ s1 * (hi + lo/128); word w = channels 64c+16t+4(w&3).., c = w>>2
-  float sfac[2];          // per column: softmax_scale * log2(e) * s1 / 128
-  float m[2], l[2];       // running max (log2 domain) and this lane's share of the running sum
-  float o[8][4];          // O^T accumulators: m-tile j, rows d = 16g+2j (+1), columns 2t, 2t+1
+  uint32_t qa[4][4];  // A fragments of q for the 4 k-steps: {hi, lo, hi', lo'} words (see mma_begin)
+  float sfac;         // head g: softmax_scale * log2(e) * s1 / 128
+  float m, l;         // head g: running max (log2 domain, uniform over t) and this lane's share of the sum
+  float o[8][4];      // O^T accumulators: m-tile j, rows d = 16g+2j (+1), columns 2t, 2t+1
+  uint32_t k_off[2], v_off;  // lane-constant shared-memory offsets of the fragment reads
 };
 
-// D += A(16x32, row, s8) * B(32x8, col, s8), s32 accumulate.
-__device__ __forceinline__ void imma16832(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
-                                          uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-      : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
-// Start of an (entry, head) segment: load the G query heads, split each into two int8 terms
-// (per-head scale s1 = absmax/127; hi = rint(q/s1), lo = rint((q - hi*s1) * 128/s1), so the
-// representation error is below absmax * 2^-15), and reset the softmax state.
+// Start of an (entry, head) segment: load head g of the GQA group and split it into two int8
+// terms (s1 = absmax/127; hi = rint(q/s1), lo = rint((q - hi*s1) * 128/s1), so
+// q ~ s1*(hi + lo/128) with an error below absmax * 2^-15), and reset the softmax state.
+// k-step s = 2c+jj covers channels 64c + 16t + 8jj + {0..3} (first k half) and +4 (second half).
 __device__ __forceinline__ void mma_begin(MmaState& st, const uint16_t* __restrict__ q, long long q_sb, long long q_sh,
                                           int b, int h, int G, float scale_log2, int lane) {
   const int g = lane >> 2, t = lane & 3;
@@ -306,7 +329,7 @@ __device__ __forceinline__ void mma_begin(MmaState& st, const uint16_t* __restri
   const float s1 = amax > 0.f ? amax * (1.f / 127.f) : 1.f;
   const float inv = 1.f / s1;
 #pragma unroll
-  for (int w = 0; w < 8; ++w) {
+  for (int w = 0; w < 8; ++w) {  // word w = channels 64(w>>2) + 16t + 4(w&3) + {0..3}
     uint32_t hi_w = 0, lo_w = 0;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -316,122 +339,113 @@ __device__ __forceinline__ void mma_begin(MmaState& st, const uint16_t* __restri
       hi_w |= ((uint32_t)(int)hi & 0xFFu) << (8 * i);
       lo_w |= ((uint32_t)(int)lo & 0xFFu) << (8 * i);
     }
-    st.qh[w] = hi_w;
-    st.ql[w] = lo_w;
+    // A fragment of k-step w>>1: a0 = (row g: hi, k 4t..), a1 = (row g+8: lo, k 4t..), a2/a3 = k 16+4t..
+    st.qa[w >> 1][2 * (w & 1)] = hi_w;
+    st.qa[w >> 1][2 * (w & 1) + 1] = lo_w;
   }
-#pragma unroll
-  for (int j = 0; j < 2; ++j) {
-    const int col = 2 * t + j;  // owned by lanes with g == col
-    const float s1_c = __shfl_sync(0xffffffffu, s1, 4 * col);
-    st.sfac[j] = col < G ? scale_log2 * s1_c * (1.f / 128.f) : 0.f;
-    st.m[j] = -INFINITY;
-    st.l[j] = 0.f;
-  }
+  st.sfac = g < G ? scale_log2 * s1 * (1.f / 128.f) : 0.f;
+  st.m = -INFINITY;
+  st.l = 0.f;
 #pragma unroll
   for (int j = 0; j < 8; ++j)
 #pragma unroll
     for (int i = 0; i < 4; ++i) st.o[j][i] = 0.f;
 }
 
-__device__ __forceinline__ void mma_tile(MmaState& st, const uint8_t* stage, int nvalid, int lane) {
+__device__ __forceinline__ void mma_init_lane(MmaState& st, int lane) {
   const int g = lane >> 2, t = lane & 3;
-  const uint8_t* sK = stage;
-  const uint8_t* sV = stage + kTile * kD;
+  st.k_off[0] = g * kD + ((t ^ ((g & 1) << 2)) << 4);
+  st.k_off[1] = g * kD + (((t + 4) ^ ((g & 1) << 2)) << 4);
+  st.v_off = kTile * kD + 2 * t * kD + ((g ^ (2 * t)) << 4);
+}
+
+__device__ __forceinline__ void mma_tile(MmaState& st, const uint8_t* stage, int nvalid, int lane) {
+  const int t = lane & 3;
   const float* sS = reinterpret_cast<const float*>(stage + 2 * kTile * kD);
   constexpr uint32_t kMagic = 0x64646464u, kFlip = 0x80808080u;
 
-  // ---- S^T = K . q on the int8 tensor cores: raw code words are the A fragments (rows g, g+8),
-  // 4 k-steps of 32 channels, one accumulator chain per q term
-  int dh[4] = {0, 0, 0, 0}, dl[4] = {0, 0, 0, 0};
+  // ---- S = q . K^T on the int8 tensor cores.  B fragment of lane (g,t): token g (first MMA
+  // group) / g+8 (second), raw code words; one 16-byte read feeds two k-steps.
+  int c1[4] = {0, 0, 0, 0}, c2[4] = {0, 0, 0, 0};
 #pragma unroll
   for (int c = 0; c < 2; ++c) {
-    const int chunk = t + 4 * c;
-    const uint4 r0 = *reinterpret_cast<const uint4*>(sK + g * kD + ((chunk ^ ((g & 1) << 2)) << 4));
-    const uint4 r1 = *reinterpret_cast<const uint4*>(sK + (g + 8) * kD + ((chunk ^ ((g & 1) << 2)) << 4));
-    imma16832(dh, r0.x, r1.x, r0.y, r1.y, st.qh[4 * c], st.qh[4 * c + 1]);
-    imma16832(dl, r0.x, r1.x, r0.y, r1.y, st.ql[4 * c], st.ql[4 * c + 1]);
-    imma16832(dh, r0.z, r1.z, r0.w, r1.w, st.qh[4 * c + 2], st.qh[4 * c + 3]);
-    imma16832(dl, r0.z, r1.z, r0.w, r1.w, st.ql[4 * c + 2], st.ql[4 * c + 3]);
+    const uint4 w0 = *reinterpret_cast<const uint4*>(stage + st.k_off[c]);
+    const uint4 w1 = *reinterpret_cast<const uint4*>(stage + st.k_off[c] + 8 * kD);
+    imma16832(c1, st.qa[2 * c], w0.x, w0.y);
+    imma16832(c2, st.qa[2 * c], w1.x, w1.y);
+    imma16832(c1, st.qa[2 * c + 1], w0.z, w0.w);
+    imma16832(c2, st.qa[2 * c + 1], w1.z, w1.w);
   }
-  float s[4];
-#pragma unroll
-  for (int i = 0; i < 4; ++i) s[i] = (float)(dh[i] * 128 + dl[i]);  // |dh| <= 128*127*127, so no overflow
-  const float ks0 = sS[g], ks1 = sS[g + 8], vs0 = sS[16 + g], vs1 = sS[24 + g];
-  const bool v0 = g < nvalid, v1 = g + 8 < nvalid;  // both true except in a sequence's last tile
-  // s[0]: (tok g, col 2t)  s[1]: (tok g, col 2t+1)  s[2]: (tok g+8, col 2t)  s[3]: (tok g+8, col 2t+1)
-  float p[4];
-  float alpha[2];
-#pragma unroll
-  for (int j = 0; j < 2; ++j) {
-    const float a = v0 ? s[j] * (ks0 * st.sfac[j]) : -INFINITY;
-    const float b = v1 ? s[2 + j] * (ks1 * st.sfac[j]) : -INFINITY;
-    float mx = fmaxf(a, b);
-    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
-    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
-    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
-    const float m_new = fmaxf(st.m[j], mx);
-    alpha[j] = fast_exp2(st.m[j] - m_new);
-    const float pa = fast_exp2(a - m_new), pb = fast_exp2(b - m_new);  // exp2(-inf) = 0 for masked rows
-    st.l[j] = st.l[j] * alpha[j] + (pa + pb);
-    st.m[j] = m_new;
-    p[j] = pa * vs0;      // v_scale of masked rows was zero-filled
-    p[2 + j] = pb * vs1;
+  // rows g (high term) and g+8 (low term) of head g, tokens 2t, 2t+1 (c1) and 2t+8, 2t+9 (c2)
+  const float2 ks_a = *reinterpret_cast<const float2*>(sS + 2 * t), ks_b = *reinterpret_cast<const float2*>(sS + 8 + 2 * t);
+  const float2 vs_a = *reinterpret_cast<const float2*>(sS + 16 + 2 * t), vs_b = *reinterpret_cast<const float2*>(sS + 24 + 2 * t);
+  float a[4];
+  a[0] = (float)(c1[0] * 128 + c1[2]) * (ks_a.x * st.sfac);  // |hi| <= 128*127*127, so no overflow
+  a[1] = (float)(c1[1] * 128 + c1[3]) * (ks_a.y * st.sfac);
+  a[2] = (float)(c2[0] * 128 + c2[2]) * (ks_b.x * st.sfac);
+  a[3] = (float)(c2[1] * 128 + c2[3]) * (ks_b.y * st.sfac);
+  if (nvalid < kTile) {  // a sequence's last tile: rows past the end do not exist (their scales were zero-filled)
+    if (2 * t >= nvalid) a[0] = -INFINITY;
+    if (2 * t + 1 >= nvalid) a[1] = -INFINITY;
+    if (2 * t + 8 >= nvalid) a[2] = -INFINITY;
+    if (2 * t + 9 >= nvalid) a[3] = -INFINITY;
   }
-  // ---- P' fragments: lane (g,t) needs, for head column g, tokens (t, t+8) and (t+4, t+12)
-  const uint32_t y0 = pack_half2(p[0], p[2]), y1 = pack_half2(p[1], p[3]);  // (tok g, tok g+8) of col 2t / 2t+1
-  const int src = 4 * t + (g >> 1);
-  const uint32_t a0 = __shfl_sync(0xffffffffu, y0, src), a1 = __shfl_sync(0xffffffffu, y1, src);
-  const uint32_t c0 = __shfl_sync(0xffffffffu, y0, src + 16), c1 = __shfl_sync(0xffffffffu, y1, src + 16);
-  const uint32_t pb0 = (g & 1) ? a1 : a0, pb1 = (g & 1) ? c1 : c0;
+  float mx = fmaxf(fmaxf(a[0], a[1]), fmaxf(a[2], a[3]));
+  mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+  mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+  const float m_new = fmaxf(st.m, mx);
+  const float alpha = fast_exp2(st.m - m_new);
+  const float p0 = fast_exp2(a[0] - m_new), p1 = fast_exp2(a[1] - m_new);  // exp2(-inf) = 0 for masked rows
+  const float p2 = fast_exp2(a[2] - m_new), p3 = fast_exp2(a[3] - m_new);
+  st.l = st.l * alpha + ((p0 + p1) + (p2 + p3));
+  st.m = m_new;
+  // P' = p * v_scale is already the B fragment of the second contraction: k = 2t, 2t+1 | 2t+8, 2t+9, n = head g
+  const uint32_t pb0 = pack_half2(p0 * vs_a.x, p1 * vs_a.y), pb1 = pack_half2(p2 * vs_b.x, p3 * vs_b.y);
 
-  // ---- rescale O only when some running max moved (warp-uniform test)
-  const bool moved = (alpha[0] != 1.f) || (alpha[1] != 1.f);
-  if (__any_sync(0xffffffffu, moved)) {
+  // ---- rescale O only when some running max moved (warp-uniform test); columns 2t, 2t+1 belong to
+  // heads whose state lives in lanes 8t.. and 8t+4..
+  if (__any_sync(0xffffffffu, alpha != 1.f)) {
+    const float al0 = __shfl_sync(0xffffffffu, alpha, 8 * t), al1 = __shfl_sync(0xffffffffu, alpha, 8 * t + 4);
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      st.o[j][0] *= alpha[0]; st.o[j][1] *= alpha[1];
-      st.o[j][2] *= alpha[0]; st.o[j][3] *= alpha[1];
+      st.o[j][0] *= al0; st.o[j][1] *= al1;
+      st.o[j][2] *= al0; st.o[j][3] *= al1;
     }
   }
-  // ---- O^T += V^T . P' : lane reads channels 16g..16g+15 of tokens t, t+4, t+8, t+12
+  // ---- O^T += V^T . P' : lane reads channels 16g..16g+15 of tokens 2t, 2t+1, 2t+8, 2t+9
   uint32_t vw[4][4];
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    const int r = t + 4 * i;
-    uint4 raw = *reinterpret_cast<const uint4*>(sV + r * kD + ((g ^ ((2 * r) & 7)) << 4));
+    const uint4 raw = *reinterpret_cast<const uint4*>(stage + st.v_off + (i & 1) * kD + (i >> 1) * 8 * kD);
     vw[i][0] = raw.x ^ kFlip; vw[i][1] = raw.y ^ kFlip; vw[i][2] = raw.z ^ kFlip; vw[i][3] = raw.w ^ kFlip;
   }
   constexpr uint32_t kBias = 0x64806480u;  // half2(1152, 1152)
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
     const uint32_t sel = (j & 1) ? 0x7362u : 0x5140u;
-    const uint32_t xa = prmt(vw[0][j >> 1], vw[2][j >> 1], sel);  // tokens t, t+8: (d0,d0',d1,d1')
-    const uint32_t xb = prmt(vw[1][j >> 1], vw[3][j >> 1], sel);  // tokens t+4, t+12
+    const uint32_t xa = prmt(vw[0][j >> 1], vw[1][j >> 1], sel);  // tokens 2t, 2t+1: (d0,d0',d1,d1')
+    const uint32_t xb = prmt(vw[2][j >> 1], vw[3][j >> 1], sel);  // tokens 2t+8, 2t+9
     mma16816(st.o[j], hsub2_u32(prmt(xa, kMagic, 0x5140u), kBias), hsub2_u32(prmt(xa, kMagic, 0x7362u), kBias),
              hsub2_u32(prmt(xb, kMagic, 0x5140u), kBias), hsub2_u32(prmt(xb, kMagic, 0x7362u), kBias), pb0, pb1);
   }
 }
 
 // Finish an (entry, head) segment: final bf16 rows when the warp saw every tile, otherwise an
-// fp32 partial (acc[G][128], m[G], l[G]) in workspace slot `slot`.
+// fp32 partial (acc[G][128], m[G], l[G]) in the given workspace slot.
 __device__ __forceinline__ void mma_end(MmaState& st, bool whole, uint16_t* __restrict__ out, long long o_sb,
                                         long long o_sh, int b, int h, int G, float* __restrict__ part_o,
                                         float* __restrict__ part_ml, int lane) {
   const int g = lane >> 2, t = lane & 3;
+  float l = st.l;
+  l += __shfl_xor_sync(0xffffffffu, l, 1);
+  l += __shfl_xor_sync(0xffffffffu, l, 2);
 #pragma unroll
   for (int j = 0; j < 2; ++j) {
-    float l = st.l[j];
-    l += __shfl_xor_sync(0xffffffffu, l, 4);
-    l += __shfl_xor_sync(0xffffffffu, l, 8);
-    l += __shfl_xor_sync(0xffffffffu, l, 16);
-    st.l[j] = l;
-  }
-#pragma unroll
-  for (int j = 0; j < 2; ++j) {
-    const int col = 2 * t + j;
+    const int col = 2 * t + j;  // this lane's output column; its softmax state lives in lanes 4*col..
+    const float l_c = __shfl_sync(0xffffffffu, l, 4 * col), m_c = __shfl_sync(0xffffffffu, st.m, 4 * col);
     if (col >= G) continue;
     if (whole) {
-      const float inv = 1.f / st.l[j];
+      const float inv = 1.f / l_c;
       uint32_t w[8];
 #pragma unroll
       for (int i = 0; i < 8; ++i)  // channels 16g + 2i, 16g + 2i + 1
@@ -445,8 +459,8 @@ __device__ __forceinline__ void mma_end(MmaState& st, bool whole, uint16_t* __re
       for (int i = 0; i < 8; i += 2)
         *reinterpret_cast<float4*>(dst + 2 * i) = make_float4(st.o[i][j], st.o[i][2 + j], st.o[i + 1][j], st.o[i + 1][2 + j]);
       if (g == 0) {
-        part_ml[col * 2] = st.m[j];
-        part_ml[col * 2 + 1] = st.l[j];
+        part_ml[col * 2] = m_c;
+        part_ml[col * 2 + 1] = l_c;
       }
     }
   }
@@ -524,7 +538,7 @@ __device__ __forceinline__ void scalar_tile(ScalarState& st, const float* qs, fl
   for (int gq = 0; gq < kMaxG; ++gq)
     if (gq < G) { st.o[gq][0] *= alpha[gq]; st.o[gq][1] *= alpha[gq]; st.o[gq][2] *= alpha[gq]; st.o[gq][3] *= alpha[gq]; }
   for (int r = 0; r < kTile; ++r) {
-    const uint32_t w = *reinterpret_cast<const uint32_t*>(sV + r * kD + (((lane >> 2) ^ ((2 * r) & 7)) << 4) + 4 * (lane & 3));
+    const uint32_t w = *reinterpret_cast<const uint32_t*>(sV + r * kD + (((lane >> 2) ^ (r & 6)) << 4) + 4 * (lane & 3));
     float vf[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) vf[i] = (float)(int)(int8_t)((w >> (8 * i)) & 0xFFu);
@@ -586,71 +600,66 @@ decode_attn_kernel(const uint16_t* __restrict__ q, long long q_sb, long long q_s
   const int w = blockIdx.x * kWarps + warp;
   const long long u_begin = (long long)w * part.per;
   if (u_begin >= part.U) return;
-  const int u0 = (int)u_begin, u1 = min(u0 + part.per, part.U);
-  const int ntiles = u1 - u0;
+  const int u0 = (int)u_begin;
+  const int ntiles = min(part.per, part.U - u0);
 
   float* ws_ml = reinterpret_cast<float*>(workspace + ws_prefix_bytes(B));
   float* ws_o = reinterpret_cast<float*>(workspace + ws_prefix_bytes(B) + ws_ml_bytes(W, G));
   uint8_t* my_ring = ring + warp * kStages * kTileBytes;
+  const uint32_t my_ring_s = smem_u32(my_ring);
   float* my_q = q_s + warp * (kMaxG * kD + kMaxG * kTile);
 
-  Cursor load_cur, cur;
-  load_cur.seek(chunk_prefix, nchunks, chunk, cached_lens, nd, c.Hkv, c.page_size, u0);
-  cur = load_cur;
+  Cursor pc;  // producer position (runs kStages-1 tiles ahead of the consumer)
+  pc.seek(chunk_prefix, nchunks, chunk, cached_lens, nd, c.Hkv, c.page_size, u0);
+  Cursor cc = pc;  // consumer position, advanced segment by segment
   PageWindow win{-1, 0, -1};
   const LaneCopy lc = make_lane_copy(c, lane);
 
-  // prologue: kStages-1 tiles in flight
+  int p_left = ntiles;  // tiles not yet issued
 #pragma unroll
   for (int i = 0; i < kStages - 1; ++i) {
-    if (i < ntiles) {
-      issue_tile(c, load_cur, win, lc, my_ring + i * kTileBytes, lane, status);
-      if (i + 1 < ntiles) load_cur.next(cached_lens, nd, c.Hkv, c.page_size);
+    if (p_left > 0) {
+      issue_tile(c, pc, win, lc, my_ring_s + i * kTileBytes, lane, status);
+      if (--p_left > 0) pc.next(cached_lens, nd, c.Hkv, c.page_size);
     }
     cp_async_commit();
   }
 
   typename std::conditional<kScalar, ScalarState, MmaState>::type st;
-  bool fresh = true;       // next tile starts an (entry, head) segment
-  bool first_seg = true;   // that segment is the first of this warp's range
-  for (int i = 0; i < ntiles; ++i) {
-    const int ahead = i + kStages - 1;
-    if (ahead < ntiles) {
-      issue_tile(c, load_cur, win, lc, my_ring + (ahead % kStages) * kTileBytes, lane, status);
-      if (ahead + 1 < ntiles) load_cur.next(cached_lens, nd, c.Hkv, c.page_size);
+  if constexpr (!kScalar) mma_init_lane(st, lane);
+  int stage_c = 0, stage_p = kStages - 1;  // ring slots of the tile consumed / issued next
+  int done = 0;
+  while (done < ntiles) {
+    // one segment: the tiles [cc.tile, cc.tile + seg) of (entry cc.b, head cc.h)
+    const int seg = min(cc.T - cc.tile, ntiles - done);
+    if constexpr (kScalar) scalar_begin(st, my_q, q, q_sb, q_sh, cc.b, cc.h, G, scale_log2, lane);
+    else mma_begin(st, q, q_sb, q_sh, cc.b, cc.h, G, scale_log2, lane);
+    int remaining = cc.n - cc.tile * kTile;  // tokens from this tile to the end of the sequence
+    for (int k = 0; k < seg; ++k) {
+      if (p_left > 0) {
+        issue_tile(c, pc, win, lc, my_ring_s + stage_p * kTileBytes, lane, status);
+        if (--p_left > 0) pc.next(cached_lens, nd, c.Hkv, c.page_size);
+      }
+      cp_async_commit();
+      cp_async_wait<kStages - 1>();
+      __syncwarp();
+      const uint8_t* stage = my_ring + stage_c * kTileBytes;
+      if constexpr (kScalar) scalar_tile(st, my_q, my_q + kMaxG * kD, stage, min(remaining, kTile), G, lane);
+      else mma_tile(st, stage, remaining, lane);
+      __syncwarp();
+      remaining -= kTile;
+      stage_c = (stage_c + 1) & (kStages - 1);
+      stage_p = (stage_p + 1) & (kStages - 1);
     }
-    cp_async_commit();
-    cp_async_wait<kStages - 1>();
-    __syncwarp();
-
-    if (fresh) {
-      if constexpr (kScalar) scalar_begin(st, my_q, q, q_sb, q_sh, cur.b, cur.h, G, scale_log2, lane);
-      else mma_begin(st, q, q_sb, q_sh, cur.b, cur.h, G, scale_log2, lane);
-      fresh = false;
-    }
-    const uint8_t* stage = my_ring + (i % kStages) * kTileBytes;
-    const int nvalid = min(kTile, cur.n - cur.tile * kTile);
-    if constexpr (kScalar) scalar_tile(st, my_q, my_q + kMaxG * kD, stage, nvalid, G, lane);
-    else mma_tile(st, stage, nvalid, lane);
-    __syncwarp();
-
-    const bool seg_last = (cur.tile + 1 == cur.T) || (i + 1 == ntiles);
-    if (seg_last) {
-      // tiles of this (entry, head) seen by this warp end at cur.tile; they began at tile
-      // max(0, cur.tile - i_since_seg_start).  The segment is whole iff it began at tile 0 and
-      // ends at T-1; it began at tile 0 unless it is the first segment and the range started inside it.
-      const int seg_first_unit = cur.base + cur.h * cur.T;   // flat index of tile 0
-      const bool began_at_zero = seg_first_unit >= u0;
-      const bool whole = began_at_zero && (cur.tile + 1 == cur.T);
-      const int slot = first_seg ? 0 : 1;
-      float* po = ws_o + ((size_t)w * 2 + slot) * G * kD;
-      float* pml = ws_ml + ((size_t)w * 2 + slot) * G * 2;
-      if constexpr (kScalar) scalar_end(st, whole, out, o_sb, o_sh, cur.b, cur.h, G, po, pml, lane);
-      else mma_end(st, whole, out, o_sb, o_sh, cur.b, cur.h, G, po, pml, lane);
-      fresh = true;
-      first_seg = false;
-    }
-    if (i + 1 < ntiles) cur.next(cached_lens, nd, c.Hkv, c.page_size);
+    // whole iff the segment began at the sequence's first tile and reached its last one
+    const bool whole = cc.tile == 0 && seg == cc.T;
+    const int slot = done == 0 ? 0 : 1;
+    float* po = ws_o + ((size_t)w * 2 + slot) * G * kD;
+    float* pml = ws_ml + ((size_t)w * 2 + slot) * G * 2;
+    if constexpr (kScalar) scalar_end(st, whole, out, o_sb, o_sh, cc.b, cc.h, G, po, pml, lane);
+    else mma_end(st, whole, out, o_sb, o_sh, cc.b, cc.h, G, po, pml, lane);
+    done += seg;
+    if (done < ntiles) cc.next_segment(cached_lens, nd, c.Hkv);
   }
   cp_async_wait<0>();
 }
