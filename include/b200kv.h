@@ -147,15 +147,22 @@ int b200kv_prefill_attn(const void* q, int64_t q_stride_n, int64_t q_stride_h,
                         int32_t N, int32_t Hq, int32_t Hkv, int32_t D, void* stream);
 
 /* Bytes of fp32 workspace b200kv_decode_attn needs for a batch of B entries on a device with
- * `sm_count` SMs (replaces the three partial buffers of kernels.py:305-311). */
+ * `sm_count` SMs (replaces the three partial buffers of kernels.py:305-311).
+ * Contract: the workspace must be ZERO-filled once when it is allocated.  It holds, besides the
+ * split partials, one arrival counter per (entry, kv head); the kernel returns every counter to
+ * zero, so the same workspace can serve any number of stream-ordered calls WITH THE SAME B AND
+ * HEAD COUNTS (the counters' place depends on them; zero-fill again before changing shape).  Two
+ * calls that overlap on the GPU must not share a workspace. */
 size_t b200kv_decode_attn_workspace_bytes(int32_t B, int32_t Hq, int32_t Hkv, int32_t D, int32_t sm_count);
 
 /* Replaces decode_attention (kernels.py:272-361): split-K GQA decode attention over the int8
  * cache with in-kernel dequantization, one new token per entry, followed by the cross-split
  * log-sum-exp reduction.  Entry b < *num_decoding attends tokens [0, cached_lens[b]] and its
  * result is written to out[b] (bf16 [>=B,Hq,D]); other rows of `out` are not touched.
- * q bf16 [B,Hq,D] is the q_out of b200kv_write_decode.  `variant`: 0 = tensor-core kernel
- * (the product path), 1 = scalar CUDA-core kernel kept for cross-checking. */
+ * q bf16 [B,Hq,D] is the q_out of b200kv_write_decode.  `variant` bit 0: 0 = tensor-core kernel
+ * (the product path), 1 = scalar CUDA-core kernel kept for cross-checking; bit 1: 0 = the
+ * cross-split reduction is fused into the attention kernel (the warp delivering the last piece of
+ * an (entry, head) merges them), 1 = it runs as a second kernel like the reference's. */
 int b200kv_decode_attn(const void* q, int64_t q_stride_b, int64_t q_stride_h,
                        const b200kv_cache* cache, const b200kv_table* table,
                        const int32_t* cached_lens, const int32_t* num_decoding, float scale,

@@ -159,7 +159,7 @@ __host__ __device__ __forceinline__ Partition make_partition(int total_tiles_one
 // entry's page table (table column and first row inside that page); they advance incrementally
 // so the hot loop never divides.
 struct Cursor {
-  int b, h, tile, T, n, slot, row0;
+  int b, h, tile, T, n, slot, row0, base;  // base: flat index of (entry b, head 0, tile 0)
   __device__ __forceinline__ void seek(const int* chunk_prefix, int nchunks, int chunk, const int32_t* cached_lens,
                                        int nd, int Hkv, int page_size, int u) {
     int lo = 0, hi = nchunks;  // largest chunk whose first flat index is <= u
@@ -176,7 +176,8 @@ struct Cursor {
       ++b;
     }
     n = cached_lens[b] + 1;
-    int r = u - Hkv * run;
+    base = Hkv * run;
+    int r = u - base;
     h = r / T;
     tile = r - h * T;
     slot = (tile * kTile) / page_size;
@@ -187,6 +188,7 @@ struct Cursor {
     tile = 0; slot = 0; row0 = 0;
     if (++h < Hkv) return;
     h = 0;
+    base += Hkv * T;
     do { ++b; T = tiles_of(cached_lens, b, nd); } while (T == 0);
     n = cached_lens[b] + 1;
   }
@@ -575,8 +577,46 @@ __device__ __forceinline__ void scalar_end(ScalarState& st, bool whole, uint16_t
 }
 
 // ------------------------------------------------------------------ main kernel
-// Workspace: int32 prefix[B+1] (padded to 256 B) | float ml[W][2][G][2] | float acc[W][2][G][128]
+// Workspace: int32 prefix[B+1] (padded to 256 B; read by the separate reduction kernel) |
+// int32 arrivals[B*Hkv] (padded; zero on entry, left zero: counts the partials of each (entry, head)
+// when the reduction is fused into this kernel) | float ml[W][2][G][2] | float acc[W][2][G][128]
 __host__ __device__ inline size_t ws_prefix_bytes(int B) { return (((size_t)(B + 1) * 4 + 255) / 256) * 256; }
+__host__ __device__ inline size_t ws_count_bytes(int B, int Hkv) { return (((size_t)B * Hkv * 4 + 255) / 256) * 256; }
+__host__ __device__ inline size_t ws_head_bytes(int B, int Hkv) { return ws_prefix_bytes(B) + ws_count_bytes(B, Hkv); }
+
+// Merge the partials of one (entry, head) - the pieces written by workers w_first..w_last - and
+// write the final bf16 rows.  One warp; lane l owns channels 4l..4l+3.  Loads bypass L1 (the
+// partials were written by other SMs).
+__device__ __forceinline__ void merge_partials(const float* __restrict__ ws_ml, const float* __restrict__ ws_o,
+                                               int w_first, int w_last, int slot_first, int G,
+                                               uint16_t* __restrict__ out_row, long long o_sh, int lane) {
+  for (int col = 0; col < G; ++col) {
+    float M = -INFINITY;
+    for (int w = w_first + lane; w <= w_last; w += 32) {
+      const size_t base = ((size_t)w * 2 + (w == w_first ? slot_first : 0)) * G + col;
+      M = fmaxf(M, __ldcg(ws_ml + base * 2));
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+    float L = 0.f;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+    for (int w = w_first; w <= w_last; ++w) {
+      const size_t base = ((size_t)w * 2 + (w == w_first ? slot_first : 0)) * G + col;
+      const float2 ml = __ldcg(reinterpret_cast<const float2*>(ws_ml + base * 2));
+      const float4 o = __ldcg(reinterpret_cast<const float4*>(ws_o + base * kD + 4 * lane));
+      const float wg = fast_exp2(ml.x - M);
+      L = fmaf(ml.y, wg, L);
+      acc.x = fmaf(o.x, wg, acc.x); acc.y = fmaf(o.y, wg, acc.y);
+      acc.z = fmaf(o.z, wg, acc.z); acc.w = fmaf(o.w, wg, acc.w);
+    }
+    const float inv = 1.f / L;
+    uint2 r;
+    r.x = float_to_bf16_bits(acc.x * inv) | (float_to_bf16_bits(acc.y * inv) << 16);
+    r.y = float_to_bf16_bits(acc.z * inv) | (float_to_bf16_bits(acc.w * inv) << 16);
+    *reinterpret_cast<uint2*>(out_row + col * o_sh + 4 * lane) = r;
+  }
+}
 __host__ __device__ inline size_t ws_ml_bytes(int W, int G) { return (((size_t)W * 2 * G * 2 * 4 + 255) / 256) * 256; }
 
 template <bool kScalar>
@@ -584,7 +624,7 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm)
 decode_attn_kernel(const uint16_t* __restrict__ q, long long q_sb, long long q_sh, CacheView c,
                    const int32_t* __restrict__ cached_lens, const int32_t* __restrict__ num_decoding, float scale_log2,
                    uint16_t* __restrict__ out, long long o_sb, long long o_sh, uint8_t* __restrict__ workspace, int B,
-                   int G, int min_tiles, int32_t* status) {
+                   int G, int min_tiles, int fused, int32_t* status) {
   extern __shared__ __align__(128) uint8_t smem[];
   uint8_t* ring = smem;                                                       // kWarps * kStages * kTileBytes
   float* q_s = reinterpret_cast<float*>(ring + kWarps * kStages * kTileBytes);  // scalar variant: kWarps * (G*128 + G*16)
@@ -603,8 +643,9 @@ decode_attn_kernel(const uint16_t* __restrict__ q, long long q_sb, long long q_s
   const int u0 = (int)u_begin;
   const int ntiles = min(part.per, part.U - u0);
 
-  float* ws_ml = reinterpret_cast<float*>(workspace + ws_prefix_bytes(B));
-  float* ws_o = reinterpret_cast<float*>(workspace + ws_prefix_bytes(B) + ws_ml_bytes(W, G));
+  int* ws_count = reinterpret_cast<int*>(workspace + ws_prefix_bytes(B));
+  float* ws_ml = reinterpret_cast<float*>(workspace + ws_head_bytes(B, c.Hkv));
+  float* ws_o = reinterpret_cast<float*>(workspace + ws_head_bytes(B, c.Hkv) + ws_ml_bytes(W, G));
   uint8_t* my_ring = ring + warp * kStages * kTileBytes;
   const uint32_t my_ring_s = smem_u32(my_ring);
   float* my_q = q_s + warp * (kMaxG * kD + kMaxG * kTile);
@@ -658,6 +699,23 @@ decode_attn_kernel(const uint16_t* __restrict__ q, long long q_sb, long long q_s
     float* pml = ws_ml + ((size_t)w * 2 + slot) * G * 2;
     if constexpr (kScalar) scalar_end(st, whole, out, o_sb, o_sh, cc.b, cc.h, G, po, pml, lane);
     else mma_end(st, whole, out, o_sb, o_sh, cc.b, cc.h, G, po, pml, lane);
+    if (fused && !whole) {
+      // Fused cross-split reduction: the warp that delivers the last piece of (entry, head) merges
+      // all of them.  Release: partial stores -> fence -> counter; acquire: counter -> fence -> loads.
+      const int s0 = cc.base + cc.h * cc.T;  // flat index of this (entry, head)'s first tile
+      const int w_first = s0 / part.per, w_last = (s0 + cc.T - 1) / part.per;
+      __threadfence();
+      __syncwarp();
+      int arrived = 0;
+      if (lane == 0) arrived = atomicAdd(ws_count + cc.b * c.Hkv + cc.h, 1) + 1;
+      arrived = __shfl_sync(0xffffffffu, arrived, 0);
+      if (arrived == w_last - w_first + 1) {
+        __threadfence();
+        merge_partials(ws_ml, ws_o, w_first, w_last, s0 > w_first * part.per ? 1 : 0, G,
+                       out + cc.b * o_sb + (long long)(cc.h * G) * o_sh, o_sh, lane);
+        if (lane == 0) ws_count[cc.b * c.Hkv + cc.h] = 0;  // leave the counter zero for the next call
+      }
+    }
     done += seg;
     if (done < ntiles) cc.next_segment(cached_lens, nd, c.Hkv);
   }
@@ -665,13 +723,21 @@ decode_attn_kernel(const uint16_t* __restrict__ q, long long q_sb, long long q_s
 }
 
 // ------------------------------------------------------------------ cross-split reduction
-// grid (B, Hkv), 128 threads (one per channel).  kernels.py:216-264, with exp2 because the
-// running maxima are kept in the log2 domain.
+// grid (B, Hkv), 128 threads.  kernels.py:216-264, with exp2 because the running maxima are kept
+// in the log2 domain.  Worker w's piece of (b, h) is in its slot 1 only when it is not the first
+// segment of w's range.  Partials are merged up to 128 at a time: thread i fetches (m, l) of
+// partial i (one parallel round of loads), the block agrees on the maximum, then the four warps
+// each sum every fourth partial with 16-byte loads (lane l owns channels 4l..4l+3) and the four
+// sums are added through shared memory - so even a sequence cut into 64 pieces costs a few rounds
+// of memory latency, not 64.
 __global__ void __launch_bounds__(kD)
 decode_combine_kernel(const uint8_t* __restrict__ workspace, const int32_t* __restrict__ num_decoding,
                       uint16_t* __restrict__ out, long long o_sb, long long o_sh, int B, int Hkv, int G, int W,
                       int min_tiles) {
-  const int b = blockIdx.x, h = blockIdx.y, d = threadIdx.x;
+  __shared__ float wgt_s[kD];
+  __shared__ float red_s[4];
+  __shared__ __align__(16) float acc_s[4][kD];
+  const int b = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
   if (b >= min(*num_decoding, B)) return;
   const int* prefix = reinterpret_cast<const int*>(workspace);
   const int T = prefix[b + 1] - prefix[b];
@@ -680,23 +746,57 @@ decode_combine_kernel(const uint8_t* __restrict__ workspace, const int32_t* __re
   const int s = Hkv * prefix[b] + h * T, e = s + T;
   const int w_first = s / part.per, w_last = (e - 1) / part.per;
   if (w_first == w_last) return;  // one warp saw the whole sequence and wrote the output itself
-  const float* ws_ml = reinterpret_cast<const float*>(workspace + ws_prefix_bytes(B));
-  const float* ws_o = reinterpret_cast<const float*>(workspace + ws_prefix_bytes(B) + ws_ml_bytes(W, G));
+  const float* ws_ml = reinterpret_cast<const float*>(workspace + ws_head_bytes(B, Hkv));
+  const float* ws_o = reinterpret_cast<const float*>(workspace + ws_head_bytes(B, Hkv) + ws_ml_bytes(W, G));
+  const int slot_first = s > w_first * part.per ? 1 : 0;
+  const int warp = tid >> 5, lane = tid & 31;
+
   for (int col = 0; col < G; ++col) {
-    float M = -INFINITY;
-    for (int w = w_first; w <= w_last; ++w) {
-      const int slot = (w == w_first && s > w * part.per) ? 1 : 0;
-      M = fmaxf(M, ws_ml[(((size_t)w * 2 + slot) * G + col) * 2]);
+    float M = -INFINITY, L = 0.f;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int w0 = w_first; w0 <= w_last; w0 += kD) {
+      const int nb = min(kD, w_last - w0 + 1);
+      float m_i = -INFINITY, l_i = 0.f;
+      if (tid < nb) {
+        const int w = w0 + tid;
+        const size_t base = ((size_t)w * 2 + (w == w_first ? slot_first : 0)) * G + col;
+        m_i = ws_ml[base * 2];
+        l_i = ws_ml[base * 2 + 1];
+      }
+      float mx = m_i;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+      if (lane == 0) red_s[warp] = mx;
+      __syncthreads();
+      const float M_new = fmaxf(M, fmaxf(fmaxf(red_s[0], red_s[1]), fmaxf(red_s[2], red_s[3])));
+      __syncthreads();
+      const float w_i = tid < nb ? fast_exp2(m_i - M_new) : 0.f;
+      wgt_s[tid] = w_i;
+      float ls = l_i * w_i;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) ls += __shfl_xor_sync(0xffffffffu, ls, o);
+      if (lane == 0) red_s[warp] = ls;
+      __syncthreads();
+      const float rescale = fast_exp2(M - M_new);  // 0 on the first batch (M = -inf)
+      L = L * rescale + ((red_s[0] + red_s[1]) + (red_s[2] + red_s[3]));
+      acc.x *= rescale; acc.y *= rescale; acc.z *= rescale; acc.w *= rescale;
+#pragma unroll 4
+      for (int i = warp; i < nb; i += 4) {
+        const int w = w0 + i;
+        const size_t base = ((size_t)w * 2 + (w == w_first ? slot_first : 0)) * G + col;
+        const float4 o = *reinterpret_cast<const float4*>(ws_o + base * kD + 4 * lane);
+        const float wg = wgt_s[i];
+        acc.x = fmaf(o.x, wg, acc.x); acc.y = fmaf(o.y, wg, acc.y);
+        acc.z = fmaf(o.z, wg, acc.z); acc.w = fmaf(o.w, wg, acc.w);
+      }
+      M = M_new;
+      __syncthreads();  // before wgt_s / red_s are rewritten
     }
-    float acc = 0.f, L = 0.f;
-    for (int w = w_first; w <= w_last; ++w) {
-      const int slot = (w == w_first && s > w * part.per) ? 1 : 0;
-      const size_t base = ((size_t)w * 2 + slot) * G + col;
-      const float wgt = fast_exp2(ws_ml[base * 2] - M);
-      L = fmaf(ws_ml[base * 2 + 1], wgt, L);
-      acc = fmaf(ws_o[base * kD + d], wgt, acc);
-    }
-    out[b * o_sb + (long long)(h * G + col) * o_sh + d] = (uint16_t)float_to_bf16_bits(acc / L);
+    *reinterpret_cast<float4*>(&acc_s[warp][4 * lane]) = acc;
+    __syncthreads();
+    const float v = (acc_s[0][tid] + acc_s[1][tid]) + (acc_s[2][tid] + acc_s[3][tid]);
+    out[b * o_sb + (long long)(h * G + col) * o_sh + tid] = (uint16_t)float_to_bf16_bits(v / L);
+    __syncthreads();  // before acc_s is rewritten for the next column
   }
 }
 
@@ -716,7 +816,7 @@ extern "C" size_t b200kv_decode_attn_workspace_bytes(int32_t B, int32_t Hq, int3
   if (B < 0 || Hq < 1 || Hkv < 1 || Hq % Hkv || D != kD || sm_count < 1) return 0;
   const int G = Hq / Hkv;
   const int W = sm_count * kCtasPerSm * kWarps;
-  return ws_prefix_bytes(B) + ws_ml_bytes(W, G) + (size_t)W * 2 * G * kD * 4;
+  return ws_head_bytes(B, Hkv) + ws_ml_bytes(W, G) + (size_t)W * 2 * G * kD * 4;
 }
 
 extern "C" int b200kv_decode_attn(const void* q, int64_t q_sb, int64_t q_sh, const b200kv_cache* cache,
@@ -728,7 +828,7 @@ extern "C" int b200kv_decode_attn(const void* q, int64_t q_sb, int64_t q_sh, con
   int rc = check_cache(cache, table);
   if (rc) return rc;
   const int Hkv = cache->num_kv_heads;
-  if (B < 0 || Hq < 1 || Hq % Hkv || Hq / Hkv > kMaxG || sm_count < 1 || (variant != 0 && variant != 1)) return B200KV_E_SHAPE;
+  if (B < 0 || Hq < 1 || Hq % Hkv || Hq / Hkv > kMaxG || sm_count < 1 || variant < 0 || variant > 3) return B200KV_E_SHAPE;
   if (B > kMaxB) return B200KV_E_RANGE;
   if (!aligned(q, 16) || !aligned(out, 16) || !aligned(workspace, 256) || (q_sb % 8) || (q_sh % 8) || (o_sb % 8) || (o_sh % 8))
     return B200KV_E_ALIGN;
@@ -740,25 +840,27 @@ extern "C" int b200kv_decode_attn(const void* q, int64_t q_sb, int64_t q_sh, con
   const int min_tiles = 4;  // at least 64 tokens per partial, like the reference's MIN_PIECE (kernels.py:295)
   const float scale_log2 = scale * 1.4426950408889634f;
   cudaStream_t s = (cudaStream_t)stream;
-  const bool scalar = variant == 1;
+  const bool scalar = (variant & 1) != 0;
+  const int fused = (variant & 2) ? 0 : 1;
   const size_t smem = main_smem_bytes(B, scalar);
   static bool attr_set[2] = {false, false};  // the opt-in to > 48 KB of dynamic shared memory is per function
-  if (!attr_set[variant]) {
+  if (!attr_set[variant & 1]) {
     cudaError_t e = scalar ? cudaFuncSetAttribute(decode_attn_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
                            : cudaFuncSetAttribute(decode_attn_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return B200KV_E_LAUNCH;
-    attr_set[variant] = true;
+    attr_set[variant & 1] = true;
   }
   CacheView view = make_view(cache, table);
   if (scalar)
     decode_attn_kernel<true><<<grid, kWarps * 32, smem, s>>>((const uint16_t*)q, q_sb, q_sh, view, cached_lens, num_decoding,
                                                             scale_log2, (uint16_t*)out, o_sb, o_sh, (uint8_t*)workspace, B,
-                                                            G, min_tiles, status);
+                                                            G, min_tiles, fused, status);
   else
     decode_attn_kernel<false><<<grid, kWarps * 32, smem, s>>>((const uint16_t*)q, q_sb, q_sh, view, cached_lens,
                                                              num_decoding, scale_log2, (uint16_t*)out, o_sb, o_sh,
-                                                             (uint8_t*)workspace, B, G, min_tiles, status);
+                                                             (uint8_t*)workspace, B, G, min_tiles, fused, status);
   if (cudaGetLastError() != cudaSuccess) return B200KV_E_LAUNCH;
+  if (fused) return B200KV_OK;
   decode_combine_kernel<<<dim3(B, Hkv), kD, 0, s>>>((const uint8_t*)workspace, num_decoding, (uint16_t*)out, o_sb, o_sh, B,
                                                     Hkv, G, W, min_tiles);
   return cudaGetLastError() == cudaSuccess ? B200KV_OK : B200KV_E_LAUNCH;

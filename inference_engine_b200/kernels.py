@@ -74,6 +74,28 @@ def check_status(device=None) -> int:
     return val
 
 
+_workspaces: dict[tuple, torch.Tensor] = {}
+
+
+def decode_workspace(device: torch.device, B: int, Hq: int, Hkv: int, nbytes: int) -> torch.Tensor:
+    """Workspace of decode_attention (split partials + arrival counters) for one (device, batch
+    size, head counts), allocated zeroed on first use and reused by every later call of that shape:
+    the C ABI wants the counters zero on entry and leaves them zero, and their place in the buffer
+    depends on B.  Calls on one device must be stream-ordered (the reference engine is
+    single-stream); a new shape allocates, so run each shape once before graph capture (the
+    engine's capture_graph warm-up does)."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    key = (idx, B, Hq, Hkv)
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        if torch.cuda.is_current_stream_capturing():
+            raise RuntimeError("decode_attention workspace must exist before CUDA-graph capture: "
+                               "run the same call once eagerly first")
+        ws = torch.zeros(nbytes, device=torch.device("cuda", idx), dtype=torch.uint8)
+        _workspaces[key] = ws
+    return ws
+
+
 def _require_cuda(*tensors: torch.Tensor) -> None:
     for t in tensors:
         if not t.is_cuda:
@@ -139,11 +161,11 @@ def decode_attention(
     nbytes = lib.b200kv_decode_attn_workspace_bytes(B, Hq, Hkv, D, sms)
     if nbytes == 0:
         raise ValueError("decode_attention: unsupported geometry")
-    workspace = torch.empty(nbytes, device=q.device, dtype=torch.uint8)
+    workspace = decode_workspace(q.device, B, Hq, Hkv, nbytes)
     cs, ts = _cache_struct(kv_cache), _table_struct(slot_ids)
     rc = lib.b200kv_decode_attn(
         q.data_ptr(), q.stride(0), q.stride(1), ctypes.byref(cs), ctypes.byref(ts), _i32(cached_lens),
-        _i32(num_decoding), float(scale), out.data_ptr(), out.stride(0), out.stride(1), workspace.data_ptr(), nbytes,
+        _i32(num_decoding), float(scale), out.data_ptr(), out.stride(0), out.stride(1), workspace.data_ptr(), workspace.numel(),
         B, Hq, sms, variant, status_word(q.device).data_ptr(), _stream())
     _lib.check(rc, "decode_attention")
     return out

@@ -66,7 +66,7 @@ def test_reference_golden(K, golden, variant):
     check(H.to_f32(out)[:nd], O.decode_attention(O.from_bf16_bits(g["da_q_bf16"]), cache, g["da_cached"], g["da_slots"], nd, SCALE)[:nd])
 
 
-@pytest.mark.parametrize("variant", [0, 1])
+@pytest.mark.parametrize("variant", [0, 1, 2])
 @pytest.mark.parametrize("paged", [True, False])
 def test_boundaries(K, variant, paged):
     """Context lengths on every tile, page and split boundary, in both cache layouts."""
@@ -87,12 +87,13 @@ def test_cfg1_quantized_gaussian(K, variant):
     assert err.max() <= 2e-3 and err.mean() <= 2e-4, (err.max(), err.mean())
 
 
+@pytest.mark.parametrize("variant", [0, 2])
 @pytest.mark.parametrize("B,n", [(1, 4096), (3, 2048), (64, 512), (256, 128), (37, 700)])
-def test_split_shapes(K, B, n):
+def test_split_shapes(K, B, n, variant):
     """Shapes where sequences are split over many warps (B small) and where one warp owns many
     sequences (B large)."""
     rng = np.random.default_rng(B * 100003 + n)
-    got, want = run_case(K, rng, [n] * B, 16, True, 0, gauss=True)
+    got, want = run_case(K, rng, [n] * B, 16, True, variant, gauss=True)
     err = np.abs(got - want)
     # outputs are below 1 in magnitude: 4e-3 is one bf16 ulp there (a rounding flip), the mean is the real gate
     assert err.max() <= 4e-3 and err.mean() <= 1e-4, (err.max(), err.mean())
@@ -165,3 +166,23 @@ def test_argument_validation(K):
         K.decode_attention(q, cache, H.i32([30, 30]), table, H.i32([2]), SCALE)
     with pytest.raises(RuntimeError):
         K.decode_attention(q.cpu(), cache, H.i32([30, 30]), table, H.i32([2]), SCALE)
+
+
+def test_repeated_calls_leave_the_workspace_reusable(K):
+    """The arrival counters must be back at zero after every call: the same inputs give the same
+    bits on three consecutive calls, and a different batch in between does not disturb them."""
+    rng = np.random.default_rng(5)
+    lens = [3000, 70, 1500, 16]
+    table = H.random_block_table(rng, lens, 16, 300)
+    cache = H.cache_to_torch(H.random_filled_cache(rng, 300, 16, gauss=True))
+    q = H.bf16_tensor(H.randn_bf16(rng, 4, HQ, D))
+    cached, tab, nd = H.i32([n - 1 for n in lens]), H.i32(table), H.i32([4])
+    first = K.decode_attention(q, cache, cached, tab, nd, SCALE).clone()
+    K.decode_attention(q[:2], cache, cached[:2], tab[:2], H.i32([2]), SCALE)
+    for _ in range(2):
+        again = K.decode_attention(q, cache, cached, tab, nd, SCALE)
+        assert torch.equal(first, again)
+    ws = K.decode_workspace(q.device, 4, HQ, HKV, 1)
+    counters = ws[: 4096].view(torch.int32)
+    torch.cuda.synchronize()
+    assert int(counters[64:128].abs().sum()) == 0  # the arrival counters follow the 256-byte prefix area
