@@ -33,6 +33,11 @@ CACHE_BYTES_PER_TOKEN = HKV * (2 * D + 8)  # int8 K+V codes and fp32 K+V scales 
 WRITE_BYTES_PER_TOKEN = 14656  # q,k,v,cos,sin read (8448) + q', codes, scales written (6208)
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum of one B=64, ctx=4096 launch (ncu capture summarised in
+# profiles/decode_attn_B64_ctx4096.md); reported as roofline.traffic when the workload is that cell
+NCU_TRAFFIC_BYTES = 576049152
+
+
 def attn_bytes(B: int, n: int) -> int:
     """Algorithmic bytes of one decode_attention call: cache stream + q read + out write."""
     return B * n * CACHE_BYTES_PER_TOKEN + 2 * (B * HQ * D * 2)
@@ -94,13 +99,15 @@ class ClockSampler:
 
 # ----------------------------------------------------------------------------- CPU arm
 class CpuSample:
-    """The CPU port of decode attention (the oracle) on `seqs` of the workload's sequences of one
-    layer; `run()` returns seconds for one pass."""
+    """The CPU port of the reference math (C/OpenMP restatement in oracle/, all host threads) on one
+    layer's worth of the workload: decode attention over `seqs` sequences x ctx tokens, repeated
+    `passes` times (a step of `passes` layers).  `run()` returns seconds for all passes."""
 
-    def __init__(self, B: int, n: int, seqs: int, seed: int = 2):
+    def __init__(self, B: int, n: int, seqs: int, passes: int, seed: int = 2):
+        from oracle import c_oracle as C
         from oracle import oracle as O
 
-        self.O, self.n, self.seqs = O, n, seqs
+        self.C, self.n, self.seqs, self.passes = C, n, seqs, passes
         rng = np.random.default_rng(seed)
         pages_per_seq = (n + PAGE - 1) // PAGE
         num_pages = seqs * pages_per_seq
@@ -112,25 +119,18 @@ class CpuSample:
         self.table = rng.permutation(num_pages).astype(np.int32).reshape(seqs, pages_per_seq)
         self.q = O.bf16_round(rng.standard_normal((seqs, HQ, D)).astype(np.float32))
         self.cached = np.full(seqs, n - 1, np.int32)
-        self.bytes = attn_bytes(seqs, n)
-        self.sample = (f"decode attention, {seqs} of {B} sequences x ctx {n}, 1 layer "
-                       f"(numpy port of the reference math; the reference itself is Triton-only)")
+        self.out = np.zeros((seqs, HQ, D), np.float32)
+        self.threads = C.threads()
+        self.bytes = passes * attn_bytes(seqs, n)
+        self.sample = (f"decode attention, {seqs} of {B} sequences x ctx {n}, {passes} layer passes per step "
+                       f"(C/OpenMP port of the reference math, {self.threads} threads; the reference itself is "
+                       f"Triton-only and has no CPU path)")
 
-    def run(self, threads: int) -> float:
-        try:
-            from threadpoolctl import threadpool_limits
-        except ImportError:  # pragma: no cover
-            threadpool_limits = None
-        ctx = threadpool_limits(limits=threads) if threadpool_limits is not None else None
-        if ctx is not None:
-            ctx.__enter__()
-        try:
-            t0 = time.perf_counter()
-            self.O.decode_attention(self.q, self.cache, self.cached, self.table, self.seqs, D ** -0.5)
-            return time.perf_counter() - t0
-        finally:
-            if ctx is not None:
-                ctx.__exit__(None, None, None)
+    def run(self) -> float:
+        t0 = time.perf_counter()
+        for _ in range(self.passes):
+            self.C.decode_attention(self.q, self.cache, self.cached, self.table, self.seqs, D ** -0.5, out=self.out)
+        return time.perf_counter() - t0
 
 
 def run_reference(args):
@@ -139,9 +139,8 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    threads = os.cpu_count() or 1
-    cs = CpuSample(args.batch, args.ctx, max(1, min(args.batch, args.cpu_seqs)))
-    secs = [cs.run(threads) for _ in range(args.warmup + args.steps)][args.warmup:]
+    cs = CpuSample(args.batch, args.ctx, max(1, min(args.batch, args.cpu_seqs)), args.layers)
+    secs = [cs.run() for _ in range(args.warmup + args.steps)][args.warmup:]
     dt = float(np.mean(secs))
     v = cs.bytes / dt / 1e9
     print(json.dumps({
@@ -149,7 +148,7 @@ def run_reference(args):
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(1e3 * dt, 3),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp32", "data": "synthetic",
         "config": workload_config(args, l2="n/a (CPU)"),
-        "cpu_baseline": {"value": round(v, 4), "unit": "GB/s", "cores": threads, "kind": "port", "sample": cs.sample},
+        "cpu_baseline": {"value": round(v, 4), "unit": "GB/s", "cores": cs.threads, "kind": "port", "sample": cs.sample},
         "e2e": {"value": round(v, 4), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "tokens_per_s": round(cs.seqs / dt, 3),
     }))
@@ -266,10 +265,10 @@ def run_b200(args):
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
-        threads = os.cpu_count() or 1
-        cs = CpuSample(B, n, max(1, min(B, args.cpu_seqs)))
-        dt = cs.run(threads)
-        cpu = {"value": round(cs.bytes / dt / 1e9, 4), "unit": "GB/s", "cores": threads, "kind": "port",
+        cs = CpuSample(B, n, max(1, min(B, args.cpu_seqs)), L)
+        cs.run()
+        dt = min(cs.run() for _ in range(3))
+        cpu = {"value": round(cs.bytes / dt / 1e9, 4), "unit": "GB/s", "cores": cs.threads, "kind": "port",
                "sample": cs.sample, "seconds": round(dt, 2)}
     if rank == 0:
         print(json.dumps({
@@ -279,13 +278,14 @@ def run_b200(args):
             "data": "synthetic", "config": workload_config(args, l2=f"step streams {step_bytes / 1e9:.1f} GB per GPU, far above the 126 MB L2"),
             "pct_of_8TBs": round(100 * value / world / 8000.0, 2),
             "tokens_per_s": round(world * B * args.steps / (ms_dev * 1e-3), 1),
-            "roofline": {"bound": "hbm", "kernel": "decode_attn_kernel<mma> + decode_combine_kernel (one decode_attention call)",
+            "roofline": {"bound": "hbm", "kernel": "decode_attn_kernel (tensor-core variant, cross-split reduction fused in): one per decode_attention call",
                          "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 4),
                          "peak_kind": peak_kind, "us_per_call": round(per_call_s * 1e6, 2),
-                         "algorithmic_bytes_per_call": attn_bytes(B, n), "traffic": args.traffic},
+                         "algorithmic_bytes_per_call": attn_bytes(B, n),
+                         "traffic": args.traffic if (B, n) == (64, 4096) else None},
             "e2e": {"value": round(e2e, 1), "unit": "GB/s", "ms_per_step": round(ms_e2e / args.steps, 4),
                     "h2d_bytes_per_step": step.h2d_bytes, "d2h_bytes_per_step": step.d2h_bytes},
-            "gpu_launches": args.steps * L * 3,
+            "gpu_launches": args.steps * L * 2,
             "cpu_baseline": cpu, "clocks": clocks.summary(),
         }))
     if world > 1:
@@ -301,9 +301,9 @@ def main():
     ap.add_argument("--batch", type=int, default=64, help="sequences per GPU")
     ap.add_argument("--ctx", type=int, default=4096, help="tokens attended per sequence, the new one included")
     ap.add_argument("--layers", type=int, default=28)
-    ap.add_argument("--cpu-seqs", type=int, default=16, help="sequences in the CPU baseline sample")
+    ap.add_argument("--cpu-seqs", type=int, default=64, help="sequences in the CPU baseline sample")
     ap.add_argument("--no-cpu", action="store_true")
-    ap.add_argument("--traffic", type=float, default=None, help="ncu DRAM bytes per decode_attention call, if known")
+    ap.add_argument("--traffic", type=float, default=NCU_TRAFFIC_BYTES, help="ncu DRAM bytes per decode_attention call, if known")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
