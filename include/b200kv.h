@@ -46,7 +46,8 @@ enum {
   B200KV_E_ALIGN = -3,     /* pointer or stride not aligned as the kernels need */
   B200KV_E_WORKSPACE = -4, /* caller-provided workspace too small */
   B200KV_E_LAUNCH = -5,    /* the CUDA runtime rejected a launch (see cudaGetLastError) */
-  B200KV_E_RANGE = -6      /* a size argument is out of the supported range */
+  B200KV_E_RANGE = -6,     /* a size argument is out of the supported range */
+  B200KV_E_STATIC_LIMIT = -7 /* b200kv_decode_attn_static: the call needs more scratch than the built-in array holds */
 };
 
 /* Bits OR-ed into the optional device status word. */
@@ -170,6 +171,35 @@ int b200kv_decode_attn(const void* q, int64_t q_stride_b, int64_t q_stride_h,
                        void* workspace, size_t workspace_bytes,
                        int32_t B, int32_t Hq, int32_t sm_count, int32_t variant,
                        int32_t* status, void* stream);
+
+/* b200kv_decode_attn for callers that must not allocate.  It has no counterpart in the reference
+ * (whose wrapper allocates three partial buffers per call, kernels.py:305-311).
+ *
+ * Same computation and same result as b200kv_decode_attn with variant 0, but the caller passes
+ * no workspace: the scratch (arrival counters and fp32 split partials) is a fixed 8 MiB array
+ * inside the library's device image, so this call reaches neither cudaMalloc/cudaFree nor any
+ * allocating library routine.  Meant for hosts that cannot allocate where they call attention:
+ * a server whose own pool already owns all device memory, code running inside another
+ * component's stream capture, or a loop that cannot afford the device-wide synchronisation an
+ * allocation implies.
+ *
+ * Limit: the call is rejected with B200KV_E_STATIC_LIMIT (nothing launched) when
+ * b200kv_decode_attn_workspace_bytes(B, Hq, Hkv, D, sm_count) exceeds
+ * b200kv_decode_attn_static_limit() = 8 MiB.  On a 148-SM device with 8 KV heads that admits
+ * Hq/Hkv = 2 up to B of about 130,000 entries and Hq/Hkv = 4 up to about 25,000; Hq/Hkv = 8 does
+ * not fit.  Every GPU that loads the library keeps the 8 MiB until the process ends.
+ *
+ * The first call on each device looks up the array's device address (one cudaGetSymbolAddress,
+ * with that device current); make that first call before any stream capture begins.
+ * All calls on a device share the one array: each call clears the counters it needs on `stream`
+ * before its kernel, and calls that overlap on the GPU (different streams, no dependency between
+ * them) race on it - order them, or use b200kv_decode_attn with separate workspaces. */
+size_t b200kv_decode_attn_static_limit(void);
+int b200kv_decode_attn_static(const void* q, int64_t q_stride_b, int64_t q_stride_h,
+                              const b200kv_cache* cache, const b200kv_table* table,
+                              const int32_t* cached_lens, const int32_t* num_decoding, float scale,
+                              void* out, int64_t o_stride_b, int64_t o_stride_h,
+                              int32_t B, int32_t Hq, int32_t sm_count, int32_t* status, void* stream);
 
 #ifdef __cplusplus
 }

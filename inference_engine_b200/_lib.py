@@ -55,6 +55,9 @@ SIGNATURES = {
     "b200kv_decode_attn": (c_int32, [c_void_p, c_int64, c_int64, P_CACHE, P_TABLE, c_void_p, c_void_p, c_float, c_void_p,
                                      c_int64, c_int64, c_void_p, c_size_t, c_int32, c_int32, c_int32, c_int32, c_void_p,
                                      c_void_p]),
+    "b200kv_decode_attn_static_limit": (c_size_t, []),
+    "b200kv_decode_attn_static": (c_int32, [c_void_p, c_int64, c_int64, P_CACHE, P_TABLE, c_void_p, c_void_p, c_float,
+                                            c_void_p, c_int64, c_int64, c_int32, c_int32, c_int32, c_void_p, c_void_p]),
 }
 
 _lib = None

@@ -12,6 +12,7 @@ extern "C" const char* b200kv_error_string(int code) {
     case B200KV_E_WORKSPACE: return "workspace too small (see b200kv_decode_attn_workspace_bytes)";
     case B200KV_E_LAUNCH: return "CUDA launch failed";
     case B200KV_E_RANGE: return "size argument out of range";
+    case B200KV_E_STATIC_LIMIT: return "this batch needs more scratch than the 8 MiB built into the library: use b200kv_decode_attn with a caller workspace";
     default: return "unknown b200kv error";
   }
 }

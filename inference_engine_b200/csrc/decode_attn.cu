@@ -865,3 +865,48 @@ extern "C" int b200kv_decode_attn(const void* q, int64_t q_sb, int64_t q_sh, con
                                                     Hkv, G, W, min_tiles);
   return cudaGetLastError() == cudaSuccess ? B200KV_OK : B200KV_E_LAUNCH;
 }
+
+// ------------------------------------------------------------------ entry point that allocates nothing
+// Some hosts of this library may not create device memory at all when they reach the attention
+// call: a serving process that hands the whole HBM budget to its own KV-cache pool at start-up has
+// nothing left for cudaMalloc to carve from, a plug-in that runs inside someone else's stream
+// capture must not call an allocator (cudaMalloc synchronises the device and is illegal while
+// capturing), and latency-critical loops avoid it because its cost is unbounded.  For them the
+// scratch of the decode kernel (arrival counters + split partials) lives in a fixed array that is
+// part of the library image: every GPU that loads the library holds these bytes until the process
+// exits.
+namespace b200kv {
+constexpr size_t kStaticScratchBytes = 8u << 20;  // 148 SMs, 8 KV heads: Hq/Hkv = 2 to B ~ 130,000, Hq/Hkv = 4 to B ~ 25,000
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+constexpr int kMaxDevices = 64;
+static unsigned char* g_static_scratch_ptr[kMaxDevices] = {};  // device address per ordinal, set on first use
+}  // namespace b200kv
+
+extern "C" size_t b200kv_decode_attn_static_limit(void) { return kStaticScratchBytes; }
+
+extern "C" int b200kv_decode_attn_static(const void* q, int64_t q_sb, int64_t q_sh, const b200kv_cache* cache,
+                                         const b200kv_table* table, const int32_t* cached_lens,
+                                         const int32_t* num_decoding, float scale, void* out, int64_t o_sb,
+                                         int64_t o_sh, int32_t B, int32_t Hq, int32_t sm_count, int32_t* status,
+                                         void* stream) {
+  if (!cache) return B200KV_E_NULL;
+  const size_t need = b200kv_decode_attn_workspace_bytes(B, Hq, cache->num_kv_heads, cache->head_dim, sm_count);
+  if (need == 0) return B200KV_E_SHAPE;
+  if (need > kStaticScratchBytes) return B200KV_E_STATIC_LIMIT;
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return B200KV_E_LAUNCH;
+  if (!g_static_scratch_ptr[dev]) {
+    // In host code the array's name is only a handle; the kernel needs the address the symbol has
+    // on the current device.  Done once per device, with that device current.
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_static_scratch) != cudaSuccess || !p) return B200KV_E_LAUNCH;
+    g_static_scratch_ptr[dev] = static_cast<unsigned char*>(p);
+  }
+  unsigned char* scratch = g_static_scratch_ptr[dev];
+  // The array keeps whatever the previous call (possibly of another batch size) left behind; the
+  // prefix + arrival-counter head of THIS call's layout must start at zero.
+  if (B > 0 && cudaMemsetAsync(scratch, 0, ws_head_bytes(B, cache->num_kv_heads), (cudaStream_t)stream) != cudaSuccess)
+    return B200KV_E_LAUNCH;
+  return b200kv_decode_attn(q, q_sb, q_sh, cache, table, cached_lens, num_decoding, scale, out, o_sb, o_sh, scratch,
+                            kStaticScratchBytes, B, Hq, sm_count, 0, status, stream);
+}

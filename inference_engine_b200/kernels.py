@@ -171,6 +171,27 @@ def decode_attention(
     return out
 
 
+def decode_attention_static(q, kv_cache: LayerKVCache, cached_lens, slot_ids, num_decoding, scale, out: torch.Tensor):
+    """decode_attention for callers that must not allocate device memory at this point (all of it
+    already belongs to their own pool, or an allocator call is not allowed where they run): the
+    kernel's scratch is an 8 MiB array built into the library instead of a tensor, and `out` must
+    be supplied, so nothing here allocates.  Same result as decode_attention.  Raises ValueError
+    when the batch needs more than the built-in scratch.  Calls on one device share that array:
+    keep them stream-ordered.  Make the first call on a device outside any graph capture."""
+    _require_cuda(q, kv_cache.k, cached_lens, slot_ids, num_decoding, out)
+    lib = _lib.load()
+    B, Hq, D = q.shape
+    assert q.dtype == torch.bfloat16 and q.stride(-1) == 1
+    assert out.shape[0] >= B and out.shape[1:] == (Hq, D) and out.stride(-1) == 1
+    cs, ts = _cache_struct(kv_cache), _table_struct(slot_ids)
+    rc = lib.b200kv_decode_attn_static(
+        q.data_ptr(), q.stride(0), q.stride(1), ctypes.byref(cs), ctypes.byref(ts), _i32(cached_lens),
+        _i32(num_decoding), float(scale), out.data_ptr(), out.stride(0), out.stride(1), B, Hq, num_sms(q.device),
+        status_word(q.device).data_ptr(), _stream())
+    _lib.check(rc, "decode_attention_static")
+    return out
+
+
 def fused_rope_kv_decode(
     q: torch.Tensor,  # (B, Hq, D), one new token per sequence
     k: torch.Tensor,  # (B, Hkv, D)
