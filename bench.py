@@ -120,6 +120,7 @@ class CpuSample:
         self.q = O.bf16_round(rng.standard_normal((seqs, HQ, D)).astype(np.float32))
         self.cached = np.full(seqs, n - 1, np.int32)
         self.out = np.zeros((seqs, HQ, D), np.float32)
+        C.set_threads(os.cpu_count() or 1)
         self.threads = C.threads()
         self.bytes = passes * attn_bytes(seqs, n)
         self.sample = (f"decode attention, {seqs} of {B} sequences x ctx {n}, {passes} layer passes per step "

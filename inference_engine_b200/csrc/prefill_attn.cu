@@ -1,77 +1,64 @@
-// Packed variable-length causal attention for prefilling entries (chunked prefill):
-// every query row of an entry's chunk attends the entry's dequantized prefix (bf16, in full)
-// and the rows of its own chunk up to itself.  Replaces prefill_attention_kernel
-// (qwen3-1.7b/kernels.py:987-1126).
+// Packed variable-length causal attention for prefilling entries (chunked prefill): every query
+// row of an entry's chunk attends the entry's dequantized prefix (bf16, in full) and the rows of
+// its own chunk up to itself.  Replaces prefill_attention_kernel (qwen3-1.7b/kernels.py:987-1126).
 //
-// This first version is a straightforward CUDA-core kernel (fp32 FMAs, one warp per query row):
-// grid (num_tiles, Hq), 4 warps; warp w takes rows w, w+4, ... of its tile.  Keys are consumed
-// 32 at a time: each lane scores one key (q broadcast from shared memory), the warp does the
-// online-softmax update, then accumulates P.V with lane l owning channels 4l..4l+3.
+// Tensor-core flash attention: a CTA of 4 warps owns 64 query rows of one q head (a 128-row tile
+// of the caller is two such CTAs); each warp owns 16 rows.  Keys are consumed 64 at a time from
+// a double-buffered shared-memory ring filled with 16-byte cp.async copies (rows padded to 272
+// bytes so that ldmatrix reads are conflict-free).  S = Q K^T and O += P V run as bf16
+// mma.m16n8k16 with fp32 accumulation; K fragments come from ldmatrix, V fragments from
+// ldmatrix.trans; P is rounded to bf16 before P.V exactly as the reference does
+// (kernels.py:1068,1113); softmax in fp32 registers with exp2 and log2(e) folded into the scale
+// (kernels.py:1167-1168).  The score accumulator layout of one k16 slice is the A-fragment layout
+// of the second product, so P never leaves registers.
 #include "common.cuh"
 
 namespace b200kv {
 
 constexpr int kPfWarps = 4;
+constexpr int kPfRows = 16 * kPfWarps;   // query rows per CTA
+constexpr int kPfKeys = 64;              // keys per block
+constexpr int kPfRowBytes = kD * 2 + 16; // 272: padded bf16 row
+constexpr int kPfTileBytes = kPfKeys * kPfRowBytes;
 
-__device__ __forceinline__ float warp_max_f(float v) {
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
-  return v;
+__device__ __forceinline__ uint32_t pf_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void pf_cp16(uint32_t dst, const void* src, int bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
 }
-__device__ __forceinline__ float warp_sum_f(float v) {
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-  return v;
+__device__ __forceinline__ void pf_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void pf_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ float pf_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  return float_to_bf16_bits(lo) | (float_to_bf16_bits(hi) << 16);
 }
 
-struct KeySource {
-  const uint16_t* k;
-  const uint16_t* v;
-  long long k_stride, v_stride;  // elements between consecutive keys
-};
-
-// Consume keys [0, count) of `src` (key j's row at base + j*stride); keys j > limit are masked.
-__device__ __forceinline__ void consume(const KeySource& src, int count, int limit, const float* q_s, float scale_log2,
-                                        float& m, float& l, float (&acc)[4], int lane) {
-  for (int base = 0; base < count; base += 32) {
-    const int j = base + lane;
-    const bool live = j < count && j <= limit;
-    float s = -INFINITY;
-    if (live) {
-      const uint4* row = reinterpret_cast<const uint4*>(src.k + j * src.k_stride);
-      float dot = 0.f;
-#pragma unroll 4
-      for (int c = 0; c < 16; ++c) {
-        uint4 raw = row[c];
-        uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+// Copy `count` (<= 64) key rows of 128 bf16 (row j at src + j*stride elements) into a padded
+// tile; rows past `count` are zero-filled.
+__device__ __forceinline__ void load_tile(uint32_t dst, const uint16_t* src, long long stride, int count, int tid) {
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          dot = fmaf(q_s[8 * c + 2 * i], bf16_bits_to_float(w[i] & 0xFFFFu), dot);
-          dot = fmaf(q_s[8 * c + 2 * i + 1], bf16_bits_to_float(w[i] >> 16), dot);
-        }
-      }
-      s = dot * scale_log2;
-    }
-    const float mx = warp_max_f(s);
-    if (mx == -INFINITY) continue;  // every key of this group is masked (warp-uniform)
-    const float m_new = fmaxf(m, mx);
-    const float alpha = exp2f(m - m_new);
-    // the reference rounds P to bf16 before P.V (kernels.py:1068,1113); keep fp32 here (closer to exact)
-    const float p = live ? exp2f(s - m_new) : 0.f;
-    l = l * alpha + warp_sum_f(p);
-    m = m_new;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) acc[i] *= alpha;
-    const int nk = min(32, count - base);
-    for (int jj = 0; jj < nk; ++jj) {
-      const float pj = __shfl_sync(0xffffffffu, p, jj);
-      if (pj == 0.f) continue;
-      uint2 raw = *reinterpret_cast<const uint2*>(src.v + (long long)(base + jj) * src.v_stride + 4 * lane);
-      acc[0] = fmaf(pj, bf16_bits_to_float(raw.x & 0xFFFFu), acc[0]);
-      acc[1] = fmaf(pj, bf16_bits_to_float(raw.x >> 16), acc[1]);
-      acc[2] = fmaf(pj, bf16_bits_to_float(raw.y & 0xFFFFu), acc[2]);
-      acc[3] = fmaf(pj, bf16_bits_to_float(raw.y >> 16), acc[3]);
-    }
+  for (int i = 0; i < (kPfKeys * 16) / (kPfWarps * 32); ++i) {
+    const int c = tid + i * kPfWarps * 32, r = c >> 4, col = c & 15;
+    const bool valid = r < count;
+    pf_cp16(dst + r * kPfRowBytes + col * 16, valid ? src + r * stride + col * 8 : src, valid ? 16 : 0);
   }
 }
 
@@ -79,40 +66,147 @@ __global__ void __launch_bounds__(kPfWarps * 32)
 prefill_attn_kernel(const uint16_t* __restrict__ q, long long q_sn, long long q_sh, const uint16_t* __restrict__ k,
                     long long k_sn, long long k_sh, const uint16_t* __restrict__ v, long long v_sn, long long v_sh,
                     const int32_t* __restrict__ seq_ids, const int32_t* __restrict__ cu_seqlens,
-                    const int32_t* __restrict__ tile_start, int block_m, const uint16_t* __restrict__ k_prefix,
+                    const int32_t* __restrict__ tile_start, int block_m, int subs, const uint16_t* __restrict__ k_prefix,
                     const uint16_t* __restrict__ v_prefix, long long p_sh, long long p_sn,
                     const int32_t* __restrict__ cu_cached, uint16_t* __restrict__ out, long long o_sn, long long o_sh,
                     int N, int G, float scale_log2) {
-  __shared__ __align__(16) float q_all[kPfWarps][kD];
-  const int row_start = tile_start[blockIdx.x];
-  if (row_start < 0 || row_start >= N) return;
+  extern __shared__ __align__(128) uint8_t pf_smem[];
+  const int tile = blockIdx.x / subs, sub = blockIdx.x - tile * subs;
+  const int tile_row = tile_start[tile];
+  if (tile_row < 0 || tile_row >= N) return;
   const int hq = blockIdx.y, hk = hq / G;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int seq = seq_ids[row_start];
+  const int seq = seq_ids[tile_row];
   const int prefix_start = cu_cached[seq], prefix_len = cu_cached[seq + 1] - prefix_start;
   const int seq_start = cu_seqlens[seq], seq_end = min(cu_seqlens[seq + 1], N);
-  const int row_end = min(row_start + block_m, seq_end);
-  float* q_s = q_all[warp];
-  KeySource pre{k_prefix + hk * p_sh + (long long)prefix_start * p_sn, v_prefix + hk * p_sh + (long long)prefix_start * p_sn, p_sn, p_sn};
-  KeySource own{k + (long long)seq_start * k_sn + hk * k_sh, v + (long long)seq_start * v_sn + hk * v_sh, k_sn, v_sn};
-  for (int r = row_start + warp; r < row_end; r += kPfWarps) {
-    __syncwarp();
-    {
-      uint2 raw = *reinterpret_cast<const uint2*>(q + r * q_sn + hq * q_sh + 4 * lane);
-      q_s[4 * lane] = bf16_bits_to_float(raw.x & 0xFFFFu);
-      q_s[4 * lane + 1] = bf16_bits_to_float(raw.x >> 16);
-      q_s[4 * lane + 2] = bf16_bits_to_float(raw.y & 0xFFFFu);
-      q_s[4 * lane + 3] = bf16_bits_to_float(raw.y >> 16);
+  const int row_end = min(tile_row + block_m, seq_end);
+  const int row0 = tile_row + sub * kPfRows;  // first query row of this CTA
+  if (row0 >= row_end) return;
+  const int cta_last = min(row0 + kPfRows, row_end) - 1;  // last query row of this CTA
+  const int own_keys = cta_last - seq_start + 1;          // causal: keys up to the last query
+  const int nb_pre = (prefix_len + kPfKeys - 1) / kPfKeys, nb_own = (own_keys + kPfKeys - 1) / kPfKeys;
+  const int nb = nb_pre + nb_own;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+  const uint32_t smem0 = pf_smem_u32(pf_smem);
+  const uint16_t* kpre = k_prefix + hk * p_sh + (long long)prefix_start * p_sn;
+  const uint16_t* vpre = v_prefix + hk * p_sh + (long long)prefix_start * p_sn;
+  const uint16_t* kown = k + (long long)seq_start * k_sn + hk * k_sh;
+  const uint16_t* vown = v + (long long)seq_start * v_sn + hk * v_sh;
+
+  auto issue = [&](int kb) {
+    const uint32_t sk = smem0 + (kb & 1) * 2 * kPfTileBytes, sv = sk + kPfTileBytes;
+    if (kb < nb_pre) {
+      const int j0 = kb * kPfKeys, cnt = min(kPfKeys, prefix_len - j0);
+      load_tile(sk, kpre + (long long)j0 * p_sn, p_sn, cnt, tid);
+      load_tile(sv, vpre + (long long)j0 * p_sn, p_sn, cnt, tid);
+    } else {
+      const int j0 = (kb - nb_pre) * kPfKeys, cnt = min(kPfKeys, own_keys - j0);
+      load_tile(sk, kown + (long long)j0 * k_sn, k_sn, cnt, tid);
+      load_tile(sv, vown + (long long)j0 * v_sn, v_sn, cnt, tid);
     }
-    __syncwarp();
-    float m = -INFINITY, l = 0.f, acc[4] = {0.f, 0.f, 0.f, 0.f};
-    consume(pre, prefix_len, prefix_len, q_s, scale_log2, m, l, acc, lane);
-    consume(own, r - seq_start + 1, r - seq_start, q_s, scale_log2, m, l, acc, lane);
-    const float inv = l != 0.f ? 1.f / l : 0.f;
-    uint2 w;
-    w.x = float_to_bf16_bits(acc[0] * inv) | (float_to_bf16_bits(acc[1] * inv) << 16);
-    w.y = float_to_bf16_bits(acc[2] * inv) | (float_to_bf16_bits(acc[3] * inv) << 16);
-    *reinterpret_cast<uint2*>(out + r * o_sn + hq * o_sh + 4 * lane) = w;
+    pf_commit();
+  };
+  issue(0);
+
+  // Q fragments of this warp's 16 rows (rows past the end are read from a valid row and never stored)
+  const int qr0 = row0 + warp * 16 + g, qr1 = qr0 + 8;
+  const uint16_t* q0 = q + (long long)min(qr0, row_end - 1) * q_sn + hq * q_sh;
+  const uint16_t* q1 = q + (long long)min(qr1, row_end - 1) * q_sn + hq * q_sh;
+  uint32_t qa[8][4];
+#pragma unroll
+  for (int s = 0; s < 8; ++s) {
+    qa[s][0] = *reinterpret_cast<const uint32_t*>(q0 + 16 * s + 2 * t);
+    qa[s][1] = *reinterpret_cast<const uint32_t*>(q1 + 16 * s + 2 * t);
+    qa[s][2] = *reinterpret_cast<const uint32_t*>(q0 + 16 * s + 8 + 2 * t);
+    qa[s][3] = *reinterpret_cast<const uint32_t*>(q1 + 16 * s + 8 + 2 * t);
+  }
+  float o[16][4];
+#pragma unroll
+  for (int j = 0; j < 16; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;  // rows g and g+8 (l: this lane's share)
+  // ldmatrix lane addressing inside a tile (see the fragment notes at the top of the file)
+  const uint32_t k_lane = ((lane >> 4) * 8 + (lane & 7)) * kPfRowBytes + ((lane >> 3) & 1) * 16;
+  const uint32_t v_lane = (((lane >> 3) & 1) * 8 + (lane & 7)) * kPfRowBytes + (lane >> 4) * 16;
+
+  for (int kb = 0; kb < nb; ++kb) {
+    if (kb + 1 < nb) { issue(kb + 1); pf_wait<1>(); } else { pf_wait<0>(); }
+    __syncthreads();
+    const uint32_t sk = smem0 + (kb & 1) * 2 * kPfTileBytes, sv = sk + kPfTileBytes;
+    // ---- S = Q K^T for 64 keys: 8 n-tiles of 8 keys
+    float s[8][4];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks) {     // 16 channels per step
+#pragma unroll
+      for (int jp = 0; jp < 4; ++jp) {   // 16 keys per ldmatrix.x4
+        uint32_t b[4];
+        ldsm_x4(b, sk + k_lane + jp * 16 * kPfRowBytes + ks * 32);
+        mma_bf16(s[2 * jp], qa[ks], b[0], b[1]);
+        mma_bf16(s[2 * jp + 1], qa[ks], b[2], b[3]);
+      }
+    }
+    // ---- mask + online softmax.  s[j][0..1]: row g, keys 8j+2t, +1;  s[j][2..3]: row g+8
+    const bool pre = kb < nb_pre;
+    const int j0 = pre ? kb * kPfKeys : (kb - nb_pre) * kPfKeys;
+    // visible key count per row inside this block
+    const int lim0 = pre ? prefix_len - j0 : min(own_keys, qr0 - seq_start + 1) - j0;
+    const int lim1 = pre ? prefix_len - j0 : min(own_keys, qr1 - seq_start + 1) - j0;
+    float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int kk = 8 * j + 2 * t;
+      s[j][0] = kk < lim0 ? s[j][0] * scale_log2 : -INFINITY;
+      s[j][1] = kk + 1 < lim0 ? s[j][1] * scale_log2 : -INFINITY;
+      s[j][2] = kk < lim1 ? s[j][2] * scale_log2 : -INFINITY;
+      s[j][3] = kk + 1 < lim1 ? s[j][3] * scale_log2 : -INFINITY;
+      mx0 = fmaxf(mx0, fmaxf(s[j][0], s[j][1]));
+      mx1 = fmaxf(mx1, fmaxf(s[j][2], s[j][3]));
+    }
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+    const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+    const float sm0 = mn0 == -INFINITY ? 0.f : mn0, sm1 = mn1 == -INFINITY ? 0.f : mn1;  // kernels.py:1062
+    const float al0 = pf_exp2(m0 - sm0), al1 = pf_exp2(m1 - sm1);
+    m0 = mn0; m1 = mn1;
+    uint32_t pa[4][4];  // P as A fragments of the 4 k16 slices
+    float ps0 = 0.f, ps1 = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float p0 = pf_exp2(s[j][0] - sm0), p1 = pf_exp2(s[j][1] - sm0);
+      const float p2 = pf_exp2(s[j][2] - sm1), p3 = pf_exp2(s[j][3] - sm1);
+      ps0 += p0 + p1; ps1 += p2 + p3;
+      pa[j >> 1][(j & 1) * 2] = pack_bf16x2(p0, p1);      // a0 / a2: row g
+      pa[j >> 1][(j & 1) * 2 + 1] = pack_bf16x2(p2, p3);  // a1 / a3: row g+8
+    }
+    l0 = l0 * al0 + ps0; l1 = l1 * al1 + ps1;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) { o[j][0] *= al0; o[j][1] *= al0; o[j][2] *= al1; o[j][3] *= al1; }
+    // ---- O += P V: 4 k16 slices of keys x 16 n-tiles of 8 channels
+#pragma unroll
+    for (int kk = 0; kk < 4; ++kk) {
+#pragma unroll
+      for (int dp = 0; dp < 8; ++dp) {   // 16 channels per ldmatrix.x4.trans
+        uint32_t b[4];
+        ldsm_x4_trans(b, sv + v_lane + kk * 16 * kPfRowBytes + dp * 32);
+        mma_bf16(o[2 * dp], pa[kk], b[0], b[1]);
+        mma_bf16(o[2 * dp + 1], pa[kk], b[2], b[3]);
+      }
+    }
+    __syncthreads();  // everyone is done with this stage before it is refilled
+  }
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+  const float i0 = l0 != 0.f ? 1.f / l0 : 0.f, i1 = l1 != 0.f ? 1.f / l1 : 0.f;  // kernels.py:1118
+  if (qr0 < row_end) {
+    uint16_t* dst = out + (long long)qr0 * o_sn + hq * o_sh + 2 * t;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) *reinterpret_cast<uint32_t*>(dst + 8 * j) = pack_bf16x2(o[j][0] * i0, o[j][1] * i0);
+  }
+  if (qr1 < row_end) {
+    uint16_t* dst = out + (long long)qr1 * o_sn + hq * o_sh + 2 * t;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) *reinterpret_cast<uint32_t*>(dst + 8 * j) = pack_bf16x2(o[j][2] * i1, o[j][3] * i1);
   }
 }
 
@@ -136,10 +230,18 @@ extern "C" int b200kv_prefill_attn(const void* q, int64_t q_sn, int64_t q_sh, co
   for (int64_t s : strides)
     if (s % 8) return B200KV_E_ALIGN;
   if (N == 0 || num_tiles == 0) return B200KV_OK;
+  const int subs = (block_m + kPfRows - 1) / kPfRows;
+  const size_t smem = 4 * (size_t)kPfTileBytes;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(prefill_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+      return B200KV_E_LAUNCH;
+    attr_set = true;
+  }
   const float scale_log2 = (1.0f / sqrtf((float)D)) * 1.4426950408889634f;
-  prefill_attn_kernel<<<dim3(num_tiles, Hq), kPfWarps * 32, 0, (cudaStream_t)stream>>>(
+  prefill_attn_kernel<<<dim3(num_tiles * subs, Hq), kPfWarps * 32, smem, (cudaStream_t)stream>>>(
       (const uint16_t*)q, q_sn, q_sh, (const uint16_t*)k, k_sn, k_sh, (const uint16_t*)v, v_sn, v_sh, seq_ids, cu_seqlens,
-      tile_start, block_m, (const uint16_t*)k_prefix, (const uint16_t*)v_prefix, p_sh, p_sn, cu_cached, (uint16_t*)out,
-      o_sn, o_sh, N, Hq / Hkv, scale_log2);
+      tile_start, block_m, subs, (const uint16_t*)k_prefix, (const uint16_t*)v_prefix, p_sh, p_sn, cu_cached,
+      (uint16_t*)out, o_sn, o_sh, N, Hq / Hkv, scale_log2);
   return cudaGetLastError() == cudaSuccess ? B200KV_OK : B200KV_E_LAUNCH;
 }

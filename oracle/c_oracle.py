@@ -26,6 +26,11 @@ def _p(a: np.ndarray):
     return a.ctypes.data_as(C.c_void_p)
 
 
+def set_threads(n: int) -> None:
+    """Use n OpenMP threads (launchers such as torchrun export OMP_NUM_THREADS=1)."""
+    lib().kv_set_threads(C.c_int(int(n)))
+
+
 def threads() -> int:
     return int(lib().kv_threads())
 

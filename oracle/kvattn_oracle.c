@@ -37,6 +37,14 @@ static float pairwise_sum64(const float* a) {
   return ((r[0] + r[1]) + (r[2] + r[3])) + ((r[4] + r[5]) + (r[6] + r[7]));
 }
 
+void kv_set_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
 int kv_threads(void) {
 #ifdef _OPENMP
   return omp_get_max_threads();
