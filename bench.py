@@ -293,6 +293,71 @@ def run_b200(args):
         dist.destroy_process_group()
 
 
+def run_sweep(args):
+    """--sweep: decode attention alone over the 45-cell grid B in {1..256} x ctx in {128..4096}
+    (the 40 cells of the sweep config plus the 5 largest it drops), one JSON line per cell.
+    Every cell runs a CUDA graph of L calls on L distinct layer caches, L chosen so that the graph
+    streams at least 300 MB (more than the 126 MB L2) and at least 28 layers."""
+    import torch
+
+    from inference_engine_b200 import kernels as K
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    peak, peak_kind = peaks()
+    gen = torch.Generator(device=dev).manual_seed(2)
+    dropped = {(256, 4096), (256, 2048), (128, 4096), (256, 1024), (128, 2048)}
+    for B in (1, 2, 4, 8, 16, 32, 64, 128, 256):
+        for n in (128, 512, 1024, 2048, 4096):
+            nbytes = attn_bytes(B, n)
+            L = int(min(1024, max(28, -(-300_000_000 // nbytes))))
+            pages_per_seq = (n + PAGE - 1) // PAGE
+            num_pages = B * pages_per_seq + 1
+            caches = []
+            for _ in range(L):
+                c = K.make_layer_cache(num_pages, HKV, PAGE, D, device=dev)
+                c.k.copy_(torch.randint(-127, 128, c.k.shape, generator=gen, device=dev, dtype=torch.int8))
+                c.v.copy_(torch.randint(-127, 128, c.v.shape, generator=gen, device=dev, dtype=torch.int8))
+                c.k_scale.fill_(0.02)
+                c.v_scale.fill_(0.02)
+                caches.append(c)
+            table = torch.randperm(num_pages - 1, generator=torch.Generator().manual_seed(2)).to(torch.int32)
+            table = table.reshape(B, pages_per_seq).to(dev)
+            q = torch.randn(B, HQ, D, generator=gen, device=dev).to(torch.bfloat16)
+            out = torch.empty_like(q)
+            cached = torch.full((B,), n - 1, dtype=torch.int32, device=dev)
+            nd = torch.tensor([B], dtype=torch.int32, device=dev)
+
+            def calls():
+                for c in caches:
+                    K.decode_attention(q, c, cached, table, nd, D ** -0.5, out=out)
+
+            calls()
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                calls()
+            for _ in range(3):
+                graph.replay()
+            torch.cuda.synchronize()
+            times = []
+            for _ in range(args.steps):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                graph.replay()
+                e1.record()
+                torch.cuda.synchronize()
+                times.append(e0.elapsed_time(e1) * 1e3 / L)
+            us = statistics.median(times)
+            gbs = nbytes / us / 1e3
+            print(json.dumps({"B": B, "ctx": n, "layers_in_graph": L, "us_per_call": round(us, 2),
+                              "us_min": round(min(times), 2), "gbs": round(gbs, 1), "pct_of_8TBs": round(gbs / 80.0, 2),
+                              "frac_of_measured": round(gbs / peak, 4), "in_sweep_config": (B, n) not in dropped,
+                              "bytes": nbytes}), flush=True)
+            del caches, graph
+            torch.cuda.empty_cache()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -305,8 +370,11 @@ def main():
     ap.add_argument("--cpu-seqs", type=int, default=64, help="sequences in the CPU baseline sample")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--traffic", type=float, default=NCU_TRAFFIC_BYTES, help="ncu DRAM bytes per decode_attention call, if known")
+    ap.add_argument("--sweep", action="store_true", help="decode-attention shape sweep instead of the headline step")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.sweep:
+        run_sweep(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_b200(args)

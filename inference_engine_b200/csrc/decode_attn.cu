@@ -591,6 +591,7 @@ __device__ __forceinline__ void merge_partials(const float* __restrict__ ws_ml, 
                                                int w_first, int w_last, int slot_first, int G,
                                                uint16_t* __restrict__ out_row, long long o_sh, int lane) {
   for (int col = 0; col < G; ++col) {
+    // pass 1: global maximum, lanes spread over the pieces
     float M = -INFINITY;
     for (int w = w_first + lane; w <= w_last; w += 32) {
       const size_t base = ((size_t)w * 2 + (w == w_first ? slot_first : 0)) * G + col;
@@ -598,25 +599,41 @@ __device__ __forceinline__ void merge_partials(const float* __restrict__ ws_ml, 
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
-    float L = 0.f;
+    // pass 2, 32 pieces at a time: lane i turns piece i's (m, l) into a weight; then every lane
+    // sums its four channels over the batch - the loads do not depend on each other, so up to 8
+    // are in flight per lane
+    float Lsum = 0.f;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 4
-    for (int w = w_first; w <= w_last; ++w) {
-      const size_t base = ((size_t)w * 2 + (w == w_first ? slot_first : 0)) * G + col;
-      const float2 ml = __ldcg(reinterpret_cast<const float2*>(ws_ml + base * 2));
-      const float4 o = __ldcg(reinterpret_cast<const float4*>(ws_o + base * kD + 4 * lane));
-      const float wg = fast_exp2(ml.x - M);
-      L = fmaf(ml.y, wg, L);
-      acc.x = fmaf(o.x, wg, acc.x); acc.y = fmaf(o.y, wg, acc.y);
-      acc.z = fmaf(o.z, wg, acc.z); acc.w = fmaf(o.w, wg, acc.w);
+    for (int w0 = w_first; w0 <= w_last; w0 += 32) {
+      const int nb = min(32, w_last - w0 + 1);
+      float wgt = 0.f;
+      if (lane < nb) {
+        const int w = w0 + lane;
+        const size_t base = ((size_t)w * 2 + (w == w_first ? slot_first : 0)) * G + col;
+        const float2 ml = __ldcg(reinterpret_cast<const float2*>(ws_ml + base * 2));
+        wgt = fast_exp2(ml.x - M);
+        Lsum = fmaf(ml.y, wgt, Lsum);
+      }
+#pragma unroll 8
+      for (int i = 0; i < nb; ++i) {
+        const int w = w0 + i;
+        const size_t base = ((size_t)w * 2 + (w == w_first ? slot_first : 0)) * G + col;
+        const float4 o = __ldcg(reinterpret_cast<const float4*>(ws_o + base * kD + 4 * lane));
+        const float wg = __shfl_sync(0xffffffffu, wgt, i);
+        acc.x = fmaf(o.x, wg, acc.x); acc.y = fmaf(o.y, wg, acc.y);
+        acc.z = fmaf(o.z, wg, acc.z); acc.w = fmaf(o.w, wg, acc.w);
+      }
     }
-    const float inv = 1.f / L;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) Lsum += __shfl_xor_sync(0xffffffffu, Lsum, o);
+    const float inv = 1.f / Lsum;
     uint2 r;
     r.x = float_to_bf16_bits(acc.x * inv) | (float_to_bf16_bits(acc.y * inv) << 16);
     r.y = float_to_bf16_bits(acc.z * inv) | (float_to_bf16_bits(acc.w * inv) << 16);
     *reinterpret_cast<uint2*>(out_row + col * o_sh + 4 * lane) = r;
   }
 }
+
 __host__ __device__ inline size_t ws_ml_bytes(int W, int G) { return (((size_t)W * 2 * G * 2 * 4 + 255) / 256) * 256; }
 
 template <bool kScalar>
