@@ -176,6 +176,7 @@ def run_b200(args):
     local = int(os.environ.get("LOCAL_RANK", "0"))
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the kernels have no CPU path")
+    K.set_early_start(not args.no_early_start)
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
@@ -370,6 +371,7 @@ def main():
     ap.add_argument("--cpu-seqs", type=int, default=64, help="sequences in the CPU baseline sample")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--traffic", type=float, default=NCU_TRAFFIC_BYTES, help="ncu DRAM bytes per decode_attention call, if known")
+    ap.add_argument("--no-early-start", action="store_true", help="launch decode attention without programmatic early start")
     ap.add_argument("--sweep", action="store_true", help="decode-attention shape sweep instead of the headline step")
     args = ap.parse_args()
     if args.sweep:

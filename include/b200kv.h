@@ -163,7 +163,12 @@ size_t b200kv_decode_attn_workspace_bytes(int32_t B, int32_t Hq, int32_t Hkv, in
  * q bf16 [B,Hq,D] is the q_out of b200kv_write_decode.  `variant` bit 0: 0 = tensor-core kernel
  * (the product path), 1 = scalar CUDA-core kernel kept for cross-checking; bit 1: 0 = the
  * cross-split reduction is fused into the attention kernel (the warp delivering the last piece of
- * an (entry, head) merges them), 1 = it runs as a second kernel like the reference's. */
+ * an (entry, head) merges them), 1 = it runs as a second kernel like the reference's; bit 2: 1 =
+ * early start: the kernel may be scheduled while the kernel launched just before it on `stream`
+ * is still running, and reads cached_lens, num_decoding and the block table before waiting for
+ * it (cache, q and workspace are read after the wait).  Set it only when that preceding kernel
+ * does not write those three arrays - true for b200kv_write_decode, the call the engine makes
+ * right before (architecture.py:101-123). */
 int b200kv_decode_attn(const void* q, int64_t q_stride_b, int64_t q_stride_h,
                        const b200kv_cache* cache, const b200kv_table* table,
                        const int32_t* cached_lens, const int32_t* num_decoding, float scale,

@@ -103,21 +103,38 @@ __device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1
 }
 
 // ------------------------------------------------------------------ partition (all CTAs agree)
-__device__ __forceinline__ int tiles_of(const int32_t* __restrict__ cached_lens, int b, int nd) {
-  return b < nd ? (cached_lens[b] + 1 + kTile - 1) / kTile : 0;
-}
+constexpr int kSmemLens = 512;  // token counts of the first entries are kept in shared memory
+
+// Tokens each entry attends (cached_len + 1; 0 past num_decoding), from shared memory for the
+// first kSmemLens entries (no global round trip when a warp positions itself), else from global.
+struct Lens {
+  const int32_t* __restrict__ g;
+  const int* s;
+  int nd;
+  __device__ __forceinline__ int n(int b) const { return b < kSmemLens ? s[b] : (b < nd ? g[b] + 1 : 0); }
+  __device__ __forceinline__ int tiles(int b) const { return (n(b) + kTile - 1) / kTile; }
+};
 
 // Tiles per kv head of entries [0,B), scanned by the whole CTA.  Thread i owns the `chunk`
 // consecutive entries starting at i*chunk; chunk_prefix[i] (shared, blockDim.x+1 ints) is the
-// number of tiles before that chunk, chunk_prefix[blockDim.x] the total.  When `gprefix` is
-// given (one CTA does this) the per-entry exclusive prefix [B+1] is also written to global
-// memory for the reduction kernel.
-__device__ void scan_tiles(const int32_t* __restrict__ cached_lens, int B, int nd, int chunk, int* chunk_prefix,
-                           int* __restrict__ gprefix) {
+// number of tiles before that chunk, chunk_prefix[blockDim.x] the total; lens_s receives the
+// token counts of the first kSmemLens entries.  The loads of cached_lens do not wait for
+// num_decoding (it only masks them).  When `gprefix` is given (one CTA does this) the per-entry
+// exclusive prefix [B+1] is also written to global memory for the separate reduction kernel.
+__device__ void scan_tiles(const int32_t* __restrict__ cached_lens, int B, const int32_t* __restrict__ num_decoding,
+                           int chunk, int* chunk_prefix, int* lens_s, int* __restrict__ gprefix, int& nd_out) {
   const int tid = threadIdx.x, nt = blockDim.x;
   const int lo = min(tid * chunk, B), hi = min(lo + chunk, B);
+  const int nd_raw = *num_decoding;
+  int first = lo < hi ? cached_lens[lo] : 0;  // issued together with the load above
+  const int nd = min(nd_raw, B);
   int sum = 0;
-  for (int b = lo; b < hi; ++b) sum += tiles_of(cached_lens, b, nd);
+  for (int b = lo; b < hi; ++b) {
+    const int cl = b == lo ? first : cached_lens[b];
+    const int n = b < nd ? cl + 1 : 0;
+    if (b < kSmemLens) lens_s[b] = n;
+    sum += (n + kTile - 1) / kTile;
+  }
   chunk_prefix[tid] = sum;
   __syncthreads();
   if (tid < 32) {  // exclusive scan of the nt chunk sums by one warp
@@ -140,10 +157,11 @@ __device__ void scan_tiles(const int32_t* __restrict__ cached_lens, int B, int n
     int run = chunk_prefix[tid];
     for (int b = lo; b < hi; ++b) {
       gprefix[b] = run;
-      run += tiles_of(cached_lens, b, nd);
+      run += (b < nd ? (cached_lens[b] + 1 + kTile - 1) / kTile : 0);
     }
     if (tid == 0) gprefix[B] = chunk_prefix[nt];
   }
+  nd_out = nd;
 }
 
 __host__ __device__ __forceinline__ Partition make_partition(int total_tiles_one_head, int Hkv, int W, int min_tiles) {
@@ -160,8 +178,8 @@ __host__ __device__ __forceinline__ Partition make_partition(int total_tiles_one
 // so the hot loop never divides.
 struct Cursor {
   int b, h, tile, T, n, slot, row0, base;  // base: flat index of (entry b, head 0, tile 0)
-  __device__ __forceinline__ void seek(const int* chunk_prefix, int nchunks, int chunk, const int32_t* cached_lens,
-                                       int nd, int Hkv, int page_size, int u) {
+  __device__ __forceinline__ void seek(const int* chunk_prefix, int nchunks, int chunk, const Lens& lens, int Hkv,
+                                       int page_size, int u) {
     int lo = 0, hi = nchunks;  // largest chunk whose first flat index is <= u
     while (hi - lo > 1) {
       int mid = (lo + hi) >> 1;
@@ -170,12 +188,12 @@ struct Cursor {
     b = lo * chunk;
     int run = chunk_prefix[lo];
     while (true) {
-      T = tiles_of(cached_lens, b, nd);
+      T = lens.tiles(b);
       if (Hkv * (run + T) > u) break;
       run += T;
       ++b;
     }
-    n = cached_lens[b] + 1;
+    n = lens.n(b);
     base = Hkv * run;
     int r = u - base;
     h = r / T;
@@ -184,16 +202,16 @@ struct Cursor {
     row0 = tile * kTile - slot * page_size;
   }
   // First tile of the next (entry, head); only called while one exists.
-  __device__ __forceinline__ void next_segment(const int32_t* cached_lens, int nd, int Hkv) {
+  __device__ __forceinline__ void next_segment(const Lens& lens, int Hkv) {
     tile = 0; slot = 0; row0 = 0;
     if (++h < Hkv) return;
     h = 0;
     base += Hkv * T;
-    do { ++b; T = tiles_of(cached_lens, b, nd); } while (T == 0);
-    n = cached_lens[b] + 1;
+    do { ++b; T = lens.tiles(b); } while (T == 0);
+    n = lens.n(b);
   }
   // Next tile in flat order; only called while one exists.
-  __device__ __forceinline__ void next(const int32_t* cached_lens, int nd, int Hkv, int page_size) {
+  __device__ __forceinline__ void next(const Lens& lens, int Hkv, int page_size) {
     if (++tile < T) {
       row0 += kTile;
       const bool wrap = row0 >= page_size;
@@ -201,7 +219,7 @@ struct Cursor {
       slot += wrap ? 1 : 0;
       return;
     }
-    next_segment(cached_lens, nd, Hkv);
+    next_segment(lens, Hkv);
   }
 };
 
@@ -641,15 +659,21 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm)
 decode_attn_kernel(const uint16_t* __restrict__ q, long long q_sb, long long q_sh, CacheView c,
                    const int32_t* __restrict__ cached_lens, const int32_t* __restrict__ num_decoding, float scale_log2,
                    uint16_t* __restrict__ out, long long o_sb, long long o_sh, uint8_t* __restrict__ workspace, int B,
-                   int G, int min_tiles, int fused, int32_t* status) {
+                   int G, int min_tiles, int fused, int early, int32_t* status) {
   extern __shared__ __align__(128) uint8_t smem[];
   uint8_t* ring = smem;                                                       // kWarps * kStages * kTileBytes
   float* q_s = reinterpret_cast<float*>(ring + kWarps * kStages * kTileBytes);  // scalar variant: kWarps * (G*128 + G*16)
   int* chunk_prefix = reinterpret_cast<int*>(q_s + (kScalar ? kWarps * (kMaxG * kD + kMaxG * kTile) : 0));
 
-  const int nd = min(*num_decoding, B);
+  // Let a programmatically-dependent successor be scheduled as SMs free up (it waits for this grid
+  // to complete before it touches anything this grid writes).
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  int* lens_s = chunk_prefix + kWarps * 32 + 1;
   const int nchunks = blockDim.x, chunk = (B + nchunks - 1) / nchunks;
-  scan_tiles(cached_lens, B, nd, chunk, chunk_prefix, blockIdx.x == 0 ? reinterpret_cast<int*>(workspace) : nullptr);
+  int nd;
+  scan_tiles(cached_lens, B, num_decoding, chunk, chunk_prefix, lens_s,
+             (blockIdx.x == 0 && !fused) ? reinterpret_cast<int*>(workspace) : nullptr, nd);
+  const Lens lens{cached_lens, lens_s, nd};
   const int W = gridDim.x * kWarps;
   const Partition part = make_partition(chunk_prefix[nchunks], c.Hkv, W, min_tiles);
 
@@ -668,17 +692,20 @@ decode_attn_kernel(const uint16_t* __restrict__ q, long long q_sb, long long q_s
   float* my_q = q_s + warp * (kMaxG * kD + kMaxG * kTile);
 
   Cursor pc;  // producer position (runs kStages-1 tiles ahead of the consumer)
-  pc.seek(chunk_prefix, nchunks, chunk, cached_lens, nd, c.Hkv, c.page_size, u0);
+  pc.seek(chunk_prefix, nchunks, chunk, lens, c.Hkv, c.page_size, u0);
   Cursor cc = pc;  // consumer position, advanced segment by segment
   PageWindow win{-1, 0, -1};
   const LaneCopy lc = make_lane_copy(c, lane);
 
+  // Early start: everything above read only the batch metadata.  The cache, q and the workspace
+  // may still be in flight from the kernel launched just before this one: wait for it here.
+  if (early) asm volatile("griddepcontrol.wait;" ::: "memory");
   int p_left = ntiles;  // tiles not yet issued
 #pragma unroll
   for (int i = 0; i < kStages - 1; ++i) {
     if (p_left > 0) {
       issue_tile(c, pc, win, lc, my_ring_s + i * kTileBytes, lane, status);
-      if (--p_left > 0) pc.next(cached_lens, nd, c.Hkv, c.page_size);
+      if (--p_left > 0) pc.next(lens, c.Hkv, c.page_size);
     }
     cp_async_commit();
   }
@@ -696,7 +723,7 @@ decode_attn_kernel(const uint16_t* __restrict__ q, long long q_sb, long long q_s
     for (int k = 0; k < seg; ++k) {
       if (p_left > 0) {
         issue_tile(c, pc, win, lc, my_ring_s + stage_p * kTileBytes, lane, status);
-        if (--p_left > 0) pc.next(cached_lens, nd, c.Hkv, c.page_size);
+        if (--p_left > 0) pc.next(lens, c.Hkv, c.page_size);
       }
       cp_async_commit();
       cp_async_wait<kStages - 1>();
@@ -734,7 +761,7 @@ decode_attn_kernel(const uint16_t* __restrict__ q, long long q_sb, long long q_s
       }
     }
     done += seg;
-    if (done < ntiles) cc.next_segment(cached_lens, nd, c.Hkv);
+    if (done < ntiles) cc.next_segment(lens, c.Hkv);
   }
   cp_async_wait<0>();
 }
@@ -820,7 +847,7 @@ decode_combine_kernel(const uint8_t* __restrict__ workspace, const int32_t* __re
 static size_t main_smem_bytes(int B, bool scalar) {
   size_t s = (size_t)kWarps * kStages * kTileBytes;
   if (scalar) s += (size_t)kWarps * (kMaxG * kD + kMaxG * kTile) * 4;
-  s += (size_t)(kWarps * 32 + 1) * 4;
+  s += (size_t)(kWarps * 32 + 1 + kSmemLens) * 4;
   (void)B;
   return s;
 }
@@ -845,7 +872,7 @@ extern "C" int b200kv_decode_attn(const void* q, int64_t q_sb, int64_t q_sh, con
   int rc = check_cache(cache, table);
   if (rc) return rc;
   const int Hkv = cache->num_kv_heads;
-  if (B < 0 || Hq < 1 || Hq % Hkv || Hq / Hkv > kMaxG || sm_count < 1 || variant < 0 || variant > 3) return B200KV_E_SHAPE;
+  if (B < 0 || Hq < 1 || Hq % Hkv || Hq / Hkv > kMaxG || sm_count < 1 || variant < 0 || variant > 7) return B200KV_E_SHAPE;
   if (B > kMaxB) return B200KV_E_RANGE;
   if (!aligned(q, 16) || !aligned(out, 16) || !aligned(workspace, 256) || (q_sb % 8) || (q_sh % 8) || (o_sb % 8) || (o_sh % 8))
     return B200KV_E_ALIGN;
@@ -859,6 +886,7 @@ extern "C" int b200kv_decode_attn(const void* q, int64_t q_sb, int64_t q_sh, con
   cudaStream_t s = (cudaStream_t)stream;
   const bool scalar = (variant & 1) != 0;
   const int fused = (variant & 2) ? 0 : 1;
+  const int early = ((variant & 4) && fused) ? 1 : 0;  // the separate reduction kernel's prefix array is written before the wait
   const size_t smem = main_smem_bytes(B, scalar);
   static bool attr_set[2] = {false, false};  // the opt-in to > 48 KB of dynamic shared memory is per function
   if (!attr_set[variant & 1]) {
@@ -868,14 +896,21 @@ extern "C" int b200kv_decode_attn(const void* q, int64_t q_sb, int64_t q_sh, con
     attr_set[variant & 1] = true;
   }
   CacheView view = make_view(cache, table);
-  if (scalar)
-    decode_attn_kernel<true><<<grid, kWarps * 32, smem, s>>>((const uint16_t*)q, q_sb, q_sh, view, cached_lens, num_decoding,
-                                                            scale_log2, (uint16_t*)out, o_sb, o_sh, (uint8_t*)workspace, B,
-                                                            G, min_tiles, fused, status);
-  else
-    decode_attn_kernel<false><<<grid, kWarps * 32, smem, s>>>((const uint16_t*)q, q_sb, q_sh, view, cached_lens,
-                                                             num_decoding, scale_log2, (uint16_t*)out, o_sb, o_sh,
-                                                             (uint8_t*)workspace, B, G, min_tiles, fused, status);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(kWarps * 32);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = early ? 1 : 0;
+  cudaError_t le = cudaLaunchKernelEx(&cfg, scalar ? decode_attn_kernel<true> : decode_attn_kernel<false>,
+                                      (const uint16_t*)q, (long long)q_sb, (long long)q_sh, view, cached_lens, num_decoding,
+                                      scale_log2, (uint16_t*)out, (long long)o_sb, (long long)o_sh, (uint8_t*)workspace,
+                                      (int)B, G, min_tiles, fused, early, status);
+  if (le != cudaSuccess) return B200KV_E_LAUNCH;
   if (cudaGetLastError() != cudaSuccess) return B200KV_E_LAUNCH;
   if (fused) return B200KV_OK;
   decode_combine_kernel<<<dim3(B, Hkv), kD, 0, s>>>((const uint8_t*)workspace, num_decoding, (uint16_t*)out, o_sb, o_sh, B,

@@ -120,6 +120,9 @@ write_decode_kernel(const uint16_t* __restrict__ q, long long q_sb, long long q_
                     CacheView c, const int32_t* __restrict__ cached_lens, const int32_t* __restrict__ num_decoding,
                     uint16_t* __restrict__ q_out, long long o_sb, long long o_sh, int Hq, float eps, int32_t* status) {
   __shared__ __align__(16) float sq_all[kWarpsPerBlock][kD];
+  // A successor launched with programmatic stream serialization (decode attention's early start)
+  // may be scheduled now; it waits for this grid to finish before it reads the cache or q_out.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int b = blockIdx.x;
   if (b >= *num_decoding) return;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;

@@ -74,6 +74,19 @@ def check_status(device=None) -> int:
     return val
 
 
+_early_start = False
+
+
+def set_early_start(enabled: bool) -> None:
+    """Allow decode_attention's kernel to be scheduled while the kernel enqueued just before it is
+    still running (it reads only cached_lens, num_decoding and the block table before waiting for
+    that kernel).  Safe when the preceding kernel on the stream does not write those arrays, which
+    holds for the engine's decode path (fused_rope_kv_decode precedes decode_attention,
+    architecture.py:101-123).  Off by default."""
+    global _early_start
+    _early_start = bool(enabled)
+
+
 _workspaces: dict[tuple, torch.Tensor] = {}
 
 
@@ -166,7 +179,7 @@ def decode_attention(
     rc = lib.b200kv_decode_attn(
         q.data_ptr(), q.stride(0), q.stride(1), ctypes.byref(cs), ctypes.byref(ts), _i32(cached_lens),
         _i32(num_decoding), float(scale), out.data_ptr(), out.stride(0), out.stride(1), workspace.data_ptr(), workspace.numel(),
-        B, Hq, sms, variant, status_word(q.device).data_ptr(), _stream())
+        B, Hq, sms, variant | (4 if _early_start else 0), status_word(q.device).data_ptr(), _stream())
     _lib.check(rc, "decode_attention")
     return out
 

@@ -186,3 +186,44 @@ def test_repeated_calls_leave_the_workspace_reusable(K):
     counters = ws[: 4096].view(torch.int32)
     torch.cuda.synchronize()
     assert int(counters[64:128].abs().sum()) == 0  # the arrival counters follow the 256-byte prefix area
+
+
+def test_early_start_after_quantize_on_write(K):
+    """Decode attention launched with programmatic early start right behind the write kernel whose
+    new token it must see, several layers back to back on one stream: every layer's output must
+    equal the oracle's, i.e. the kernel really waited for the write before reading the cache."""
+    rng = np.random.default_rng(17)
+    lens = [257, 16, 1000, 64, 3]
+    B, P, layers = len(lens), 16, 4
+    pages = sum((n + P - 1) // P for n in lens) + 2
+    table = H.random_block_table(rng, lens, P, pages)
+    cached = np.array([n - 1 for n in lens], np.int32)
+    cos, sin = O.rope_tables(cached)
+    w = O.bf16_round((1 + 0.02 * rng.standard_normal(D)).astype(np.float32))
+    caches, dev_caches, qkvs, wants = [], [], [], []
+    for _ in range(layers):
+        cache = H.random_filled_cache(rng, pages, P, gauss=True)
+        dev_caches.append(H.cache_to_torch(cache))
+        qkv = H.randn_bf16(rng, B, (HQ + 2 * HKV) * D)
+        q, k, v = (qkv[:, : HQ * D].reshape(B, HQ, D), qkv[:, HQ * D : (HQ + HKV) * D].reshape(B, HKV, D),
+                   qkv[:, (HQ + HKV) * D :].reshape(B, HKV, D))
+        qr = O.write_decode(q, k, v, w, w, cos, sin, table, cache, cached, B, 1e-6)
+        wants.append(O.decode_attention(qr, cache, cached, table, B, SCALE))
+        qkvs.append(H.bf16_tensor(qkv))
+    tw, tcos, tsin = H.bf16_tensor(w), H.bf16_tensor(cos)[:, None, :], H.bf16_tensor(sin)[:, None, :]
+    ttab, tcl, tnd = H.i32(table), H.i32(cached), H.i32([B])
+    K.set_early_start(True)
+    try:
+        for rep in range(3):
+            outs = []
+            for l in range(layers):
+                tq, tk, tv = qkvs[l].split([HQ * D, HKV * D, HKV * D], dim=-1)
+                qr = K.fused_rope_kv_decode(tq.view(B, HQ, D), tk.view(B, HKV, D), tv.view(B, HKV, D), tw, tw, tcos, tsin,
+                                            ttab, dev_caches[l], tcl, tnd, 1e-6)
+                outs.append(K.decode_attention(qr, dev_caches[l], tcl, ttab, tnd, SCALE))
+            torch.cuda.synchronize()
+            for l in range(layers):
+                check(H.to_f32(outs[l]), wants[l])
+    finally:
+        K.set_early_start(False)
+    assert K.check_status() == 0
