@@ -222,11 +222,15 @@ def run_b200(args):
         for l in range(L):
             K.decode_attention(q_dev[l], caches[l], step.dev_cached, step.dev_table, step.dev_nd, D ** -0.5, out=attn_out[l])
 
+    # The roofline figure is for the kernel by itself: no early start here, or consecutive attention
+    # launches would overlap each other's tails and the per-launch time would flatter the kernel.
+    K.set_early_start(False)
     attn_only()
     torch.cuda.synchronize()
     attn_graph = torch.cuda.CUDAGraph()
     with torch.cuda.graph(attn_graph):
         attn_only()
+    K.set_early_start(not args.no_early_start)
 
     def barrier():
         if world > 1:

@@ -697,18 +697,25 @@ decode_attn_kernel(const uint16_t* __restrict__ q, long long q_sb, long long q_s
   PageWindow win{-1, 0, -1};
   const LaneCopy lc = make_lane_copy(c, lane);
 
-  // Early start: everything above read only the batch metadata.  The cache, q and the workspace
-  // may still be in flight from the kernel launched just before this one: wait for it here.
-  if (early) asm volatile("griddepcontrol.wait;" ::: "memory");
+  // Early start: everything above read only the batch metadata.  q, the workspace and the newest
+  // token of every sequence (the last tile) may still be in flight from the kernel launched just
+  // before this one (the quantize-on-write of this layer), so those wait for it; older tiles are
+  // not touched by it and are fetched right away, hiding the first burst behind that kernel.
+  bool must_wait = early != 0;
   int p_left = ntiles;  // tiles not yet issued
 #pragma unroll
   for (int i = 0; i < kStages - 1; ++i) {
     if (p_left > 0) {
+      if (must_wait && pc.tile == pc.T - 1) {
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        must_wait = false;
+      }
       issue_tile(c, pc, win, lc, my_ring_s + i * kTileBytes, lane, status);
       if (--p_left > 0) pc.next(lens, c.Hkv, c.page_size);
     }
     cp_async_commit();
   }
+  if (must_wait) asm volatile("griddepcontrol.wait;" ::: "memory");
 
   typename std::conditional<kScalar, ScalarState, MmaState>::type st;
   if constexpr (!kScalar) mma_init_lane(st, lane);
