@@ -602,49 +602,76 @@ __host__ __device__ inline size_t ws_prefix_bytes(int B) { return (((size_t)(B +
 __host__ __device__ inline size_t ws_count_bytes(int B, int Hkv) { return (((size_t)B * Hkv * 4 + 255) / 256) * 256; }
 __host__ __device__ inline size_t ws_head_bytes(int B, int Hkv) { return ws_prefix_bytes(B) + ws_count_bytes(B, Hkv); }
 
-// Merge the partials of one (entry, head) - the pieces written by workers w_first..w_last - and
-// write the final bf16 rows.  One warp; lane l owns channels 4l..4l+3.  Loads bypass L1 (the
-// partials were written by other SMs).
+// The pieces of one (entry, head) that reached the workspace, in tile order.  Its flat tile range
+// [s0, e) is covered by warps w_first..w_last; CTAs c_lo..c_hi-1 lie entirely inside it, each of
+// those summed its four pieces in shared memory and left ONE piece in the slot of its first warp.
+// So the list is: warps [w_first, kWarps*c_lo), then every kWarps-th warp up to kWarps*c_hi, then
+// warps [kWarps*c_hi, w_last].  A warp's piece is in its slot 1 only if it is w_first and the
+// (entry, head) starts inside that warp's range.
+struct Pieces {
+  int w_first, n_a, w_b, n_b, w_c, n, slot_first;
+  __device__ __forceinline__ Pieces(const Partition& part, int s0, int e) {
+    w_first = s0 / part.per;
+    const int w_last = (e - 1) / part.per;
+    const int span = kWarps * part.per;
+    const int c_lo = (s0 + span - 1) / span, c_hi = min(e, part.U) / span;
+    slot_first = s0 > w_first * part.per ? 1 : 0;
+    if (c_hi > c_lo) {
+      w_b = kWarps * c_lo; w_c = kWarps * c_hi;
+      n_a = w_b - w_first; n_b = c_hi - c_lo;
+      n = n_a + n_b + (w_last - w_c + 1);
+    } else {
+      w_b = w_c = w_first; n_a = 0; n_b = 0;
+      n = w_last - w_first + 1;
+    }
+  }
+  // workspace slot index (2 * warp + slot) of piece k
+  __device__ __forceinline__ int slot_of(int k) const {
+    const int w = k < n_a ? w_first + k : (k < n_a + n_b ? w_b + kWarps * (k - n_a) : w_c + (k - n_a - n_b));
+    return 2 * w + (w == w_first ? slot_first : 0);
+  }
+};
+
+// Merge the pieces of one (entry, head) and write the final bf16 rows.  One warp; lane l owns
+// channels 4l..4l+3.  Loads bypass L1 (the pieces were written by other SMs).  Sixteen pieces per
+// round: lane k fetches (m, l) of piece k while every lane fetches its channels of all sixteen in
+// the same round of memory latency (the loads are unconditional and independent; a padded slot
+// repeats the last piece and gets weight zero), then an online-softmax update folds the round in.
 __device__ __forceinline__ void merge_partials(const float* __restrict__ ws_ml, const float* __restrict__ ws_o,
-                                               int w_first, int w_last, int slot_first, int G,
-                                               uint16_t* __restrict__ out_row, long long o_sh, int lane) {
+                                               const Pieces& pc, int G, uint16_t* __restrict__ out_row, long long o_sh,
+                                               int lane) {
+  constexpr int kRound = 16;
   for (int col = 0; col < G; ++col) {
-    // pass 1: global maximum, lanes spread over the pieces
-    float M = -INFINITY;
-    for (int w = w_first + lane; w <= w_last; w += 32) {
-      const size_t base = ((size_t)w * 2 + (w == w_first ? slot_first : 0)) * G + col;
-      M = fmaxf(M, __ldcg(ws_ml + base * 2));
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
-    // pass 2, 32 pieces at a time: lane i turns piece i's (m, l) into a weight; then every lane
-    // sums its four channels over the batch - the loads do not depend on each other, so up to 8
-    // are in flight per lane
-    float Lsum = 0.f;
+    float M = -INFINITY, L = 0.f;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int w0 = w_first; w0 <= w_last; w0 += 32) {
-      const int nb = min(32, w_last - w0 + 1);
-      float wgt = 0.f;
-      if (lane < nb) {
-        const int w = w0 + lane;
-        const size_t base = ((size_t)w * 2 + (w == w_first ? slot_first : 0)) * G + col;
-        const float2 ml = __ldcg(reinterpret_cast<const float2*>(ws_ml + base * 2));
-        wgt = fast_exp2(ml.x - M);
-        Lsum = fmaf(ml.y, wgt, Lsum);
-      }
-#pragma unroll 8
-      for (int i = 0; i < nb; ++i) {
-        const int w = w0 + i;
-        const size_t base = ((size_t)w * 2 + (w == w_first ? slot_first : 0)) * G + col;
-        const float4 o = __ldcg(reinterpret_cast<const float4*>(ws_o + base * kD + 4 * lane));
-        const float wg = __shfl_sync(0xffffffffu, wgt, i);
-        acc.x = fmaf(o.x, wg, acc.x); acc.y = fmaf(o.y, wg, acc.y);
-        acc.z = fmaf(o.z, wg, acc.z); acc.w = fmaf(o.w, wg, acc.w);
-      }
-    }
+    for (int k0 = 0; k0 < pc.n; k0 += kRound) {
+      const int nb = min(kRound, pc.n - k0);
+      float2 ml = make_float2(-INFINITY, 0.f);
+      if (lane < nb) ml = __ldcg(reinterpret_cast<const float2*>(ws_ml + ((size_t)pc.slot_of(k0 + lane) * G + col) * 2));
+      float4 buf[kRound];
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) Lsum += __shfl_xor_sync(0xffffffffu, Lsum, o);
-    const float inv = 1.f / Lsum;
+      for (int j = 0; j < kRound; ++j)
+        buf[j] = __ldcg(reinterpret_cast<const float4*>(ws_o + ((size_t)pc.slot_of(k0 + min(j, nb - 1)) * G + col) * kD + 4 * lane));
+      float mb = ml.x;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) mb = fmaxf(mb, __shfl_xor_sync(0xffffffffu, mb, o));
+      const float M_new = fmaxf(M, mb);
+      const float resc = M == -INFINITY ? 0.f : fast_exp2(M - M_new);
+      const float wgt = lane < nb ? fast_exp2(ml.x - M_new) : 0.f;
+      float ls = ml.y * wgt;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) ls += __shfl_xor_sync(0xffffffffu, ls, o);
+      L = L * resc + ls;
+      acc.x *= resc; acc.y *= resc; acc.z *= resc; acc.w *= resc;
+#pragma unroll
+      for (int j = 0; j < kRound; ++j) {
+        const float wg = __shfl_sync(0xffffffffu, wgt, j);
+        acc.x = fmaf(buf[j].x, wg, acc.x); acc.y = fmaf(buf[j].y, wg, acc.y);
+        acc.z = fmaf(buf[j].z, wg, acc.z); acc.w = fmaf(buf[j].w, wg, acc.w);
+      }
+      M = M_new;
+    }
+    const float inv = 1.f / L;
     uint2 r;
     r.x = float_to_bf16_bits(acc.x * inv) | (float_to_bf16_bits(acc.y * inv) << 16);
     r.y = float_to_bf16_bits(acc.z * inv) | (float_to_bf16_bits(acc.w * inv) << 16);
@@ -669,6 +696,8 @@ decode_attn_kernel(const uint16_t* __restrict__ q, long long q_sb, long long q_s
   // to complete before it touches anything this grid writes).
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   int* lens_s = chunk_prefix + kWarps * 32 + 1;
+  int* cta_arrive = lens_s + kSmemLens;  // how many of this CTA's warps have parked a piece in shared memory
+  if (threadIdx.x == 0) *cta_arrive = 0;  // ordered before any use by the barriers inside scan_tiles
   const int nchunks = blockDim.x, chunk = (B + nchunks - 1) / nchunks;
   int nd;
   scan_tiles(cached_lens, B, num_decoding, chunk, chunk_prefix, lens_s,
@@ -746,24 +775,78 @@ decode_attn_kernel(const uint16_t* __restrict__ q, long long q_sb, long long q_s
     // whole iff the segment began at the sequence's first tile and reached its last one
     const bool whole = cc.tile == 0 && seg == cc.T;
     const int slot = done == 0 ? 0 : 1;
+    const int s0 = cc.base + cc.h * cc.T;  // flat tile range of this (entry, head): [s0, s0 + T)
+    uint16_t* out_row = out + cc.b * o_sb + (long long)(cc.h * G) * o_sh;
+    // Do all four warps of this CTA hold pieces of this same (entry, head)?  Then the pieces meet
+    // in shared memory and one warp forwards their sum (no global round trip for three of them).
+    const int cta_u0 = blockIdx.x * kWarps * part.per, cta_u1 = cta_u0 + kWarps * part.per;
+    const bool cta_inside = !whole && s0 <= cta_u0 && cta_u1 <= s0 + cc.T && cta_u1 <= part.U;
+    bool deliver = !whole;                       // a piece of mine (or my CTA's sum) goes to the workspace
     float* po = ws_o + ((size_t)w * 2 + slot) * G * kD;
     float* pml = ws_ml + ((size_t)w * 2 + slot) * G * 2;
-    if constexpr (kScalar) scalar_end(st, whole, out, o_sb, o_sh, cc.b, cc.h, G, po, pml, lane);
-    else mma_end(st, whole, out, o_sb, o_sh, cc.b, cc.h, G, po, pml, lane);
-    if (fused && !whole) {
+    if (cta_inside) {
+      cp_async_wait<0>();
+      __syncwarp();
+      float* so = reinterpret_cast<float*>(my_ring);  // [G][128] then [G][2]; the ring is idle now
+      if constexpr (kScalar) scalar_end(st, false, out, o_sb, o_sh, cc.b, cc.h, G, so, so + kMaxG * kD, lane);
+      else mma_end(st, false, out, o_sb, o_sh, cc.b, cc.h, G, so, so + kMaxG * kD, lane);
+      __threadfence_block();
+      __syncwarp();
+      int t = 0;
+      if (lane == 0) t = atomicAdd(cta_arrive, 1);
+      t = __shfl_sync(0xffffffffu, t, 0);
+      deliver = t == kWarps - 1;
+      if (deliver) {  // last of the four: sum them; lane l owns channels 4l..4l+3
+        __threadfence_block();
+        const bool exact = s0 == cta_u0 && s0 + cc.T == cta_u1;  // the CTA saw the whole sequence
+        po = ws_o + ((size_t)(blockIdx.x * kWarps) * 2) * G * kD;  // slot 0 of the CTA's first warp
+        pml = ws_ml + ((size_t)(blockIdx.x * kWarps) * 2) * G * 2;
+        for (int col = 0; col < G; ++col) {
+          float m4[kWarps], M = -INFINITY;
+#pragma unroll
+          for (int i = 0; i < kWarps; ++i) {
+            m4[i] = reinterpret_cast<const float*>(ring + i * kStages * kTileBytes)[kMaxG * kD + col * 2];
+            M = fmaxf(M, m4[i]);
+          }
+          float L = 0.f;
+          float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+          for (int i = 0; i < kWarps; ++i) {
+            const float* sp = reinterpret_cast<const float*>(ring + i * kStages * kTileBytes);
+            const float wg = fast_exp2(m4[i] - M);
+            L = fmaf(sp[kMaxG * kD + col * 2 + 1], wg, L);
+            const float4 o = *reinterpret_cast<const float4*>(sp + col * kD + 4 * lane);
+            a.x = fmaf(o.x, wg, a.x); a.y = fmaf(o.y, wg, a.y); a.z = fmaf(o.z, wg, a.z); a.w = fmaf(o.w, wg, a.w);
+          }
+          if (exact) {
+            const float inv = 1.f / L;
+            uint2 r;
+            r.x = float_to_bf16_bits(a.x * inv) | (float_to_bf16_bits(a.y * inv) << 16);
+            r.y = float_to_bf16_bits(a.z * inv) | (float_to_bf16_bits(a.w * inv) << 16);
+            *reinterpret_cast<uint2*>(out_row + col * o_sh + 4 * lane) = r;
+          } else {
+            *reinterpret_cast<float4*>(po + col * kD + 4 * lane) = a;
+            if (lane == 0) { pml[col * 2] = M; pml[col * 2 + 1] = L; }
+          }
+        }
+        if (exact) deliver = false;
+      }
+    } else {
+      if constexpr (kScalar) scalar_end(st, whole, out, o_sb, o_sh, cc.b, cc.h, G, po, pml, lane);
+      else mma_end(st, whole, out, o_sb, o_sh, cc.b, cc.h, G, po, pml, lane);
+    }
+    if (fused && deliver) {
       // Fused cross-split reduction: the warp that delivers the last piece of (entry, head) merges
       // all of them.  Release: partial stores -> fence -> counter; acquire: counter -> fence -> loads.
-      const int s0 = cc.base + cc.h * cc.T;  // flat index of this (entry, head)'s first tile
-      const int w_first = s0 / part.per, w_last = (s0 + cc.T - 1) / part.per;
+      const Pieces pieces(part, s0, s0 + cc.T);
       __threadfence();
       __syncwarp();
       int arrived = 0;
       if (lane == 0) arrived = atomicAdd(ws_count + cc.b * c.Hkv + cc.h, 1) + 1;
       arrived = __shfl_sync(0xffffffffu, arrived, 0);
-      if (arrived == w_last - w_first + 1) {
+      if (arrived == pieces.n) {
         __threadfence();
-        merge_partials(ws_ml, ws_o, w_first, w_last, s0 > w_first * part.per ? 1 : 0, G,
-                       out + cc.b * o_sb + (long long)(cc.h * G) * o_sh, o_sh, lane);
+        merge_partials(ws_ml, ws_o, pieces, G, out_row, o_sh, lane);
         if (lane == 0) ws_count[cc.b * c.Hkv + cc.h] = 0;  // leave the counter zero for the next call
       }
     }
@@ -797,20 +880,20 @@ decode_combine_kernel(const uint8_t* __restrict__ workspace, const int32_t* __re
   const int s = Hkv * prefix[b] + h * T, e = s + T;
   const int w_first = s / part.per, w_last = (e - 1) / part.per;
   if (w_first == w_last) return;  // one warp saw the whole sequence and wrote the output itself
+  const Pieces pieces(part, s, e);
+  if (pieces.n == 1) return;      // one CTA saw the whole sequence, summed its pieces and wrote the output
   const float* ws_ml = reinterpret_cast<const float*>(workspace + ws_head_bytes(B, Hkv));
   const float* ws_o = reinterpret_cast<const float*>(workspace + ws_head_bytes(B, Hkv) + ws_ml_bytes(W, G));
-  const int slot_first = s > w_first * part.per ? 1 : 0;
   const int warp = tid >> 5, lane = tid & 31;
 
   for (int col = 0; col < G; ++col) {
     float M = -INFINITY, L = 0.f;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int w0 = w_first; w0 <= w_last; w0 += kD) {
-      const int nb = min(kD, w_last - w0 + 1);
+    for (int k0 = 0; k0 < pieces.n; k0 += kD) {
+      const int nb = min(kD, pieces.n - k0);
       float m_i = -INFINITY, l_i = 0.f;
       if (tid < nb) {
-        const int w = w0 + tid;
-        const size_t base = ((size_t)w * 2 + (w == w_first ? slot_first : 0)) * G + col;
+        const size_t base = (size_t)pieces.slot_of(k0 + tid) * G + col;
         m_i = ws_ml[base * 2];
         l_i = ws_ml[base * 2 + 1];
       }
@@ -828,13 +911,12 @@ decode_combine_kernel(const uint8_t* __restrict__ workspace, const int32_t* __re
       for (int o = 16; o > 0; o >>= 1) ls += __shfl_xor_sync(0xffffffffu, ls, o);
       if (lane == 0) red_s[warp] = ls;
       __syncthreads();
-      const float rescale = fast_exp2(M - M_new);  // 0 on the first batch (M = -inf)
+      const float rescale = M == -INFINITY ? 0.f : fast_exp2(M - M_new);
       L = L * rescale + ((red_s[0] + red_s[1]) + (red_s[2] + red_s[3]));
       acc.x *= rescale; acc.y *= rescale; acc.z *= rescale; acc.w *= rescale;
 #pragma unroll 4
       for (int i = warp; i < nb; i += 4) {
-        const int w = w0 + i;
-        const size_t base = ((size_t)w * 2 + (w == w_first ? slot_first : 0)) * G + col;
+        const size_t base = (size_t)pieces.slot_of(k0 + i) * G + col;
         const float4 o = *reinterpret_cast<const float4*>(ws_o + base * kD + 4 * lane);
         const float wg = wgt_s[i];
         acc.x = fmaf(o.x, wg, acc.x); acc.y = fmaf(o.y, wg, acc.y);
@@ -854,7 +936,7 @@ decode_combine_kernel(const uint8_t* __restrict__ workspace, const int32_t* __re
 static size_t main_smem_bytes(int B, bool scalar) {
   size_t s = (size_t)kWarps * kStages * kTileBytes;
   if (scalar) s += (size_t)kWarps * (kMaxG * kD + kMaxG * kTile) * 4;
-  s += (size_t)(kWarps * 32 + 1 + kSmemLens) * 4;
+  s += (size_t)(kWarps * 32 + 1 + kSmemLens + 1) * 4;
   (void)B;
   return s;
 }
