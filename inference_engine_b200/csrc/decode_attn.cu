@@ -164,10 +164,15 @@ __device__ void scan_tiles(const int32_t* __restrict__ cached_lens, int B, const
   nd_out = nd;
 }
 
-__host__ __device__ __forceinline__ Partition make_partition(int total_tiles_one_head, int Hkv, int W, int min_tiles) {
+// `per` = tiles per warp.  Never below the even share; the floor below it trades parallelism against
+// hand-offs: a piece that goes through the workspace costs about as much as 8 tiles of work, so
+// short sequences (<= 32 tiles: a whole one fits a warp, or exactly a CTA of 4 x 8) use pieces of
+// 8 tiles, longer ones pieces of 4 (64 tokens, the reference's MIN_PIECE, kernels.py:295).
+__host__ __device__ __forceinline__ Partition make_partition(int total_tiles_one_head, int Hkv, int W, int num_entries) {
   Partition p;
   p.U = total_tiles_one_head * Hkv;
   p.W = W;
+  const int min_tiles = (num_entries > 0 && total_tiles_one_head <= 32 * num_entries) ? 8 : 4;
   int per = (p.U + W - 1) / W;
   p.per = per > min_tiles ? per : min_tiles;
   return p;
@@ -686,7 +691,7 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm)
 decode_attn_kernel(const uint16_t* __restrict__ q, long long q_sb, long long q_sh, CacheView c,
                    const int32_t* __restrict__ cached_lens, const int32_t* __restrict__ num_decoding, float scale_log2,
                    uint16_t* __restrict__ out, long long o_sb, long long o_sh, uint8_t* __restrict__ workspace, int B,
-                   int G, int min_tiles, int fused, int early, int32_t* status) {
+                   int G, int fused, int early, int32_t* status) {
   extern __shared__ __align__(128) uint8_t smem[];
   uint8_t* ring = smem;                                                       // kWarps * kStages * kTileBytes
   float* q_s = reinterpret_cast<float*>(ring + kWarps * kStages * kTileBytes);  // scalar variant: kWarps * (G*128 + G*16)
@@ -704,7 +709,7 @@ decode_attn_kernel(const uint16_t* __restrict__ q, long long q_sb, long long q_s
              (blockIdx.x == 0 && !fused) ? reinterpret_cast<int*>(workspace) : nullptr, nd);
   const Lens lens{cached_lens, lens_s, nd};
   const int W = gridDim.x * kWarps;
-  const Partition part = make_partition(chunk_prefix[nchunks], c.Hkv, W, min_tiles);
+  const Partition part = make_partition(chunk_prefix[nchunks], c.Hkv, W, nd);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int w = blockIdx.x * kWarps + warp;
@@ -866,8 +871,7 @@ decode_attn_kernel(const uint16_t* __restrict__ q, long long q_sb, long long q_s
 // of memory latency, not 64.
 __global__ void __launch_bounds__(kD)
 decode_combine_kernel(const uint8_t* __restrict__ workspace, const int32_t* __restrict__ num_decoding,
-                      uint16_t* __restrict__ out, long long o_sb, long long o_sh, int B, int Hkv, int G, int W,
-                      int min_tiles) {
+                      uint16_t* __restrict__ out, long long o_sb, long long o_sh, int B, int Hkv, int G, int W) {
   __shared__ float wgt_s[kD];
   __shared__ float red_s[4];
   __shared__ __align__(16) float acc_s[4][kD];
@@ -876,7 +880,7 @@ decode_combine_kernel(const uint8_t* __restrict__ workspace, const int32_t* __re
   const int* prefix = reinterpret_cast<const int*>(workspace);
   const int T = prefix[b + 1] - prefix[b];
   if (T == 0) return;
-  const Partition part = make_partition(prefix[B], Hkv, W, min_tiles);
+  const Partition part = make_partition(prefix[B], Hkv, W, min(*num_decoding, B));
   const int s = Hkv * prefix[b] + h * T, e = s + T;
   const int w_first = s / part.per, w_last = (e - 1) / part.per;
   if (w_first == w_last) return;  // one warp saw the whole sequence and wrote the output itself
@@ -970,7 +974,6 @@ extern "C" int b200kv_decode_attn(const void* q, int64_t q_sb, int64_t q_sh, con
   const int G = Hq / Hkv;
   const int grid = sm_count * kCtasPerSm;
   const int W = grid * kWarps;
-  const int min_tiles = 4;  // at least 64 tokens per partial, like the reference's MIN_PIECE (kernels.py:295)
   const float scale_log2 = scale * 1.4426950408889634f;
   cudaStream_t s = (cudaStream_t)stream;
   const bool scalar = (variant & 1) != 0;
@@ -998,12 +1001,12 @@ extern "C" int b200kv_decode_attn(const void* q, int64_t q_sb, int64_t q_sh, con
   cudaError_t le = cudaLaunchKernelEx(&cfg, scalar ? decode_attn_kernel<true> : decode_attn_kernel<false>,
                                       (const uint16_t*)q, (long long)q_sb, (long long)q_sh, view, cached_lens, num_decoding,
                                       scale_log2, (uint16_t*)out, (long long)o_sb, (long long)o_sh, (uint8_t*)workspace,
-                                      (int)B, G, min_tiles, fused, early, status);
+                                      (int)B, G, fused, early, status);
   if (le != cudaSuccess) return B200KV_E_LAUNCH;
   if (cudaGetLastError() != cudaSuccess) return B200KV_E_LAUNCH;
   if (fused) return B200KV_OK;
   decode_combine_kernel<<<dim3(B, Hkv), kD, 0, s>>>((const uint8_t*)workspace, num_decoding, (uint16_t*)out, o_sb, o_sh, B,
-                                                    Hkv, G, W, min_tiles);
+                                                    Hkv, G, W);
   return cudaGetLastError() == cudaSuccess ? B200KV_OK : B200KV_E_LAUNCH;
 }
 
