@@ -298,6 +298,119 @@ def run_b200(args):
         dist.destroy_process_group()
 
 
+def run_sharded(args):
+    """--sharded: the sequence-sharded decode config: `--seqs` concurrent sequences with contexts
+    drawn log-uniform in [512, 32768] (seed 4), partitioned over the ranks by KV bytes
+    (inference_engine_b200.sharding), one process per GPU, no collective on the data path.  Per
+    step every rank runs quantize-on-write + decode attention for its sequences over `--layers`
+    distinct layer caches (only as many layers as fit are kept resident: the full 28-layer cache of
+    2048 such sequences is ~940 GB).  Reports aggregate new tokens per second of the attention
+    path and each rank's attention bandwidth; one NCCL all_gather after the timed region checks
+    that every sequence was served exactly once."""
+    import torch
+    import torch.distributed as dist
+
+    from inference_engine_b200 import kernels as K
+    from inference_engine_b200.host_step import HostDecodeStep
+    from inference_engine_b200.sharding import gather_outputs, plan_shards
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    K.set_early_start(not args.no_early_start)
+    rng = np.random.default_rng(4)
+    lens_all = np.exp(rng.uniform(np.log(512), np.log(32768), args.seqs)).astype(np.int64)
+    plan = plan_shards(lens_all, world)
+    mine = plan.local[rank]
+    lens = lens_all[mine]
+    B, L = len(mine), args.layers
+    pages_per = (lens + PAGE - 1) // PAGE
+    num_pages = int(pages_per.sum()) + 1
+    max_pages = int(pages_per.max())
+    table_np = np.full((B, max_pages), 0, np.int32)
+    perm = np.random.default_rng(40 + rank).permutation(num_pages - 1).astype(np.int32)
+    at = 0
+    for i, k in enumerate(pages_per):
+        table_np[i, :k] = perm[at:at + k]
+        at += int(k)
+    gen = torch.Generator(device=dev).manual_seed(4 + rank)
+    caches = []
+    for _ in range(L):
+        c = K.make_layer_cache(num_pages, HKV, PAGE, D, device=dev)
+        c.k.copy_(torch.randint(-127, 128, c.k.shape, generator=gen, device=dev, dtype=torch.int8))
+        c.v.copy_(torch.randint(-127, 128, c.v.shape, generator=gen, device=dev, dtype=torch.int8))
+        c.k_scale.fill_(0.02)
+        c.v_scale.fill_(0.02)
+        caches.append(c)
+    W = (HQ + 2 * HKV) * D
+    qkv_h = torch.randn(L, B, W, generator=torch.Generator().manual_seed(14 + rank)).to(torch.bfloat16).pin_memory()
+    pos = torch.from_numpy((lens - 1).astype(np.int32))
+    inv_freq = 1e6 ** (-torch.arange(0, D, 2, dtype=torch.float32) / D)
+    ang = pos[:, None, None] * inv_freq[None, None, :]
+    cos_h, sin_h = ang.cos().to(torch.bfloat16).pin_memory(), ang.sin().to(torch.bfloat16).pin_memory()
+    cached_h, nd_h = pos.clone().pin_memory(), torch.tensor([B], dtype=torch.int32).pin_memory()
+    table_h = torch.from_numpy(table_np).pin_memory()
+    out_h = torch.empty(L, B, HQ, D, dtype=torch.bfloat16).pin_memory()
+    step = HostDecodeStep(caches, B, HQ, HKV, D, tuple(table_h.shape))
+    step.run_host(qkv_h, cos_h, sin_h, cached_h, table_h, nd_h, out_h)
+    torch.cuda.synchronize()
+    if K.check_status(dev):
+        raise SystemExit("device status word reports an inconsistent page table")
+    step.capture()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step.run_device()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step.run_device()
+    e1.record()
+    barrier()
+    my_ms = e0.elapsed_time(e1)
+    ms = my_ms
+    if world > 1:
+        t = torch.tensor([my_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    my_bytes = L * (int(lens.sum()) * CACHE_BYTES_PER_TOKEN + B * 8192 + B * WRITE_BYTES_PER_TOKEN)
+    my_gbs = my_bytes * args.steps / (my_ms * 1e-3) / 1e9
+    stats = torch.tensor([my_gbs, float(lens.sum()), float(B)], device=dev)
+    parts = [torch.zeros_like(stats) for _ in range(world)]
+    if world > 1:
+        dist.all_gather(parts, stats)
+    else:
+        parts = [stats]
+    # verification gather, off the timed path: one output row per sequence, every sequence exactly once
+    marker = torch.from_numpy(np.asarray(mine, dtype=np.int64)).to(dev).float()[:, None]
+    got = gather_outputs(marker, plan, rank)
+    ok = bool(torch.equal(got[:, 0].cpu(), torch.arange(args.seqs, dtype=torch.float32)))
+    peak, peak_kind = peaks()
+    if rank == 0:
+        per = [{"rank": r, "gbs": round(float(p[0]), 1), "frac_of_measured_peak": round(float(p[0]) / peak, 4),
+                "kv_tokens": int(p[1]), "sequences": int(p[2])} for r, p in enumerate(parts)]
+        print(json.dumps({
+            "metric": "sharded_decode_attention_tokens_per_s", "value": round(args.seqs * args.steps / (ms * 1e-3), 1),
+            "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": round(ms / args.steps, 4), "higher_is_better": True, "scaling": "strong",
+            "data": "synthetic", "config": {"workload": f"{args.seqs} sequences, contexts log-uniform [512, 32768] (seed 4), "
+                                                        f"sharded by KV bytes over {world} GPU(s), {L} resident layer caches per step "
+                                                        f"(attention path only: write + decode attention)",
+                                            "plan_imbalance": round(plan.imbalance(), 4)},
+            "aggregate_gbs": round(sum(p["gbs"] for p in per), 1), "per_gpu": per, "all_sequences_served_once": ok}))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def run_sweep(args):
     """--sweep: decode attention alone over the 45-cell grid B in {1..256} x ctx in {128..4096}
     (the 40 cells of the sweep config plus the 5 largest it drops), one JSON line per cell.
@@ -376,10 +489,14 @@ def main():
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--traffic", type=float, default=NCU_TRAFFIC_BYTES, help="ncu DRAM bytes per decode_attention call, if known")
     ap.add_argument("--no-early-start", action="store_true", help="launch decode attention without programmatic early start")
+    ap.add_argument("--sharded", action="store_true", help="sequence-sharded decode over log-uniform contexts (torchrun for N > 1)")
+    ap.add_argument("--seqs", type=int, default=2048, help="--sharded: concurrent sequences over all GPUs")
     ap.add_argument("--sweep", action="store_true", help="decode-attention shape sweep instead of the headline step")
     args = ap.parse_args()
     if args.sweep:
         run_sweep(args)
+    elif args.sharded:
+        run_sharded(args)
     elif args.impl == "reference":
         run_reference(args)
     else:
