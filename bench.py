@@ -411,6 +411,89 @@ def run_sharded(args):
         dist.destroy_process_group()
 
 
+def run_write(args):
+    """--write: the fused quantize-on-write microbench (seed 1): T in {1, 64, 1024} new tokens,
+    q [T,16,128], k,v [T,8,128] bf16 as strided views of one [T,4096] projection row, positions
+    uniform in [0,32768), per-head QK-RMSNorm (weights 1+N(0,0.02)) + RoPE(1e6) + int8 quantize
+    into a 16-token paged cache at random free slots.  Decode flavour (fused_rope_kv_decode, fp32
+    all the way) for every T, prefill flavour (norm+rope -> bf16 -> calibration -> quantize) for
+    T >= 64.  One JSON line per case: microseconds per call (CUDA graph of 20 calls on distinct
+    caches) and algorithmic GB/s at 14,656 B per token."""
+    import torch
+
+    from inference_engine_b200 import kernels as K
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    gen = torch.Generator(device=dev).manual_seed(1)
+    reps = 20
+    for T in (1, 64, 1024):
+        qkv = torch.randn(T, (HQ + 2 * HKV) * D, generator=gen, device=dev).to(torch.bfloat16)
+        q, k, v = qkv.split([HQ * D, HKV * D, HKV * D], dim=-1)
+        q, k, v = q.view(T, HQ, D), k.view(T, HKV, D), v.view(T, HKV, D)
+        qw = (1 + 0.02 * torch.randn(D, generator=gen, device=dev)).to(torch.bfloat16)
+        kw = (1 + 0.02 * torch.randn(D, generator=gen, device=dev)).to(torch.bfloat16)
+        pos = torch.randint(0, 32768, (T,), generator=gen, device=dev, dtype=torch.int32)
+        inv_freq = 1e6 ** (-torch.arange(0, D, 2, dtype=torch.float32, device=dev) / D)
+        ang = pos[:, None, None] * inv_freq[None, None, :]
+        cos, sin = ang.cos().to(torch.bfloat16), ang.sin().to(torch.bfloat16)
+        # every token is its own sequence at position pos: page 0 of its table holds the calibration row,
+        # the page of its position a random free slot
+        num_pages = 2 * T + 2
+        perm = torch.randperm(num_pages, generator=torch.Generator().manual_seed(1)).to(torch.int32)
+        table = torch.zeros(T, 32768 // PAGE, dtype=torch.int32)
+        rows = torch.arange(T)
+        table[rows, 0] = perm[2 * rows]
+        slot = (pos.cpu() // PAGE).long()
+        table[rows, slot] = torch.where(slot > 0, perm[2 * rows + 1], perm[2 * rows])
+        table = table.to(dev)
+        caches = [K.make_layer_cache(num_pages, HKV, PAGE, D, device=dev) for _ in range(reps)]
+        nd = torch.tensor([T], dtype=torch.int32, device=dev)
+
+        def timed(fn):
+            fn()
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                fn()
+            for _ in range(3):
+                g.replay()
+            torch.cuda.synchronize()
+            ts = []
+            for _ in range(args.steps):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                g.replay()
+                e1.record()
+                torch.cuda.synchronize()
+                ts.append(e0.elapsed_time(e1) * 1e3 / reps)
+            return statistics.median(ts)
+
+        def decode_flavour():
+            for c in caches:
+                K.fused_rope_kv_decode(q, k, v, qw, kw, cos, sin, table, c, pos, nd, 1e-6)
+
+        us = timed(decode_flavour)
+        print(json.dumps({"case": "fused_rope_kv_decode", "T": T, "us_per_call": round(us, 2),
+                          "gbs": round(T * WRITE_BYTES_PER_TOKEN / us / 1e3, 1), "kernels_per_call": 1}), flush=True)
+        if T >= 64:
+            # one prefill chunk of T tokens (first chunk: calibration is computed), written from position 0
+            cu = torch.tensor([0, T], dtype=torch.int32, device=dev)
+            tab1 = torch.arange(1, 1 + (T + PAGE - 1) // PAGE, dtype=torch.int32, device=dev)[None, :].contiguous()
+            zero = torch.zeros(1, dtype=torch.int32, device=dev)
+            pcaches = [K.make_layer_cache(2 + (T + PAGE - 1) // PAGE, HKV, PAGE, D, device=dev) for _ in range(reps)]
+
+            def prefill_flavour():
+                for c in pcaches:
+                    q_p, k_p = K.fused_norm_rope_prefill(q, k, qw, kw, cos, sin, 1e-6)
+                    K.quantize_kv_prefill(k_p, v, cu, tab1, zero, zero, c)
+
+            us = timed(prefill_flavour)
+            print(json.dumps({"case": "fused_norm_rope_prefill + quantize_kv_prefill (first chunk)", "T": T,
+                              "us_per_call": round(us, 2), "gbs": round(T * WRITE_BYTES_PER_TOKEN / us / 1e3, 1),
+                              "kernels_per_call": 4}), flush=True)
+
+
 def run_sweep(args):
     """--sweep: decode attention alone over the 45-cell grid B in {1..256} x ctx in {128..4096}
     (the 40 cells of the sweep config plus the 5 largest it drops), one JSON line per cell.
@@ -491,10 +574,13 @@ def main():
     ap.add_argument("--no-early-start", action="store_true", help="launch decode attention without programmatic early start")
     ap.add_argument("--sharded", action="store_true", help="sequence-sharded decode over log-uniform contexts (torchrun for N > 1)")
     ap.add_argument("--seqs", type=int, default=2048, help="--sharded: concurrent sequences over all GPUs")
+    ap.add_argument("--write", action="store_true", help="quantize-on-write microbench (T = 1, 64, 1024)")
     ap.add_argument("--sweep", action="store_true", help="decode-attention shape sweep instead of the headline step")
     args = ap.parse_args()
     if args.sweep:
         run_sweep(args)
+    elif args.write:
+        run_write(args)
     elif args.sharded:
         run_sharded(args)
     elif args.impl == "reference":
