@@ -411,6 +411,92 @@ def run_sharded(args):
         dist.destroy_process_group()
 
 
+def run_mixed(args):
+    """--mixed: one chunked-prefill + decode step (seed 3) inside a random-init Qwen3-1.7B-shaped
+    decoder (28 layers, hidden 2048, FFN 6144, vocab 151936, tied embeddings, weights ~N(0,0.02)):
+    32 decoding sequences (contexts ~U[128,4096]) + one 992-token chunk on a prior context of
+    0/1024/2048/3072 tokens = 1024 tokens per step, int8 paged cache (16-token pages, random block
+    table).  The step is captured as one CUDA graph (embedding -> 28 layers -> final norm -> tied
+    lm_head -> argmax) and replayed; a second graph holds only the attention-path ops of the 28
+    layers on the same metadata, to state their share of the step.  One JSON line per prior."""
+    import torch
+
+    from inference_engine_b200 import kernels as K
+    from inference_engine_b200 import scaffold as S
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    gen = torch.Generator().manual_seed(3)
+    model = S.DecoderScaffold(dev, seed=3)
+    n_dec, chunk, n_tokens = 32, 992, 1024
+    entries = n_dec + 2
+    ctx = torch.randint(128, 4097, (n_dec,), generator=gen).tolist()
+    max_pages = (4096 + PAGE) // PAGE + 1
+    for prior in (0, 1024, 2048, 3072):
+        plan = S.plan_step(ctx, [(prior, chunk)], n_tokens, entries)
+        table, pages = S.assign_pages(plan, PAGE, max_pages, generator=gen)
+        ids = torch.randint(0, S.VOCAB, (n_tokens,), generator=gen).tolist()
+        inp = S.upload_step(plan, table, ids, dev)
+        dgen = torch.Generator(device=dev).manual_seed(3)
+        caches = []
+        for _ in range(S.LAYERS):
+            c = K.make_layer_cache(pages, HKV, PAGE, D, device=dev)
+            c.k.copy_(torch.randint(-127, 128, c.k.shape, generator=dgen, device=dev, dtype=torch.int8))
+            c.v.copy_(torch.randint(-127, 128, c.v.shape, generator=dgen, device=dev, dtype=torch.int8))
+            c.k_scale.uniform_(0.01, 0.04, generator=dgen)
+            c.v_scale.uniform_(0.01, 0.04, generator=dgen)
+            caches.append(c)
+        cap = max(prior, 16)
+        prefix = S.PrefixScratch(torch.empty(HKV, cap, D, device=dev, dtype=torch.bfloat16),
+                                 torch.empty(HKV, cap, D, device=dev, dtype=torch.bfloat16), inp.cu_cached)
+
+        def step():
+            return model.forward(caches, inp, inp.ids, inp.cached_lens, inp.block_table, inp.num_decoding, prefix)
+
+        qkv = torch.randn(n_tokens, (HQ + 2 * HKV) * D, generator=dgen, device=dev).to(torch.bfloat16)
+        q, k, v = qkv.split([HQ * D, HKV * D, HKV * D], dim=-1)
+        q, k, v = q.view(-1, HQ, D), k.view(-1, HKV, D), v.view(-1, HKV, D)
+        cos, sin = model.rope(inp.positions)
+
+        def star_only():
+            for L, c in zip(model.layers, caches):
+                S.attention_ops(q, k, v, L["qn"], L["kn"], cos, sin, c, inp, inp.cached_lens, inp.block_table,
+                                inp.num_decoding, prefix)
+
+        def graph_ms(fn):
+            with torch.inference_mode():
+                fn()
+                fn()
+                torch.cuda.synchronize()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    res = fn()
+            for _ in range(max(args.warmup, 3)):
+                g.replay()
+            torch.cuda.synchronize()
+            ts = []
+            for _ in range(args.steps):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                g.replay()
+                e1.record()
+                torch.cuda.synchronize()
+                ts.append(e0.elapsed_time(e1))
+            return statistics.median(ts), res
+
+        step_ms, toks = graph_ms(step)
+        star_ms, _ = graph_ms(star_only)
+        status = K.check_status(dev)
+        print(json.dumps({
+            "case": "mixed step: 32 decode (ctx~U[128,4096]) + 992-token chunk", "prior_context": prior,
+            "tokens_per_step": n_tokens, "step_ms": round(step_ms, 3), "tokens_per_s": round(n_tokens / step_ms * 1e3),
+            "attention_path_ms": round(star_ms, 3), "attention_path_share": round(star_ms / step_ms, 3),
+            "decode_kv_tokens": sum(ctx) + n_dec, "status": status, "sampled_head": toks[:4].tolist(),
+            "data": "synthetic ids, random-init weights"}), flush=True)
+        del caches, prefix
+        torch.cuda.empty_cache()
+
+
 def run_write(args):
     """--write: the fused quantize-on-write microbench (seed 1): T in {1, 64, 1024} new tokens,
     q [T,16,128], k,v [T,8,128] bf16 as strided views of one [T,4096] projection row, positions
@@ -574,6 +660,7 @@ def main():
     ap.add_argument("--no-early-start", action="store_true", help="launch decode attention without programmatic early start")
     ap.add_argument("--sharded", action="store_true", help="sequence-sharded decode over log-uniform contexts (torchrun for N > 1)")
     ap.add_argument("--seqs", type=int, default=2048, help="--sharded: concurrent sequences over all GPUs")
+    ap.add_argument("--mixed", action="store_true", help="chunked-prefill + decode step inside the decoder scaffold")
     ap.add_argument("--write", action="store_true", help="quantize-on-write microbench (T = 1, 64, 1024)")
     ap.add_argument("--sweep", action="store_true", help="decode-attention shape sweep instead of the headline step")
     args = ap.parse_args()
@@ -581,6 +668,8 @@ def main():
         run_sweep(args)
     elif args.write:
         run_write(args)
+    elif args.mixed:
+        run_mixed(args)
     elif args.sharded:
         run_sharded(args)
     elif args.impl == "reference":
