@@ -411,6 +411,61 @@ def run_sharded(args):
         dist.destroy_process_group()
 
 
+def run_prefill(args):
+    """--prefill: the chunked-prefill attention kernel alone (seed 3 shapes): one 992-row chunk on a
+    prior context of 0/1024/2048/3072 tokens, 16 q heads over 8 kv heads, block_m 128, bf16 ~N(0,1).
+    Both kernels (1 = mma.sync, 2 = tcgen05), CUDA graph of 10 calls, median of `steps` replays.
+    FLOPs counted: 4 * D * visible (query, key) pairs * q heads (causal pairs, not padded tiles)."""
+    import torch
+
+    from inference_engine_b200 import kernels as K
+    from inference_engine_b200 import scaffold as S
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    gen = torch.Generator(device=dev).manual_seed(3)
+    chunk, reps = 992, 10
+    for prior in (0, 1024, 2048, 3072):
+        plan = S.plan_step([], [(prior, chunk)], chunk, 2)
+        table, _ = S.assign_pages(plan, PAGE, (prior + chunk) // PAGE + 1)
+        inp = S.upload_step(plan, table, [0] * chunk, dev)
+        qkv = torch.randn(chunk, (HQ + 2 * HKV) * D, generator=gen, device=dev).to(torch.bfloat16)
+        q, k, v = qkv.split([HQ * D, HKV * D, HKV * D], dim=-1)
+        q, k, v = q.view(-1, HQ, D), k.view(-1, HKV, D), v.view(-1, HKV, D)
+        kp = torch.randn(HKV, max(prior, 16), D, generator=gen, device=dev).to(torch.bfloat16)
+        vp = torch.randn(HKV, max(prior, 16), D, generator=gen, device=dev).to(torch.bfloat16)
+        pairs = chunk * prior + chunk * (chunk + 1) // 2
+        flops = 4.0 * D * pairs * HQ
+        outs = {}
+        for variant in (1, 2):
+            def call():
+                for _ in range(reps):
+                    outs[variant] = K.prefill_attention(q, k, v, inp.seq_ids, inp.cu_seqlens, inp.tile_start, kp, vp,
+                                                        inp.cu_cached, 128, variant=variant)
+            call()
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                call()
+            for _ in range(3):
+                g.replay()
+            torch.cuda.synchronize()
+            ts = []
+            for _ in range(args.steps):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                g.replay()
+                e1.record()
+                torch.cuda.synchronize()
+                ts.append(e0.elapsed_time(e1) * 1e3 / reps)
+            us = statistics.median(ts)
+            print(json.dumps({"case": "prefill_attention", "kernel": {1: "mma.sync", 2: "tcgen05"}[variant],
+                              "chunk": chunk, "prior_context": prior, "us_per_call": round(us, 1),
+                              "tflops": round(flops / us / 1e6, 1), "status": K.check_status(dev)}), flush=True)
+        diff = (outs[1].float() - outs[2].float()).abs().max().item()
+        print(json.dumps({"case": "prefill_attention", "prior_context": prior, "max_abs_diff_between_kernels": diff}), flush=True)
+
+
 def run_mixed(args):
     """--mixed: one chunked-prefill + decode step (seed 3) inside a random-init Qwen3-1.7B-shaped
     decoder (28 layers, hidden 2048, FFN 6144, vocab 151936, tied embeddings, weights ~N(0,0.02)):
@@ -660,6 +715,7 @@ def main():
     ap.add_argument("--no-early-start", action="store_true", help="launch decode attention without programmatic early start")
     ap.add_argument("--sharded", action="store_true", help="sequence-sharded decode over log-uniform contexts (torchrun for N > 1)")
     ap.add_argument("--seqs", type=int, default=2048, help="--sharded: concurrent sequences over all GPUs")
+    ap.add_argument("--prefill", action="store_true", help="chunked-prefill attention kernel alone, both kernels")
     ap.add_argument("--mixed", action="store_true", help="chunked-prefill + decode step inside the decoder scaffold")
     ap.add_argument("--write", action="store_true", help="quantize-on-write microbench (T = 1, 64, 1024)")
     ap.add_argument("--sweep", action="store_true", help="decode-attention shape sweep instead of the headline step")
@@ -670,6 +726,8 @@ def main():
         run_write(args)
     elif args.mixed:
         run_mixed(args)
+    elif args.prefill:
+        run_prefill(args)
     elif args.sharded:
         run_sharded(args)
     elif args.impl == "reference":

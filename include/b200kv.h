@@ -53,7 +53,8 @@ enum {
 /* Bits OR-ed into the optional device status word. */
 enum {
   B200KV_S_BAD_PAGE = 1,    /* block-table entry outside [0, num_pages) */
-  B200KV_S_BAD_POSITION = 2 /* token position outside the entry's table (>= max_pages*page_size) */
+  B200KV_S_BAD_POSITION = 2, /* token position outside the entry's table (>= max_pages*page_size) */
+  B200KV_S_TIMEOUT = 4       /* a bounded wait inside a kernel ran out; that CTA's output rows are not written */
 };
 
 /* One layer's cache, by value.  Mirrors LayerKVCache (kernels.py:11-17). */
@@ -146,6 +147,22 @@ int b200kv_prefill_attn(const void* q, int64_t q_stride_n, int64_t q_stride_h,
                         const int32_t* cu_cached,
                         void* out, int64_t o_stride_n, int64_t o_stride_h,
                         int32_t N, int32_t Hq, int32_t Hkv, int32_t D, void* stream);
+
+/* The same operation with the kernel chosen by the caller and an optional status word.
+ * variant 0 = automatic (what b200kv_prefill_attn does: the tcgen05 kernel when block_m >= 64,
+ * else the mma.sync kernel), 1 = the mma.sync kernel (64-row CTAs, register accumulators),
+ * 2 = the tcgen05 kernel (128-row CTAs, accumulators in tensor memory).  Both give results within
+ * the attention tolerance of each other; they differ in summation order. */
+int b200kv_prefill_attn_variant(const void* q, int64_t q_stride_n, int64_t q_stride_h,
+                                const void* k, int64_t k_stride_n, int64_t k_stride_h,
+                                const void* v, int64_t v_stride_n, int64_t v_stride_h,
+                                const int32_t* seq_ids, const int32_t* cu_seqlens, const int32_t* tile_start,
+                                int32_t num_tiles, int32_t block_m,
+                                const void* k_prefix, const void* v_prefix, int64_t p_stride_h, int64_t p_stride_n,
+                                const int32_t* cu_cached,
+                                void* out, int64_t o_stride_n, int64_t o_stride_h,
+                                int32_t N, int32_t Hq, int32_t Hkv, int32_t D,
+                                int32_t variant, int32_t* status, void* stream);
 
 /* Bytes of fp32 workspace b200kv_decode_attn needs for a batch of B entries on a device with
  * `sm_count` SMs (replaces the three partial buffers of kernels.py:305-311).

@@ -27,6 +27,7 @@ UNITS = {
     "write_kernels.cu": ["-fmad=false"],
     "decode_attn.cu": [],
     "prefill_attn.cu": [],
+    "prefill_attn_tc5.cu": [],
     "host_step.cu": [],
 }
 

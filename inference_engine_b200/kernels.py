@@ -310,6 +310,8 @@ def prefill_attention(
     v_prefix: torch.Tensor,
     cu_cached: torch.Tensor,  # [B + 1] int32
     PREFILL_BLOCK_M: int,
+    *,
+    variant: int = 0,  # 0 = automatic, 1 = mma.sync kernel, 2 = tcgen05 kernel (not a reference argument)
 ) -> torch.Tensor:
     _require_cuda(q, k, v)
     lib = _lib.load()
@@ -318,11 +320,12 @@ def prefill_attention(
     assert q.stride(-1) == 1 and k.stride(-1) == 1 and v.stride(-1) == 1
     assert k_prefix.stride() == v_prefix.stride() and k_prefix.stride(-1) == 1
     out = torch.empty(N, Hq, D, device=q.device, dtype=q.dtype)
-    rc = lib.b200kv_prefill_attn(
+    rc = lib.b200kv_prefill_attn_variant(
         q.data_ptr(), q.stride(0), q.stride(1), k.data_ptr(), k.stride(0), k.stride(1), v.data_ptr(), v.stride(0),
         v.stride(1), _i32(seq_ids), _i32(cu_seqlens), _i32(tile_start), tile_start.shape[0], int(PREFILL_BLOCK_M),
         k_prefix.data_ptr(), v_prefix.data_ptr(), k_prefix.stride(0), k_prefix.stride(1), _i32(cu_cached),
-        out.data_ptr(), out.stride(0), out.stride(1), N, Hq, Hkv, D, _stream())
+        out.data_ptr(), out.stride(0), out.stride(1), N, Hq, Hkv, D, int(variant),
+        status_word(q.device).data_ptr(), _stream())
     _lib.check(rc, "prefill_attention")
     return out
 

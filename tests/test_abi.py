@@ -19,7 +19,8 @@ def declared_functions():
 def test_header_declares_the_path():
     names = declared_functions()
     for must in ("b200kv_write_decode", "b200kv_decode_attn", "b200kv_decode_attn_workspace_bytes",
-                 "b200kv_norm_rope_prefill", "b200kv_quantize_prefill", "b200kv_dequant_prefix", "b200kv_prefill_attn"):
+                 "b200kv_norm_rope_prefill", "b200kv_quantize_prefill", "b200kv_dequant_prefix", "b200kv_prefill_attn",
+                 "b200kv_prefill_attn_variant"):
         assert must in names
 
 
