@@ -3,39 +3,50 @@
 // attention of the prefilling entries over [dequantized prefix | own chunk], replacing
 // prefill_attention_kernel (qwen3-1.7b/kernels.py:987-1126).
 //
-// One CTA of 128 threads owns 128 query rows of one q head.  Thread t owns row t, which is lane
-// t of tensor memory, so every row-wise softmax quantity lives in one thread and needs no
-// shuffle.  Per block of 128 keys:
+// One CTA owns 128 query rows of one q head and runs two warpgroups of 128 threads.  The key
+// blocks (128 keys each) of the tile are dealt alternately to the two warpgroups; each keeps its
+// own running (max, sum, O) and the two are merged at the end, so while one warpgroup is in its
+// softmax the tensor core works for the other.  Inside a warpgroup, thread t owns query row t =
+// lane t of tensor memory: every row-wise softmax quantity lives in one thread, no shuffles.
+// Per key block of a warpgroup:
 //   S = Q K^T     8 x tcgen05.mma (M128 N128 K16, bf16 -> fp32), Q and K from shared memory,
-//                 S in tensor memory columns [0,128)
-//   softmax       two passes of tcgen05.ld over the thread's row (max, then exp2 / sum);
-//                 P is rounded to bf16 exactly as the reference does (kernels.py:1068,1113)
-//                 and stored back into tensor memory over the columns of S it has consumed
-//   PV = P V      8 x tcgen05.mma with P read from tensor memory and V from shared memory
-//                 (channel-contiguous, i.e. N-major B operand), into columns [128,256)
-//   O = O*a + PV  in fp32 registers (one row of 128 channels per thread)
+//                 S in the warpgroup's tensor-memory columns [0,128)
+//   softmax       one tcgen05.ld of the thread's 128 scores, max, exp2, sum; P rounded to bf16 as
+//                 the reference does (kernels.py:1068,1113) and stored over the first 64 columns of S
+//   O += P V      8 x tcgen05.mma with P read from tensor memory and V from shared memory
+//                 (channel-contiguous: N-major B operand), accumulating in columns [128,256)
+// O stays in tensor memory for the whole tile.  Its rescaling is lazy: the reference offset of the
+// exponentials only moves when the row maximum has grown by more than 2^8 since it was set (then O
+// and the sum are multiplied by the correction, a tensor-memory round trip); otherwise P is simply
+// computed against the older offset, which is the same mathematics.  The product S of the next
+// block is issued right behind P V of this one, so the tensor core never waits for the softmax
+// threads of its own warpgroup to come back.
+//
 // Q, K and V tiles are laid out in shared memory as the canonical 128-byte-swizzled layout the
 // matrix descriptors name: two blocks of 64 channels, each [row][128 bytes] with the 16-byte
 // chunk index XOR-ed with (row & 7).  K and V use the same physical layout; only their
-// descriptors differ (K: K-major, rows = N; V: N-major, rows = K).  Tiles are filled with
-// cp.async; K is refilled as soon as S is complete and V as soon as PV is complete, so the loads
-// of the next block run under the softmax of this one.  Two CTAs fit one SM (96 KB of shared
-// memory and 256 of the 512 tensor-memory columns each), so one CTA's softmax overlaps the
-// other's matrix products.
+// descriptors differ (K: K-major, rows = N; V: N-major, rows = K).  Each warpgroup fills its own
+// tiles with cp.async (two K buffers, one V buffer; rows past the visible range are zero-filled,
+// so uninitialised memory behind a prefix never reaches the tensor core): K two blocks ahead as
+// soon as S of this block is complete, V of the next block as soon as P V of this one is.
 //
-// Every wait on an mbarrier is bounded: if a completion never arrives the CTA records
-// B200KV_S_TIMEOUT in the status word, stops issuing work, frees its tensor memory and returns.
+// Every wait on an mbarrier is bounded: if a completion never arrives the warpgroup records
+// B200KV_S_TIMEOUT in the status word, stops issuing work and skips its stores; the CTA still
+// frees its tensor memory and returns.
 #include "common.cuh"
+#include "tmem_ldst.cuh"
 
 namespace b200kv {
 
-constexpr int kT5Threads = 128;
+constexpr int kT5Threads = 256;
 constexpr int kT5Tile = 128;                        // query rows per CTA = keys per block
 constexpr uint32_t kT5TileBytes = kT5Tile * kD * 2; // 32 KB
 constexpr uint32_t kT5BlockBytes = kT5Tile * 128;   // one 64-channel block of a tile: 16 KB
-constexpr uint32_t kT5Smem = 3 * kT5TileBytes + 1024 /* alignment slack */ + 64 /* barriers, tmem slot */;
-constexpr uint32_t kT5Cols = 256;                   // tensor-memory columns: S/P [0,128), PV [128,256)
+constexpr uint32_t kT5WgBytes = 3 * kT5TileBytes;   // per warpgroup: K0, K1, V
+constexpr uint32_t kT5Smem = kT5TileBytes + 2 * kT5WgBytes + 1024 /* alignment slack */ + 64 /* barriers, flags */;
+constexpr uint32_t kT5Cols = 512;                   // tensor memory: warpgroup w has S/P at 256w, O at 256w+128
 constexpr uint32_t kT5SpinLimit = 1u << 20;
+constexpr float kT5Lazy = 8.f;                      // log2 of the growth of the row maximum that forces a rescale
 
 __device__ __forceinline__ uint32_t t5_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void t5_cp16(uint32_t dst, const void* src, int bytes) {
@@ -93,29 +104,6 @@ __device__ __forceinline__ void t5_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint
       ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(acc) : "memory");
 }
 
-// This thread's lane, 32 consecutive columns starting at taddr's column.
-__device__ __forceinline__ void t5_ld32(uint32_t taddr, float (&r)[32]) {
-  uint32_t u[32];
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
-      : "=r"(u[0]), "=r"(u[1]), "=r"(u[2]), "=r"(u[3]), "=r"(u[4]), "=r"(u[5]), "=r"(u[6]), "=r"(u[7]), "=r"(u[8]),
-        "=r"(u[9]), "=r"(u[10]), "=r"(u[11]), "=r"(u[12]), "=r"(u[13]), "=r"(u[14]), "=r"(u[15]), "=r"(u[16]),
-        "=r"(u[17]), "=r"(u[18]), "=r"(u[19]), "=r"(u[20]), "=r"(u[21]), "=r"(u[22]), "=r"(u[23]), "=r"(u[24]),
-        "=r"(u[25]), "=r"(u[26]), "=r"(u[27]), "=r"(u[28]), "=r"(u[29]), "=r"(u[30]), "=r"(u[31])
-      : "r"(taddr) : "memory");
-  asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-#pragma unroll
-  for (int i = 0; i < 32; ++i) r[i] = __uint_as_float(u[i]);
-}
-__device__ __forceinline__ void t5_st16(uint32_t taddr, const uint32_t (&u)[16]) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
-      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};\n"
-      ::"r"(taddr), "r"(u[0]), "r"(u[1]), "r"(u[2]), "r"(u[3]), "r"(u[4]), "r"(u[5]), "r"(u[6]), "r"(u[7]), "r"(u[8]),
-        "r"(u[9]), "r"(u[10]), "r"(u[11]), "r"(u[12]), "r"(u[13]), "r"(u[14]), "r"(u[15]) : "memory");
-}
 __device__ __forceinline__ float t5_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
@@ -127,19 +115,23 @@ __device__ __forceinline__ uint32_t t5_pack_bf16x2(float lo, float hi) {
   return r;
 }
 
-// `count` (<= 128) rows of 128 bf16 (row j at src + j*stride elements) into a swizzled tile; rows past
+// Copied by kThreads threads (tid in [0, kThreads)): `count` (<= 128) rows of 128 bf16 (row j at src + j*stride elements) into a swizzled tile; rows past
 // `count` are zero-filled.
+template <int kThreads>
 __device__ __forceinline__ void t5_load_tile(uint32_t dst, const uint16_t* src, long long stride, int count, int tid) {
 #pragma unroll
-  for (int i = 0; i < (kT5Tile * 16) / kT5Threads; ++i) {
-    const int c = tid + i * kT5Threads, r = c >> 4, col = c & 15;
+  for (int i = 0; i < (kT5Tile * 16) / kThreads; ++i) {
+    const int c = tid + i * kThreads, r = c >> 4, col = c & 15;
     const bool valid = r < count;
     const uint32_t d = dst + (col >> 3) * kT5BlockBytes + r * 128 + (((col & 7) ^ (r & 7)) << 4);
     t5_cp16(d, valid ? src + r * stride + col * 8 : src, valid ? 16 : 0);
   }
 }
 
-__global__ void __launch_bounds__(kT5Threads, 2)
+
+__device__ __forceinline__ void t5_wg_sync(int wg) { asm volatile("bar.sync %0, 128;\n" ::"r"(wg + 1) : "memory"); }
+
+__global__ void __launch_bounds__(kT5Threads, 1)
 prefill_attn_tc5_kernel(const uint16_t* __restrict__ q, long long q_sn, long long q_sh, const uint16_t* __restrict__ k,
                         long long k_sn, long long k_sh, const uint16_t* __restrict__ v, long long v_sn, long long v_sh,
                         const int32_t* __restrict__ seq_ids, const int32_t* __restrict__ cu_seqlens,
@@ -163,17 +155,22 @@ prefill_attn_tc5_kernel(const uint16_t* __restrict__ q, long long q_sn, long lon
   const int nb_pre = (prefix_len + kT5Tile - 1) / kT5Tile, nb_own = (own_keys + kT5Tile - 1) / kT5Tile;
   const int nb = nb_pre + nb_own;
 
-  const int tid = threadIdx.x, warp = tid >> 5;
+  const int tid = threadIdx.x, wg = tid >> 7, wt = tid & 127;
+  const int n_mine = (nb - wg + 1) >> 1;  // this warpgroup's blocks: wg, wg + 2, ...
   const uint32_t base = (t5_smem_u32(t5_raw) + 1023u) & ~1023u;
-  const uint32_t sQ = base, sK = base + kT5TileBytes, sV = base + 2 * kT5TileBytes;
-  const uint32_t bar_s = base + 3 * kT5TileBytes, bar_o = bar_s + 8, slot = bar_s + 16;
+  const uint32_t sQ = base;
+  const uint32_t sK = base + kT5TileBytes + wg * kT5WgBytes;  // K buffers at sK and sK + 32 KB
+  const uint32_t sV = sK + 2 * kT5TileBytes;
+  const uint32_t bars = base + kT5TileBytes + 2 * kT5WgBytes;
+  const uint32_t bar_s = bars + wg * 16, bar_o = bar_s + 8, slot = bars + 32, dead_flag = bars + 40 + wg * 4;
 
   if (tid == 0) {
-    t5_mbar_init(bar_s, 1);
-    t5_mbar_init(bar_o, 1);
+    for (int i = 0; i < 4; ++i) t5_mbar_init(bars + 8 * i, 1);
+    asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(bars + 40), "r"(0) : "memory");
+    asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(bars + 44), "r"(0) : "memory");
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
-  if (warp == 0) {
+  if (tid < 32) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(slot), "r"(kT5Cols) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
   }
@@ -182,146 +179,220 @@ prefill_attn_tc5_kernel(const uint16_t* __restrict__ q, long long q_sn, long lon
   const uint16_t* vpre = v_prefix + hk * p_sh + (long long)prefix_start * p_sn;
   const uint16_t* kown = k + (long long)seq_start * k_sn + hk * k_sh;
   const uint16_t* vown = v + (long long)seq_start * v_sn + hk * v_sh;
-  auto load_keys = [&](uint32_t dst, int kb, bool is_v) {
+  // this warpgroup's i-th block is block wg + 2i of the tile
+  auto load_keys = [&](uint32_t dst, int i, bool is_v) {
+    const int kb = wg + 2 * i;
     if (kb < nb_pre) {
       const int j0 = kb * kT5Tile;
-      t5_load_tile(dst, (is_v ? vpre : kpre) + (long long)j0 * p_sn, p_sn, min(kT5Tile, prefix_len - j0), tid);
+      t5_load_tile<128>(dst, (is_v ? vpre : kpre) + (long long)j0 * p_sn, p_sn, min(kT5Tile, prefix_len - j0), wt);
     } else {
       const int j0 = (kb - nb_pre) * kT5Tile;
-      if (is_v) t5_load_tile(dst, vown + (long long)j0 * v_sn, v_sn, min(kT5Tile, own_keys - j0), tid);
-      else      t5_load_tile(dst, kown + (long long)j0 * k_sn, k_sn, min(kT5Tile, own_keys - j0), tid);
+      if (is_v) t5_load_tile<128>(dst, vown + (long long)j0 * v_sn, v_sn, min(kT5Tile, own_keys - j0), wt);
+      else      t5_load_tile<128>(dst, kown + (long long)j0 * k_sn, k_sn, min(kT5Tile, own_keys - j0), wt);
     }
   };
   // Q rows past the end of the packed batch are zero-filled; rows of other entries inside the tile are
   // read and computed but never stored.
-  t5_load_tile(sQ, q + (long long)row0 * q_sn + hq * q_sh, q_sn, min(kT5Tile, N - row0), tid);
-  load_keys(sK, 0, false);
+  t5_load_tile<256>(sQ, q + (long long)row0 * q_sn + hq * q_sh, q_sn, min(kT5Tile, N - row0), tid);
+  if (n_mine > 0) { load_keys(sK, 0, false); load_keys(sV, 0, true); }
+  if (n_mine > 1) load_keys(sK + kT5TileBytes, 1, false);
   t5_commit_group();
-  load_keys(sV, 0, true);
-  t5_commit_group();
-
+  t5_wait_group<0>();
+  t5_fence_async_smem();
   t5_fence_before();
   __syncthreads();
   t5_fence_after();
   uint32_t tmem;
   asm volatile("ld.shared.u32 %0, [%1];\n" : "=r"(tmem) : "r"(slot));
-  const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
-  const uint32_t tS = tmem + lane_base, tO = tmem + lane_base + 128;
+  const uint32_t tS_all = tmem + 256 * wg, tO_all = tS_all + 128;  // lane 0: what the MMA is given
+  const uint32_t lane_base = (uint32_t)(((tid >> 5) & 3) * 32) << 16;
+  const uint32_t tS = tS_all + lane_base, tO = tO_all + lane_base;  // this thread's lane
 
-  const int my_row = row0 + tid;
-  const int my_keys = min(own_keys, my_row - seq_start + 1);  // own-chunk keys this row may see
-  float o[kD];
+  auto issue_s = [&](int i) {  // S = Q K^T of this warpgroup's i-th block
+    const uint32_t kbuf = sK + (i & 1) * kT5TileBytes;
 #pragma unroll
-  for (int i = 0; i < kD; ++i) o[i] = 0.f;
-  float m = -INFINITY, l = 0.f;  // running max of the raw scores, running sum
-  bool alive = true;
-
-  for (int kb = 0; kb < nb; ++kb) {
-    const uint32_t parity = kb & 1;
-    // ---- K block kb has landed (groups in flight: [K kb][V kb])
-    t5_wait_group<1>();
-    t5_fence_async_smem();
-    t5_fence_before();
-    __syncthreads();
-    if (tid == 0 && alive) {
-      t5_fence_after();
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {  // 16 channels per instruction
-        const uint32_t off = (j >> 2) * kT5BlockBytes + (j & 3) * 32;
-        t5_mma_ss(tmem, t5_desc(sQ + off, 16, 1024), t5_desc(sK + off, 16, 1024), kT5IdescQK, j > 0);
-      }
-      t5_mma_commit(bar_s);
+    for (int j = 0; j < 8; ++j) {  // 16 channels per instruction
+      const uint32_t off = (j >> 2) * kT5BlockBytes + (j & 3) * 32;
+      t5_mma_ss(tS_all, t5_desc(sQ + off, 16, 1024), t5_desc(kbuf + off, 16, 1024), kT5IdescQK, j > 0);
     }
-    if (alive && !t5_mbar_wait(bar_s, parity)) alive = false;
-    alive = __syncthreads_and(alive);
-    if (!alive) break;
+    t5_mma_commit(bar_s);
+  };
+  if (wt == 0 && n_mine > 0) issue_s(0);
+
+  const int my_row = row0 + wt;
+  const int my_keys = min(own_keys, my_row - seq_start + 1);  // own-chunk keys this row may see
+  const int first_keys = row0 - seq_start + 1;                // ... and the tile's first row
+  float m_ref = -INFINITY, l = 0.f;  // offset of the exponentials (log2 units, scaled), running sum
+  bool dead = false;
+
+  for (int i = 0; i < n_mine; ++i) {
+    const uint32_t parity = i & 1;
+    bool ok = t5_mbar_wait(bar_s, parity);  // S of block i is complete
     t5_fence_after();
-    // K is free: refill it for the next block (an empty group keeps the group count uniform)
-    if (kb + 1 < nb) load_keys(sK, kb + 1, false);
+    // its K buffer is free: fetch K two blocks ahead (an empty group keeps the group count uniform)
+    if (ok && i + 2 < n_mine) load_keys(sK + (i & 1) * kT5TileBytes, i + 2, false);
     t5_commit_group();
 
     // ---- softmax of this thread's row
+    const int kb = wg + 2 * i;
     const bool pre = kb < nb_pre;
     const int j0 = pre ? kb * kT5Tile : (kb - nb_pre) * kT5Tile;
-    const int lim = (pre ? prefix_len : my_keys) - j0;  // keys [0, lim) of this block are visible
+    const int lim = (pre ? prefix_len : my_keys) - j0;                         // keys [0, lim) visible to this row
+    const bool full = (pre ? prefix_len : min(own_keys, first_keys)) - j0 >= kT5Tile;  // ... all 128 to every row
+    uint32_t u[128];
+    t5_ld128(tS, u);
     float mx = -INFINITY;
+    if (full) {
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      float s[32];
-      t5_ld32(tS + 32 * c, s);
+      for (int c = 0; c < 128; ++c) mx = fmaxf(mx, __uint_as_float(u[c]));
+    } else {
 #pragma unroll
-      for (int i = 0; i < 32; ++i) mx = fmaxf(mx, 32 * c + i < lim ? s[i] : -INFINITY);
+      for (int c = 0; c < 128; ++c) mx = fmaxf(mx, c < lim ? __uint_as_float(u[c]) : -INFINITY);
     }
-    const float m_new = fmaxf(m, mx);
-    const float m_use = m_new == -INFINITY ? 0.f : m_new * scale_log2;  // kernels.py:1062
-    const float alpha = t5_exp2(m * scale_log2 - m_use);
-    m = m_new;
-    float psum = 0.f;
+    const float r = mx * scale_log2;
+    const bool move = r > m_ref + kT5Lazy;  // also true for the first visible key of a row (m_ref = -inf)
+    if (__any_sync(0xffffffffu, move)) {
+      const float alpha = move ? t5_exp2(m_ref - r) : 1.f;  // 0 when nothing was accumulated yet
+      if (move) { m_ref = r; l *= alpha; }
+      if (i > 0) {  // O of the earlier blocks is complete (its completion was awaited below)
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      float s[32];
-      t5_ld32(tS + 32 * c, s);
-      uint32_t pk[16];
+        for (int c = 0; c < 4; ++c) {
+          uint32_t w[32];
+          t5_ld32(tO + 32 * c, w);
 #pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        const int kk = 32 * c + 2 * i;
-        const float p0 = kk < lim ? t5_exp2(fmaf(s[2 * i], scale_log2, -m_use)) : 0.f;
-        const float p1 = kk + 1 < lim ? t5_exp2(fmaf(s[2 * i + 1], scale_log2, -m_use)) : 0.f;
-        psum += p0 + p1;
-        pk[i] = t5_pack_bf16x2(p0, p1);
+          for (int e = 0; e < 32; ++e) w[e] = __float_as_uint(__uint_as_float(w[e]) * alpha);
+          t5_st32(tO + 32 * c, w);
+        }
       }
-      t5_st16(tS + 16 * c, pk);  // P over the columns of S already consumed
     }
-    l = l * alpha + psum;
+    const float off = m_ref == -INFINITY ? 0.f : m_ref;  // kernels.py:1062
+    float psum = 0.f;
+    uint32_t pk[64];
+    if (full) {
+#pragma unroll
+      for (int c = 0; c < 64; ++c) {
+        const float p0 = t5_exp2(fmaf(__uint_as_float(u[2 * c]), scale_log2, -off));
+        const float p1 = t5_exp2(fmaf(__uint_as_float(u[2 * c + 1]), scale_log2, -off));
+        psum += p0 + p1;
+        pk[c] = t5_pack_bf16x2(p0, p1);
+      }
+    } else {
+#pragma unroll
+      for (int c = 0; c < 64; ++c) {
+        const float p0 = 2 * c < lim ? t5_exp2(fmaf(__uint_as_float(u[2 * c]), scale_log2, -off)) : 0.f;
+        const float p1 = 2 * c + 1 < lim ? t5_exp2(fmaf(__uint_as_float(u[2 * c + 1]), scale_log2, -off)) : 0.f;
+        psum += p0 + p1;
+        pk[c] = t5_pack_bf16x2(p0, p1);
+      }
+    }
+    l += psum;
+    t5_st64(tS, pk);  // P over the first 64 columns of S
     asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
 
-    // ---- V block kb has landed (groups in flight: [V kb][K kb+1]); P is complete
+    // ---- V of block i and K of block i+1 have landed (only the newest group, K of block i+2, may be in flight)
     t5_wait_group<1>();
     t5_fence_async_smem();
+    if (!ok) asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(dead_flag), "r"(1) : "memory");
     t5_fence_before();
-    __syncthreads();
-    if (tid == 0) {
+    t5_wg_sync(wg);
+    {
+      uint32_t f;
+      asm volatile("ld.shared.u32 %0, [%1];\n" : "=r"(f) : "r"(dead_flag) : "memory");
+      if (f) { dead = true; break; }
+    }
+    if (wt == 0) {
       t5_fence_after();
 #pragma unroll
       for (int j = 0; j < 8; ++j)  // 16 keys per instruction: 8 columns of packed P, 2 KB of V rows
-        t5_mma_ts(tmem + 128, tmem + 8 * j, t5_desc(sV + j * 2048, kT5BlockBytes, 1024), kT5IdescPV, j > 0);
+        t5_mma_ts(tO_all, tS_all + 8 * j, t5_desc(sV + j * 2048, kT5BlockBytes, 1024), kT5IdescPV, (i > 0) || (j > 0));
       t5_mma_commit(bar_o);
+      if (i + 1 < n_mine) issue_s(i + 1);  // executes behind P V: it overwrites the columns P is read from
     }
-    if (!t5_mbar_wait(bar_o, parity)) alive = false;
-    alive = __syncthreads_and(alive);
-    if (!alive) break;
+    ok = t5_mbar_wait(bar_o, parity);  // P V of block i is complete: V is free, O is stable
     t5_fence_after();
-    if (kb + 1 < nb) load_keys(sV, kb + 1, true);
+    if (ok && i + 1 < n_mine) load_keys(sV, i + 1, true);
     t5_commit_group();
-
-    // ---- O = O * alpha + PV
-#pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      float pv[32];
-      t5_ld32(tO + 32 * c, pv);
-#pragma unroll
-      for (int i = 0; i < 32; ++i) o[32 * c + i] = fmaf(o[32 * c + i], alpha, pv[i]);
-    }
+    if (!ok) asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(dead_flag), "r"(1) : "memory");
   }
   t5_wait_group<0>();
-  if (!alive && tid == 0 && status) atomicOr(status, B200KV_S_TIMEOUT);
 
-  if (alive && my_row < row_end) {
-    const float inv = l != 0.f ? 1.f / l : 0.f;  // kernels.py:1118
-    uint4* dst = reinterpret_cast<uint4*>(out + (long long)my_row * o_sn + hq * o_sh);
+  // ---- merge the two warpgroups: warpgroup 1 hands its (offset, sum, O) over through shared memory
+  // (its K buffers: 64 KB, [channel][row] fp32 so that both sides touch consecutive banks)
+  const uint32_t xO = base + kT5TileBytes + kT5WgBytes, xML = sV;  // warpgroup 0's V tile holds the 2 x 128 scalars
+  t5_wg_sync(wg);  // every thread of the warpgroup is past its last use of these buffers
+  {
+    uint32_t f;
+    asm volatile("ld.shared.u32 %0, [%1];\n" : "=r"(f) : "r"(dead_flag) : "memory");
+    dead = dead || f;
+  }
+  if (wg == 1) {
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      uint4 w;
-      w.x = t5_pack_bf16x2(o[8 * i] * inv, o[8 * i + 1] * inv);
-      w.y = t5_pack_bf16x2(o[8 * i + 2] * inv, o[8 * i + 3] * inv);
-      w.z = t5_pack_bf16x2(o[8 * i + 4] * inv, o[8 * i + 5] * inv);
-      w.w = t5_pack_bf16x2(o[8 * i + 6] * inv, o[8 * i + 7] * inv);
-      dst[i] = w;
+    for (int c = 0; c < 4; ++c) {
+      uint32_t w[32];
+      if (n_mine > 0 && !dead) {
+        t5_ld32(tO + 32 * c, w);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 32; ++e) w[e] = 0u;
+      }
+#pragma unroll
+      for (int e = 0; e < 32; ++e)
+        asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(xO + ((32 * c + e) * 128 + wt) * 4), "r"(w[e]) : "memory");
+    }
+  }
+  t5_fence_before();
+  __syncthreads();  // (a) warpgroup 0 no longer uses its V tile, (b) warpgroup 1's O is visible
+  if (wg == 1) {
+    const uint32_t a = base + kT5TileBytes + 2 * kT5TileBytes;  // warpgroup 0's V tile
+    asm volatile("st.shared.f32 [%0], %1;\n" ::"r"(a + wt * 4), "f"(m_ref) : "memory");
+    asm volatile("st.shared.f32 [%0], %1;\n" ::"r"(a + 512 + wt * 4), "f"(l) : "memory");
+    asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(a + 1024), "r"(dead ? 1 : 0) : "memory");
+  }
+  __syncthreads();
+  if (wg == 0) {
+    float m1, l1;
+    uint32_t dead1;
+    asm volatile("ld.shared.f32 %0, [%1];\n" : "=f"(m1) : "r"(xML + wt * 4) : "memory");
+    asm volatile("ld.shared.f32 %0, [%1];\n" : "=f"(l1) : "r"(xML + 512 + wt * 4) : "memory");
+    asm volatile("ld.shared.u32 %0, [%1];\n" : "=r"(dead1) : "r"(xML + 1024) : "memory");
+    dead = dead || dead1;
+    if (dead && wt == 0 && status) atomicOr(status, B200KV_S_TIMEOUT);
+    if (!dead) {
+      t5_fence_after();
+      const float mm = fmaxf(m_ref, m1);
+      const float a0 = m_ref == -INFINITY ? 0.f : t5_exp2(m_ref - mm), a1 = m1 == -INFINITY ? 0.f : t5_exp2(m1 - mm);
+      const float lt = l * a0 + l1 * a1;
+      const float inv = lt != 0.f ? 1.f / lt : 0.f;  // kernels.py:1118
+      const float f0 = a0 * inv, f1 = a1 * inv;
+      uint4* dst = reinterpret_cast<uint4*>(out + (long long)my_row * o_sn + hq * o_sh);
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t w[32];
+        t5_ld32(tO + 32 * c, w);
+        float o[32];
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          float o1;
+          asm volatile("ld.shared.f32 %0, [%1];\n" : "=f"(o1) : "r"(xO + ((32 * c + e) * 128 + wt) * 4) : "memory");
+          o[e] = __uint_as_float(w[e]) * f0 + o1 * f1;
+        }
+        if (my_row < row_end) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            uint4 x;
+            x.x = t5_pack_bf16x2(o[8 * e], o[8 * e + 1]);
+            x.y = t5_pack_bf16x2(o[8 * e + 2], o[8 * e + 3]);
+            x.z = t5_pack_bf16x2(o[8 * e + 4], o[8 * e + 5]);
+            x.w = t5_pack_bf16x2(o[8 * e + 6], o[8 * e + 7]);
+            dst[4 * c + e] = x;
+          }
+        }
+      }
     }
   }
   t5_fence_before();
   __syncthreads();
-  if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(kT5Cols) : "memory");
+  if (tid < 32) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(kT5Cols) : "memory");
 }
 
 int launch_prefill_attn_tc5(const uint16_t* q, long long q_sn, long long q_sh, const uint16_t* k, long long k_sn,
