@@ -26,9 +26,11 @@
 // matrix descriptors name: two blocks of 64 channels, each [row][128 bytes] with the 16-byte
 // chunk index XOR-ed with (row & 7).  K and V use the same physical layout; only their
 // descriptors differ (K: K-major, rows = N; V: N-major, rows = K).  Each warpgroup fills its own
-// tiles with cp.async (two K buffers, one V buffer; rows past the visible range are zero-filled,
-// so uninitialised memory behind a prefix never reaches the tensor core): K two blocks ahead as
-// soon as S of this block is complete, V of the next block as soon as P V of this one is.
+// tiles with cp.async (one K tile, two V tiles; rows past the visible range are zero-filled, so
+// uninitialised memory behind a prefix never reaches the tensor core).  The tensor core executes
+// one thread's products in issue order, so the completion of S of block i also means that P V of
+// block i-1 is complete: at that one wait per block the K tile and the other V tile are free and
+// block i+1 is fetched into them, under the softmax of block i.
 //
 // Every wait on an mbarrier is bounded: if a completion never arrives the warpgroup records
 // B200KV_S_TIMEOUT in the status word, stops issuing work and skips its stores; the CTA still
@@ -42,7 +44,7 @@ constexpr int kT5Threads = 256;
 constexpr int kT5Tile = 128;                        // query rows per CTA = keys per block
 constexpr uint32_t kT5TileBytes = kT5Tile * kD * 2; // 32 KB
 constexpr uint32_t kT5BlockBytes = kT5Tile * 128;   // one 64-channel block of a tile: 16 KB
-constexpr uint32_t kT5WgBytes = 3 * kT5TileBytes;   // per warpgroup: K0, K1, V
+constexpr uint32_t kT5WgBytes = 3 * kT5TileBytes;   // per warpgroup: K, V0, V1
 constexpr uint32_t kT5Smem = kT5TileBytes + 2 * kT5WgBytes + 1024 /* alignment slack */ + 64 /* barriers, flags */;
 constexpr uint32_t kT5Cols = 512;                   // tensor memory: warpgroup w has S/P at 256w, O at 256w+128
 constexpr uint32_t kT5SpinLimit = 1u << 20;
@@ -159,8 +161,8 @@ prefill_attn_tc5_kernel(const uint16_t* __restrict__ q, long long q_sn, long lon
   const int n_mine = (nb - wg + 1) >> 1;  // this warpgroup's blocks: wg, wg + 2, ...
   const uint32_t base = (t5_smem_u32(t5_raw) + 1023u) & ~1023u;
   const uint32_t sQ = base;
-  const uint32_t sK = base + kT5TileBytes + wg * kT5WgBytes;  // K buffers at sK and sK + 32 KB
-  const uint32_t sV = sK + 2 * kT5TileBytes;
+  const uint32_t sK = base + kT5TileBytes + wg * kT5WgBytes;  // one K tile, then two V tiles
+  const uint32_t sV = sK + kT5TileBytes;
   const uint32_t bars = base + kT5TileBytes + 2 * kT5WgBytes;
   const uint32_t bar_s = bars + wg * 16, bar_o = bar_s + 8, slot = bars + 32, dead_flag = bars + 40 + wg * 4;
 
@@ -195,7 +197,6 @@ prefill_attn_tc5_kernel(const uint16_t* __restrict__ q, long long q_sn, long lon
   // read and computed but never stored.
   t5_load_tile<256>(sQ, q + (long long)row0 * q_sn + hq * q_sh, q_sn, min(kT5Tile, N - row0), tid);
   if (n_mine > 0) { load_keys(sK, 0, false); load_keys(sV, 0, true); }
-  if (n_mine > 1) load_keys(sK + kT5TileBytes, 1, false);
   t5_commit_group();
   t5_wait_group<0>();
   t5_fence_async_smem();
@@ -208,16 +209,15 @@ prefill_attn_tc5_kernel(const uint16_t* __restrict__ q, long long q_sn, long lon
   const uint32_t lane_base = (uint32_t)(((tid >> 5) & 3) * 32) << 16;
   const uint32_t tS = tS_all + lane_base, tO = tO_all + lane_base;  // this thread's lane
 
-  auto issue_s = [&](int i) {  // S = Q K^T of this warpgroup's i-th block
-    const uint32_t kbuf = sK + (i & 1) * kT5TileBytes;
+  auto issue_s = [&]() {  // S = Q K^T of the block in the K tile
 #pragma unroll
     for (int j = 0; j < 8; ++j) {  // 16 channels per instruction
       const uint32_t off = (j >> 2) * kT5BlockBytes + (j & 3) * 32;
-      t5_mma_ss(tS_all, t5_desc(sQ + off, 16, 1024), t5_desc(kbuf + off, 16, 1024), kT5IdescQK, j > 0);
+      t5_mma_ss(tS_all, t5_desc(sQ + off, 16, 1024), t5_desc(sK + off, 16, 1024), kT5IdescQK, j > 0);
     }
     t5_mma_commit(bar_s);
   };
-  if (wt == 0 && n_mine > 0) issue_s(0);
+  if (wt == 0 && n_mine > 0) issue_s();
 
   const int my_row = row0 + wt;
   const int my_keys = min(own_keys, my_row - seq_start + 1);  // own-chunk keys this row may see
@@ -227,10 +227,14 @@ prefill_attn_tc5_kernel(const uint16_t* __restrict__ q, long long q_sn, long lon
 
   for (int i = 0; i < n_mine; ++i) {
     const uint32_t parity = i & 1;
-    bool ok = t5_mbar_wait(bar_s, parity);  // S of block i is complete
+    // S of block i is complete, and with it (the tensor core runs one thread's products in order) P V of
+    // block i-1: the K tile and the other V tile are free, O is stable.  Fetch block i+1 into them.
+    const bool ok = t5_mbar_wait(bar_s, parity);
     t5_fence_after();
-    // its K buffer is free: fetch K two blocks ahead (an empty group keeps the group count uniform)
-    if (ok && i + 2 < n_mine) load_keys(sK + (i & 1) * kT5TileBytes, i + 2, false);
+    if (ok && i + 1 < n_mine) {
+      load_keys(sK, i + 1, false);
+      load_keys(sV + ((i + 1) & 1) * kT5TileBytes, i + 1, true);
+    }
     t5_commit_group();
 
     // ---- softmax of this thread's row
@@ -241,20 +245,21 @@ prefill_attn_tc5_kernel(const uint16_t* __restrict__ q, long long q_sn, long lon
     const bool full = (pre ? prefix_len : min(own_keys, first_keys)) - j0 >= kT5Tile;  // ... all 128 to every row
     uint32_t u[128];
     t5_ld128(tS, u);
-    float mx = -INFINITY;
+    float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // four chains instead of one of 128
     if (full) {
 #pragma unroll
-      for (int c = 0; c < 128; ++c) mx = fmaxf(mx, __uint_as_float(u[c]));
+      for (int c = 0; c < 128; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(u[c]));
     } else {
 #pragma unroll
-      for (int c = 0; c < 128; ++c) mx = fmaxf(mx, c < lim ? __uint_as_float(u[c]) : -INFINITY);
+      for (int c = 0; c < 128; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], c < lim ? __uint_as_float(u[c]) : -INFINITY);
     }
+    const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
     const float r = mx * scale_log2;
     const bool move = r > m_ref + kT5Lazy;  // also true for the first visible key of a row (m_ref = -inf)
     if (__any_sync(0xffffffffu, move)) {
       const float alpha = move ? t5_exp2(m_ref - r) : 1.f;  // 0 when nothing was accumulated yet
       if (move) { m_ref = r; l *= alpha; }
-      if (i > 0) {  // O of the earlier blocks is complete (its completion was awaited below)
+      if (i > 0) {  // O of the earlier blocks is complete (see above)
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           uint32_t w[32];
@@ -266,14 +271,14 @@ prefill_attn_tc5_kernel(const uint16_t* __restrict__ q, long long q_sn, long lon
       }
     }
     const float off = m_ref == -INFINITY ? 0.f : m_ref;  // kernels.py:1062
-    float psum = 0.f;
+    float ps4[4] = {0.f, 0.f, 0.f, 0.f};
     uint32_t pk[64];
     if (full) {
 #pragma unroll
       for (int c = 0; c < 64; ++c) {
         const float p0 = t5_exp2(fmaf(__uint_as_float(u[2 * c]), scale_log2, -off));
         const float p1 = t5_exp2(fmaf(__uint_as_float(u[2 * c + 1]), scale_log2, -off));
-        psum += p0 + p1;
+        ps4[c & 3] += p0 + p1;
         pk[c] = t5_pack_bf16x2(p0, p1);
       }
     } else {
@@ -281,16 +286,16 @@ prefill_attn_tc5_kernel(const uint16_t* __restrict__ q, long long q_sn, long lon
       for (int c = 0; c < 64; ++c) {
         const float p0 = 2 * c < lim ? t5_exp2(fmaf(__uint_as_float(u[2 * c]), scale_log2, -off)) : 0.f;
         const float p1 = 2 * c + 1 < lim ? t5_exp2(fmaf(__uint_as_float(u[2 * c + 1]), scale_log2, -off)) : 0.f;
-        psum += p0 + p1;
+        ps4[c & 3] += p0 + p1;
         pk[c] = t5_pack_bf16x2(p0, p1);
       }
     }
-    l += psum;
+    l += (ps4[0] + ps4[1]) + (ps4[2] + ps4[3]);
     t5_st64(tS, pk);  // P over the first 64 columns of S
     asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
 
-    // ---- V of block i and K of block i+1 have landed (only the newest group, K of block i+2, may be in flight)
-    t5_wait_group<1>();
+    // ---- K of block i+1 has landed (V of block i did one iteration ago)
+    t5_wait_group<0>();
     t5_fence_async_smem();
     if (!ok) asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(dead_flag), "r"(1) : "memory");
     t5_fence_before();
@@ -304,21 +309,21 @@ prefill_attn_tc5_kernel(const uint16_t* __restrict__ q, long long q_sn, long lon
       t5_fence_after();
 #pragma unroll
       for (int j = 0; j < 8; ++j)  // 16 keys per instruction: 8 columns of packed P, 2 KB of V rows
-        t5_mma_ts(tO_all, tS_all + 8 * j, t5_desc(sV + j * 2048, kT5BlockBytes, 1024), kT5IdescPV, (i > 0) || (j > 0));
-      t5_mma_commit(bar_o);
-      if (i + 1 < n_mine) issue_s(i + 1);  // executes behind P V: it overwrites the columns P is read from
+        t5_mma_ts(tO_all, tS_all + 8 * j, t5_desc(sV + (i & 1) * kT5TileBytes + j * 2048, kT5BlockBytes, 1024), kT5IdescPV,
+                  (i > 0) || (j > 0));
+      if (i + 1 < n_mine) issue_s();  // executes behind P V: it overwrites the columns P is read from
+      else t5_mma_commit(bar_o);      // the last P V of this warpgroup
     }
-    ok = t5_mbar_wait(bar_o, parity);  // P V of block i is complete: V is free, O is stable
-    t5_fence_after();
-    if (ok && i + 1 < n_mine) load_keys(sV, i + 1, true);
-    t5_commit_group();
-    if (!ok) asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(dead_flag), "r"(1) : "memory");
   }
   t5_wait_group<0>();
+  if (n_mine > 0 && !dead) {
+    if (!t5_mbar_wait(bar_o, 0)) asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(dead_flag), "r"(1) : "memory");
+    t5_fence_after();
+  }
 
   // ---- merge the two warpgroups: warpgroup 1 hands its (offset, sum, O) over through shared memory
-  // (its K buffers: 64 KB, [channel][row] fp32 so that both sides touch consecutive banks)
-  const uint32_t xO = base + kT5TileBytes + kT5WgBytes, xML = sV;  // warpgroup 0's V tile holds the 2 x 128 scalars
+  // (its K tile and first V tile: 64 KB, [channel][row] fp32 so that both sides touch consecutive banks)
+  const uint32_t xO = base + kT5TileBytes + kT5WgBytes, xML = base + kT5TileBytes;  // scalars: warpgroup 0's K tile
   t5_wg_sync(wg);  // every thread of the warpgroup is past its last use of these buffers
   {
     uint32_t f;
@@ -341,9 +346,9 @@ prefill_attn_tc5_kernel(const uint16_t* __restrict__ q, long long q_sn, long lon
     }
   }
   t5_fence_before();
-  __syncthreads();  // (a) warpgroup 0 no longer uses its V tile, (b) warpgroup 1's O is visible
+  __syncthreads();  // (a) warpgroup 0 no longer uses its K tile, (b) warpgroup 1's O is visible
   if (wg == 1) {
-    const uint32_t a = base + kT5TileBytes + 2 * kT5TileBytes;  // warpgroup 0's V tile
+    const uint32_t a = xML;
     asm volatile("st.shared.f32 [%0], %1;\n" ::"r"(a + wt * 4), "f"(m_ref) : "memory");
     asm volatile("st.shared.f32 [%0], %1;\n" ::"r"(a + 512 + wt * 4), "f"(l) : "memory");
     asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(a + 1024), "r"(dead ? 1 : 0) : "memory");
