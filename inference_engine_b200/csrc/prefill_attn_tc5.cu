@@ -3,34 +3,38 @@
 // attention of the prefilling entries over [dequantized prefix | own chunk], replacing
 // prefill_attention_kernel (qwen3-1.7b/kernels.py:987-1126).
 //
-// One CTA owns 128 query rows of one q head and runs two warpgroups of 128 threads.  The key
-// blocks (128 keys each) of the tile are dealt alternately to the two warpgroups; each keeps its
-// own running (max, sum, O) and the two are merged at the end, so while one warpgroup is in its
-// softmax the tensor core works for the other.  Inside a warpgroup, thread t owns query row t =
-// lane t of tensor memory: every row-wise softmax quantity lives in one thread, no shuffles.
-// Per key block of a warpgroup:
-//   S = Q K^T     8 x tcgen05.mma (M128 N128 K16, bf16 -> fp32), Q and K from shared memory,
-//                 S in the warpgroup's tensor-memory columns [0,128)
-//   softmax       one tcgen05.ld of the thread's 128 scores, max, exp2, sum; P rounded to bf16 as
-//                 the reference does (kernels.py:1068,1113) and stored over the first 64 columns of S
-//   O += P V      8 x tcgen05.mma with P read from tensor memory and V from shared memory
-//                 (channel-contiguous: N-major B operand), accumulating in columns [128,256)
+// One CTA owns 128 query rows of one q head and runs two warpgroups of 128 threads.  The keys of
+// the tile are cut into blocks of 64 and dealt alternately to the two warpgroups; each keeps its
+// own running (offset, sum, O) and the two are merged at the end.  Inside a warpgroup, thread t
+// owns query row t = lane t of tensor memory: every row-wise softmax quantity lives in one
+// thread, no shuffles.  Per key block h of a warpgroup:
+//   S(h) = Q K^T   8 x tcgen05.mma (M128 N64 K16, bf16 -> fp32), Q and K from shared memory, into
+//                  one of the warpgroup's two S buffers (64 tensor-memory columns each)
+//   softmax        one tcgen05.ld of the thread's 64 scores, max, exp2, sum; P rounded to bf16 as
+//                  the reference does (kernels.py:1068,1113) and stored over the first 32 columns
+//                  of the same S buffer
+//   O += P V       4 x tcgen05.mma (M128 N128 K16) with P read from tensor memory and V from
+//                  shared memory (channel-contiguous: N-major B operand), accumulating in the
+//                  warpgroup's 128 O columns
+// The products are software-pipelined against the softmax: right after P(h) is stored, the issuing
+// thread queues P V(h) and then S(h+2) into the buffer P(h) occupies (the tensor core executes one
+// thread's products in issue order), while S(h+1) is already complete or running in the other
+// buffer, so the warpgroup goes from one softmax straight into the next and the tensor core works
+// through the queue meanwhile.  One mbarrier wait per block.
 // O stays in tensor memory for the whole tile.  Its rescaling is lazy: the reference offset of the
-// exponentials only moves when the row maximum has grown by more than 2^8 since it was set (then O
-// and the sum are multiplied by the correction, a tensor-memory round trip); otherwise P is simply
-// computed against the older offset, which is the same mathematics.  The product S of the next
-// block is issued right behind P V of this one, so the tensor core never waits for the softmax
-// threads of its own warpgroup to come back.
+// exponentials only moves when the row maximum has grown by more than 2^8 since it was set (then,
+// after waiting for the one P V that may be in flight, O and the sum are multiplied by the
+// correction, a tensor-memory round trip); otherwise P is simply computed against the older
+// offset, which is the same mathematics.
 //
 // Q, K and V tiles are laid out in shared memory as the canonical 128-byte-swizzled layout the
 // matrix descriptors name: two blocks of 64 channels, each [row][128 bytes] with the 16-byte
 // chunk index XOR-ed with (row & 7).  K and V use the same physical layout; only their
 // descriptors differ (K: K-major, rows = N; V: N-major, rows = K).  Each warpgroup fills its own
-// tiles with cp.async (one K tile, two V tiles; rows past the visible range are zero-filled, so
-// uninitialised memory behind a prefix never reaches the tensor core).  The tensor core executes
-// one thread's products in issue order, so the completion of S of block i also means that P V of
-// block i-1 is complete: at that one wait per block the K tile and the other V tile are free and
-// block i+1 is fetched into them, under the softmax of block i.
+// rings of three K and three V tiles (64 keys = 16 KB each) with cp.async; rows past the visible
+// range are zero-filled, so uninitialised memory behind a prefix never reaches the tensor core.
+// When S(h) is complete (so is everything queued before it, P V(h-2) included), the slot of K(h)
+// takes K(h+3) and the slot of V(h-2) takes V(h+1): two softmaxes of lead for K, one for V.
 //
 // Every wait on an mbarrier is bounded: if a completion never arrives the warpgroup records
 // B200KV_S_TIMEOUT in the status word, stops issuing work and skips its stores; the CTA still
@@ -40,13 +44,14 @@
 
 namespace b200kv {
 
-constexpr int kT5Threads = 256;
-constexpr int kT5Tile = 128;                        // query rows per CTA = keys per block
-constexpr uint32_t kT5TileBytes = kT5Tile * kD * 2; // 32 KB
-constexpr uint32_t kT5BlockBytes = kT5Tile * 128;   // one 64-channel block of a tile: 16 KB
-constexpr uint32_t kT5WgBytes = 3 * kT5TileBytes;   // per warpgroup: K, V0, V1
-constexpr uint32_t kT5Smem = kT5TileBytes + 2 * kT5WgBytes + 1024 /* alignment slack */ + 64 /* barriers, flags */;
-constexpr uint32_t kT5Cols = 512;                   // tensor memory: warpgroup w has S/P at 256w, O at 256w+128
+constexpr int kT5Threads = 288;                       // two softmax warpgroups + one warp that issues the products
+constexpr int kT5Tile = 128;                         // query rows per CTA
+constexpr int kT5Keys = 64;                          // keys per block
+constexpr uint32_t kT5QBytes = kT5Tile * kD * 2;     // Q tile: 32 KB, two 64-channel blocks of 16 KB
+constexpr uint32_t kT5KvBytes = kT5Keys * kD * 2;    // K or V tile: 16 KB, two 64-channel blocks of 8 KB
+constexpr uint32_t kT5WgBytes = 6 * kT5KvBytes;      // per warpgroup: K ring of 3, V ring of 3
+constexpr uint32_t kT5Smem = kT5QBytes + 2 * kT5WgBytes + 1024 /* alignment slack */ + 128 /* barriers, flags */;
+constexpr uint32_t kT5Cols = 512;                    // tensor memory: warpgroup w has S0/P0 at 256w, S1/P1 at 256w+64, O at 256w+128
 constexpr uint32_t kT5SpinLimit = 1u << 20;
 constexpr float kT5Lazy = 8.f;                      // log2 of the growth of the row maximum that forces a rescale
 
@@ -77,6 +82,9 @@ __device__ __forceinline__ bool t5_mbar_wait(uint32_t bar, uint32_t parity) {
   }
   return false;
 }
+__device__ __forceinline__ void t5_mbar_arrive(uint32_t bar) {
+  asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.shared::cta.b64 st, [%0];\n\t}\n" ::"r"(bar) : "memory");
+}
 // Arrive on `bar` when every tcgen05.mma issued so far by this thread has completed.
 __device__ __forceinline__ void t5_mma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
@@ -88,10 +96,10 @@ __device__ __forceinline__ uint64_t t5_desc(uint32_t saddr, uint32_t lbo_bytes, 
   return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo_bytes >> 4) << 16) | ((uint64_t)(sbo_bytes >> 4) << 32) |
          (1ull << 46) | (2ull << 61);
 }
-// Instruction descriptor of kind::f16: fp32 accumulator, bf16 A and B, M = 128, N = 128.
-constexpr uint32_t kT5IdescBase = (1u << 4) | (1u << 7) | (1u << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
-constexpr uint32_t kT5IdescQK = kT5IdescBase;              // A (Q) K-major, B (K tile) K-major
-constexpr uint32_t kT5IdescPV = kT5IdescBase | (1u << 16); // B (V tile) N-major
+// Instruction descriptor of kind::f16: fp32 accumulator, bf16 A and B, M = 128, N as given.
+constexpr uint32_t t5_idesc(uint32_t n) { return (1u << 4) | (1u << 7) | (1u << 10) | ((n >> 3) << 17) | ((128u >> 4) << 24); }
+constexpr uint32_t kT5IdescQK = t5_idesc(kT5Keys);        // A (Q) K-major, B (K tile) K-major, N = 64 keys
+constexpr uint32_t kT5IdescPV = t5_idesc(kD) | (1u << 16); // B (V tile) N-major, N = 128 channels
 
 __device__ __forceinline__ void t5_mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
   asm volatile(
@@ -117,21 +125,28 @@ __device__ __forceinline__ uint32_t t5_pack_bf16x2(float lo, float hi) {
   return r;
 }
 
-// Copied by kThreads threads (tid in [0, kThreads)): `count` (<= 128) rows of 128 bf16 (row j at src + j*stride elements) into a swizzled tile; rows past
-// `count` are zero-filled.
-template <int kThreads>
+// Copied by kThreads threads (tid in [0, kThreads)): `count` (<= kRows) rows of 128 bf16 (row j at
+// src + j*stride elements) into a swizzled tile of kRows rows; rows past `count` are zero-filled.
+template <int kThreads, int kRows>
 __device__ __forceinline__ void t5_load_tile(uint32_t dst, const uint16_t* src, long long stride, int count, int tid) {
 #pragma unroll
-  for (int i = 0; i < (kT5Tile * 16) / kThreads; ++i) {
+  for (int i = 0; i < (kRows * 16) / kThreads; ++i) {
     const int c = tid + i * kThreads, r = c >> 4, col = c & 15;
     const bool valid = r < count;
-    const uint32_t d = dst + (col >> 3) * kT5BlockBytes + r * 128 + (((col & 7) ^ (r & 7)) << 4);
+    const uint32_t d = dst + (col >> 3) * (kRows * 128) + r * 128 + (((col & 7) ^ (r & 7)) << 4);
     t5_cp16(d, valid ? src + r * stride + col * 8 : src, valid ? 16 : 0);
   }
 }
 
-
 __device__ __forceinline__ void t5_wg_sync(int wg) { asm volatile("bar.sync %0, 128;\n" ::"r"(wg + 1) : "memory"); }
+__device__ __forceinline__ void t5_sts_u32(uint32_t addr, uint32_t v) {
+  asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t t5_lds_u32(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];\n" : "=r"(v) : "r"(addr) : "memory");
+  return v;
+}
 
 __global__ void __launch_bounds__(kT5Threads, 1)
 prefill_attn_tc5_kernel(const uint16_t* __restrict__ q, long long q_sn, long long q_sh, const uint16_t* __restrict__ k,
@@ -154,22 +169,34 @@ prefill_attn_tc5_kernel(const uint16_t* __restrict__ q, long long q_sn, long lon
   if (row0 >= row_end) return;
   const int cta_last = min(row0 + kT5Tile, row_end) - 1;
   const int own_keys = cta_last - seq_start + 1;  // causal: keys up to the CTA's last query
-  const int nb_pre = (prefix_len + kT5Tile - 1) / kT5Tile, nb_own = (own_keys + kT5Tile - 1) / kT5Tile;
+  const int nb_pre = (prefix_len + kT5Keys - 1) / kT5Keys, nb_own = (own_keys + kT5Keys - 1) / kT5Keys;
   const int nb = nb_pre + nb_own;
 
-  const int tid = threadIdx.x, wg = tid >> 7, wt = tid & 127;
-  const int n_mine = (nb - wg + 1) >> 1;  // this warpgroup's blocks: wg, wg + 2, ...
+  float m_ref_keep = -INFINITY, l_keep = 0.f;
+  const int tid = threadIdx.x, wg = tid >> 7, wt = tid & 127;  // wg 2 = the issuing warp
+  const int n_blk[2] = {(nb + 1) >> 1, nb >> 1};               // warpgroup w owns blocks w, w + 2, ...
+  const int n_mine = wg < 2 ? n_blk[wg] : 0;
   const uint32_t base = (t5_smem_u32(t5_raw) + 1023u) & ~1023u;
   const uint32_t sQ = base;
-  const uint32_t sK = base + kT5TileBytes + wg * kT5WgBytes;  // one K tile, then two V tiles
-  const uint32_t sV = sK + kT5TileBytes;
-  const uint32_t bars = base + kT5TileBytes + 2 * kT5WgBytes;
-  const uint32_t bar_s = bars + wg * 16, bar_o = bar_s + 8, slot = bars + 32, dead_flag = bars + 40 + wg * 4;
+  const uint32_t bars = base + kT5QBytes + 2 * kT5WgBytes;
+  // per warpgroup w at bars + 48 w: s_done[2] (one per S buffer, arrival = tcgen05.commit), o_done[2] (the
+  // last-but-one and the last P V, one phase each: a parity wait must never fall two phases behind, so these
+  // two do not share a barrier), ready[2] (one per S buffer, 128 arrivals: P stored, K and V tiles landed)
+  auto ring_k = [&](int w) { return base + kT5QBytes + w * kT5WgBytes; };
+  auto ring_v = [&](int w) { return ring_k(w) + 3 * kT5KvBytes; };
+  auto bar_s = [&](int w, int buf) { return bars + 48 * w + 8 * buf; };
+  auto bar_o = [&](int w, int which) { return bars + 48 * w + 16 + 8 * which; };
+  auto bar_r = [&](int w, int buf) { return bars + 48 * w + 32 + 8 * buf; };
+  const uint32_t slot = bars + 96, dead_flag = bars + 104;
 
   if (tid == 0) {
-    for (int i = 0; i < 4; ++i) t5_mbar_init(bars + 8 * i, 1);
-    asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(bars + 40), "r"(0) : "memory");
-    asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(bars + 44), "r"(0) : "memory");
+    for (int w = 0; w < 2; ++w)
+      for (int i = 0; i < 2; ++i) {
+        t5_mbar_init(bar_s(w, i), 1);
+        t5_mbar_init(bar_o(w, i), 1);
+        t5_mbar_init(bar_r(w, i), 128);
+      }
+    t5_sts_u32(dead_flag, 0);
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
   if (tid < 32) {
@@ -181,155 +208,170 @@ prefill_attn_tc5_kernel(const uint16_t* __restrict__ q, long long q_sn, long lon
   const uint16_t* vpre = v_prefix + hk * p_sh + (long long)prefix_start * p_sn;
   const uint16_t* kown = k + (long long)seq_start * k_sn + hk * k_sh;
   const uint16_t* vown = v + (long long)seq_start * v_sn + hk * v_sh;
-  // this warpgroup's i-th block is block wg + 2i of the tile
-  auto load_keys = [&](uint32_t dst, int i, bool is_v) {
-    const int kb = wg + 2 * i;
+  // a warpgroup's block h is block wg + 2h of the tile; it lives in slot h % 3 of that warpgroup's ring
+  auto load_keys = [&](int h, bool is_v) {
+    const int kb = wg + 2 * h;
+    const uint32_t dst = (is_v ? ring_v(wg) : ring_k(wg)) + (h % 3) * kT5KvBytes;
     if (kb < nb_pre) {
-      const int j0 = kb * kT5Tile;
-      t5_load_tile<128>(dst, (is_v ? vpre : kpre) + (long long)j0 * p_sn, p_sn, min(kT5Tile, prefix_len - j0), wt);
+      const int j0 = kb * kT5Keys;
+      t5_load_tile<128, kT5Keys>(dst, (is_v ? vpre : kpre) + (long long)j0 * p_sn, p_sn, min(kT5Keys, prefix_len - j0), wt);
     } else {
-      const int j0 = (kb - nb_pre) * kT5Tile;
-      if (is_v) t5_load_tile<128>(dst, vown + (long long)j0 * v_sn, v_sn, min(kT5Tile, own_keys - j0), wt);
-      else      t5_load_tile<128>(dst, kown + (long long)j0 * k_sn, k_sn, min(kT5Tile, own_keys - j0), wt);
+      const int j0 = (kb - nb_pre) * kT5Keys;
+      if (is_v) t5_load_tile<128, kT5Keys>(dst, vown + (long long)j0 * v_sn, v_sn, min(kT5Keys, own_keys - j0), wt);
+      else      t5_load_tile<128, kT5Keys>(dst, kown + (long long)j0 * k_sn, k_sn, min(kT5Keys, own_keys - j0), wt);
     }
   };
-  // Q rows past the end of the packed batch are zero-filled; rows of other entries inside the tile are
-  // read and computed but never stored.
-  t5_load_tile<256>(sQ, q + (long long)row0 * q_sn + hq * q_sh, q_sn, min(kT5Tile, N - row0), tid);
-  if (n_mine > 0) { load_keys(sK, 0, false); load_keys(sV, 0, true); }
-  t5_commit_group();
-  t5_wait_group<0>();
-  t5_fence_async_smem();
+  if (wg < 2) {
+    // Q rows past the end of the packed batch are zero-filled; rows of other entries inside the tile are
+    // read and computed but never stored.
+    t5_load_tile<256, kT5Tile>(sQ, q + (long long)row0 * q_sn + hq * q_sh, q_sn, min(kT5Tile, N - row0), tid);
+    for (int h = 0; h < 3; ++h)
+      if (h < n_mine) load_keys(h, false);
+    if (n_mine > 0) load_keys(0, true);
+    t5_commit_group();
+    t5_wait_group<0>();
+    t5_fence_async_smem();
+  }
   t5_fence_before();
   __syncthreads();
   t5_fence_after();
-  uint32_t tmem;
-  asm volatile("ld.shared.u32 %0, [%1];\n" : "=r"(tmem) : "r"(slot));
-  const uint32_t tS_all = tmem + 256 * wg, tO_all = tS_all + 128;  // lane 0: what the MMA is given
-  const uint32_t lane_base = (uint32_t)(((tid >> 5) & 3) * 32) << 16;
-  const uint32_t tS = tS_all + lane_base, tO = tO_all + lane_base;  // this thread's lane
-
-  auto issue_s = [&]() {  // S = Q K^T of the block in the K tile
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {  // 16 channels per instruction
-      const uint32_t off = (j >> 2) * kT5BlockBytes + (j & 3) * 32;
-      t5_mma_ss(tS_all, t5_desc(sQ + off, 16, 1024), t5_desc(sK + off, 16, 1024), kT5IdescQK, j > 0);
-    }
-    t5_mma_commit(bar_s);
-  };
-  if (wt == 0 && n_mine > 0) issue_s();
-
-  const int my_row = row0 + wt;
-  const int my_keys = min(own_keys, my_row - seq_start + 1);  // own-chunk keys this row may see
-  const int first_keys = row0 - seq_start + 1;                // ... and the tile's first row
-  float m_ref = -INFINITY, l = 0.f;  // offset of the exponentials (log2 units, scaled), running sum
+  const uint32_t tmem = t5_lds_u32(slot);
   bool dead = false;
 
-  for (int i = 0; i < n_mine; ++i) {
-    const uint32_t parity = i & 1;
-    // S of block i is complete, and with it (the tensor core runs one thread's products in order) P V of
-    // block i-1: the K tile and the other V tile are free, O is stable.  Fetch block i+1 into them.
-    const bool ok = t5_mbar_wait(bar_s, parity);
-    t5_fence_after();
-    if (ok && i + 1 < n_mine) {
-      load_keys(sK, i + 1, false);
-      load_keys(sV + ((i + 1) & 1) * kT5TileBytes, i + 1, true);
-    }
-    t5_commit_group();
-
-    // ---- softmax of this thread's row
-    const int kb = wg + 2 * i;
-    const bool pre = kb < nb_pre;
-    const int j0 = pre ? kb * kT5Tile : (kb - nb_pre) * kT5Tile;
-    const int lim = (pre ? prefix_len : my_keys) - j0;                         // keys [0, lim) visible to this row
-    const bool full = (pre ? prefix_len : min(own_keys, first_keys)) - j0 >= kT5Tile;  // ... all 128 to every row
-    uint32_t u[128];
-    t5_ld128(tS, u);
-    float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // four chains instead of one of 128
-    if (full) {
+  if (wg == 2) {
+    // ---- the issuing warp: one lane queues every product of the CTA, serving the warpgroups in turn
+    if (tid == 256) {
+      auto issue_s = [&](int w, int h) {  // S(h) = Q K(h)^T into S buffer h & 1 of warpgroup w, then the arrival
+        const uint32_t kt = ring_k(w) + (h % 3) * kT5KvBytes;
 #pragma unroll
-      for (int c = 0; c < 128; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(u[c]));
-    } else {
+        for (int j = 0; j < 8; ++j)  // 16 channels per instruction
+          t5_mma_ss(tmem + 256 * w + 64 * (h & 1), t5_desc(sQ + (j >> 2) * (kT5Tile * 128) + (j & 3) * 32, 16, 1024),
+                    t5_desc(kt + (j >> 2) * (kT5Keys * 128) + (j & 3) * 32, 16, 1024), kT5IdescQK, j > 0);
+        t5_mma_commit(bar_s(w, h & 1));
+      };
+      for (int h = 0; h < 2; ++h)
+        for (int w = 0; w < 2; ++w)
+          if (h < n_blk[w]) issue_s(w, h);
+      bool live = true;
+      for (int h = 0; h < n_blk[0] && live; ++h) {
+        for (int w = 0; w < 2; ++w) {
+          if (h >= n_blk[w]) continue;
+          // P(h) is stored and V(h), K(h+2) have landed
+          if (!t5_mbar_wait(bar_r(w, h & 1), (h >> 1) & 1)) { t5_sts_u32(dead_flag, 1); live = false; break; }
+          t5_fence_after();
+          const uint32_t vt = ring_v(w) + (h % 3) * kT5KvBytes, tw = tmem + 256 * w;
 #pragma unroll
-      for (int c = 0; c < 128; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], c < lim ? __uint_as_float(u[c]) : -INFINITY);
-    }
-    const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-    const float r = mx * scale_log2;
-    const bool move = r > m_ref + kT5Lazy;  // also true for the first visible key of a row (m_ref = -inf)
-    if (__any_sync(0xffffffffu, move)) {
-      const float alpha = move ? t5_exp2(m_ref - r) : 1.f;  // 0 when nothing was accumulated yet
-      if (move) { m_ref = r; l *= alpha; }
-      if (i > 0) {  // O of the earlier blocks is complete (see above)
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t w[32];
-          t5_ld32(tO + 32 * c, w);
-#pragma unroll
-          for (int e = 0; e < 32; ++e) w[e] = __float_as_uint(__uint_as_float(w[e]) * alpha);
-          t5_st32(tO + 32 * c, w);
+          for (int j = 0; j < 4; ++j)  // 16 keys per instruction: 8 columns of packed P, 2 KB of V rows
+            t5_mma_ts(tw + 128, tw + 64 * (h & 1) + 8 * j, t5_desc(vt + j * 2048, kT5Keys * 128, 1024), kT5IdescPV,
+                      (h > 0) || (j > 0));
+          if (h + 2 < n_blk[w]) issue_s(w, h + 2);  // executes behind P V(h): it overwrites the columns P(h) is read from
+          else t5_mma_commit(bar_o(w, h + 1 < n_blk[w] ? 0 : 1));  // the last-but-one / the last P V of the warpgroup
         }
       }
     }
-    const float off = m_ref == -INFINITY ? 0.f : m_ref;  // kernels.py:1062
-    float ps4[4] = {0.f, 0.f, 0.f, 0.f};
-    uint32_t pk[64];
-    if (full) {
-#pragma unroll
-      for (int c = 0; c < 64; ++c) {
-        const float p0 = t5_exp2(fmaf(__uint_as_float(u[2 * c]), scale_log2, -off));
-        const float p1 = t5_exp2(fmaf(__uint_as_float(u[2 * c + 1]), scale_log2, -off));
-        ps4[c & 3] += p0 + p1;
-        pk[c] = t5_pack_bf16x2(p0, p1);
-      }
-    } else {
-#pragma unroll
-      for (int c = 0; c < 64; ++c) {
-        const float p0 = 2 * c < lim ? t5_exp2(fmaf(__uint_as_float(u[2 * c]), scale_log2, -off)) : 0.f;
-        const float p1 = 2 * c + 1 < lim ? t5_exp2(fmaf(__uint_as_float(u[2 * c + 1]), scale_log2, -off)) : 0.f;
-        ps4[c & 3] += p0 + p1;
-        pk[c] = t5_pack_bf16x2(p0, p1);
-      }
-    }
-    l += (ps4[0] + ps4[1]) + (ps4[2] + ps4[3]);
-    t5_st64(tS, pk);  // P over the first 64 columns of S
-    asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
-
-    // ---- K of block i+1 has landed (V of block i did one iteration ago)
-    t5_wait_group<0>();
-    t5_fence_async_smem();
-    if (!ok) asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(dead_flag), "r"(1) : "memory");
-    t5_fence_before();
-    t5_wg_sync(wg);
-    {
-      uint32_t f;
-      asm volatile("ld.shared.u32 %0, [%1];\n" : "=r"(f) : "r"(dead_flag) : "memory");
-      if (f) { dead = true; break; }
-    }
-    if (wt == 0) {
+  } else {
+    const uint32_t lane_base = (uint32_t)(((tid >> 5) & 3) * 32) << 16;
+    const uint32_t tS = tmem + 256 * wg + lane_base, tO = tS + 128;  // this thread's lane
+    const int my_keys = min(own_keys, row0 + wt - seq_start + 1);  // own-chunk keys this row may see
+    const int first_keys = min(own_keys, row0 - seq_start + 1);    // ... and the tile's first row
+    float m_ref = -INFINITY, l = 0.f;  // offset of the exponentials (log2 units, scaled), running sum
+    bool ok = true;
+    for (int h = 0; h < n_mine && ok; ++h) {
+      // S(h) is complete, and with it everything queued before it, P V(h-2) included: the slots of K(h) and
+      // V(h-2) are free.  Fetch K(h+3) and V(h+1) into them (an empty group keeps the count uniform).
+      ok = t5_mbar_wait(bar_s(wg, h & 1), (h >> 1) & 1);
       t5_fence_after();
+      if (ok) {
+        if (h + 3 < n_mine) load_keys(h + 3, false);
+        if (h + 1 < n_mine) load_keys(h + 1, true);
+      }
+      t5_commit_group();
+
+      // ---- softmax of this thread's row
+      const int kb = wg + 2 * h;
+      const bool pre = kb < nb_pre;
+      const int j0 = pre ? kb * kT5Keys : (kb - nb_pre) * kT5Keys;
+      const int lim = (pre ? prefix_len : my_keys) - j0;                // keys [0, lim) visible to this row
+      const bool full = (pre ? prefix_len : first_keys) - j0 >= kT5Keys;  // ... all 64 to every row of the tile
+      uint32_t u[64];
+      t5_ld64(tS + 64 * (h & 1), u);
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // four chains instead of one of 64
+      if (full) {
 #pragma unroll
-      for (int j = 0; j < 8; ++j)  // 16 keys per instruction: 8 columns of packed P, 2 KB of V rows
-        t5_mma_ts(tO_all, tS_all + 8 * j, t5_desc(sV + (i & 1) * kT5TileBytes + j * 2048, kT5BlockBytes, 1024), kT5IdescPV,
-                  (i > 0) || (j > 0));
-      if (i + 1 < n_mine) issue_s();  // executes behind P V: it overwrites the columns P is read from
-      else t5_mma_commit(bar_o);      // the last P V of this warpgroup
+        for (int c = 0; c < 64; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(u[c]));
+      } else {
+#pragma unroll
+        for (int c = 0; c < 64; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], c < lim ? __uint_as_float(u[c]) : -INFINITY);
+      }
+      const float r = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
+      const bool move = r > m_ref + kT5Lazy;  // also true for the first visible key of a row (m_ref = -inf)
+      if (__any_sync(0xffffffffu, move)) {
+        const float alpha = move ? t5_exp2(m_ref - r) : 1.f;  // 0 when nothing was accumulated yet
+        if (move) { m_ref = r; l *= alpha; }
+        if (h > 0) {
+          // O must be at rest: P V(h-1) may still be queued.  Its completion is what S(h+1)'s barrier (or, for
+          // the last block, the barrier of the last-but-one P V) reports; waiting for that phase here and again
+          // at the top of the next block is harmless.
+          ok = ok && (h + 1 < n_mine ? t5_mbar_wait(bar_s(wg, (h + 1) & 1), ((h + 1) >> 1) & 1) : t5_mbar_wait(bar_o(wg, 0), 0));
+          t5_fence_after();
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            uint32_t w[32];
+            t5_ld32(tO + 32 * c, w);
+#pragma unroll
+            for (int e = 0; e < 32; ++e) w[e] = __float_as_uint(__uint_as_float(w[e]) * alpha);
+            t5_st32(tO + 32 * c, w);
+          }
+        }
+      }
+      const float off = m_ref == -INFINITY ? 0.f : m_ref;  // kernels.py:1062
+      float ps4[4] = {0.f, 0.f, 0.f, 0.f};
+      uint32_t pk[32];
+      if (full) {
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          const float p0 = t5_exp2(fmaf(__uint_as_float(u[2 * c]), scale_log2, -off));
+          const float p1 = t5_exp2(fmaf(__uint_as_float(u[2 * c + 1]), scale_log2, -off));
+          ps4[c & 3] += p0 + p1;
+          pk[c] = t5_pack_bf16x2(p0, p1);
+        }
+      } else {
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          const float p0 = 2 * c < lim ? t5_exp2(fmaf(__uint_as_float(u[2 * c]), scale_log2, -off)) : 0.f;
+          const float p1 = 2 * c + 1 < lim ? t5_exp2(fmaf(__uint_as_float(u[2 * c + 1]), scale_log2, -off)) : 0.f;
+          ps4[c & 3] += p0 + p1;
+          pk[c] = t5_pack_bf16x2(p0, p1);
+        }
+      }
+      l += (ps4[0] + ps4[1]) + (ps4[2] + ps4[3]);
+      t5_st32(tS + 64 * (h & 1), pk);  // P over the first 32 columns of this S buffer
+      asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
+      // V(h) and K(h+2) have landed (only the group issued above may still be in flight): hand over to the
+      // issuing warp
+      t5_wait_group<1>();
+      t5_fence_async_smem();
+      t5_fence_before();
+      if (ok) t5_mbar_arrive(bar_r(wg, h & 1));
     }
-  }
-  t5_wait_group<0>();
-  if (n_mine > 0 && !dead) {
-    if (!t5_mbar_wait(bar_o, 0)) asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(dead_flag), "r"(1) : "memory");
+    t5_wait_group<0>();
+    if (n_mine > 0 && ok) ok = t5_mbar_wait(bar_o(wg, 1), 0);  // the last P V
     t5_fence_after();
+    if (!ok) t5_sts_u32(dead_flag, 1);
+    // kept for the merge below
+    m_ref_keep = m_ref;
+    l_keep = l;
   }
 
   // ---- merge the two warpgroups: warpgroup 1 hands its (offset, sum, O) over through shared memory
-  // (its K tile and first V tile: 64 KB, [channel][row] fp32 so that both sides touch consecutive banks)
-  const uint32_t xO = base + kT5TileBytes + kT5WgBytes, xML = base + kT5TileBytes;  // scalars: warpgroup 0's K tile
-  t5_wg_sync(wg);  // every thread of the warpgroup is past its last use of these buffers
-  {
-    uint32_t f;
-    asm volatile("ld.shared.u32 %0, [%1];\n" : "=r"(f) : "r"(dead_flag) : "memory");
-    dead = dead || f;
-  }
+  // (the first 64 KB of its rings, [channel][row] fp32 so that both sides touch consecutive banks)
+  const uint32_t xO = base + kT5QBytes + kT5WgBytes, xML = base + kT5QBytes;  // scalars: start of warpgroup 0's rings
+  const uint32_t tO = tmem + 256 * (wg & 1) + 128 + ((uint32_t)(((tid >> 5) & 3) * 32) << 16);
+  const int my_row = row0 + wt;
+  t5_fence_before();
+  __syncthreads();  // every product of the CTA is complete (or given up), nobody uses the rings any more
+  t5_fence_after();
+  dead = t5_lds_u32(dead_flag) != 0;
   if (wg == 1) {
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
@@ -341,32 +383,20 @@ prefill_attn_tc5_kernel(const uint16_t* __restrict__ q, long long q_sn, long lon
         for (int e = 0; e < 32; ++e) w[e] = 0u;
       }
 #pragma unroll
-      for (int e = 0; e < 32; ++e)
-        asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(xO + ((32 * c + e) * 128 + wt) * 4), "r"(w[e]) : "memory");
+      for (int e = 0; e < 32; ++e) t5_sts_u32(xO + ((32 * c + e) * 128 + wt) * 4, w[e]);
     }
-  }
-  t5_fence_before();
-  __syncthreads();  // (a) warpgroup 0 no longer uses its K tile, (b) warpgroup 1's O is visible
-  if (wg == 1) {
-    const uint32_t a = xML;
-    asm volatile("st.shared.f32 [%0], %1;\n" ::"r"(a + wt * 4), "f"(m_ref) : "memory");
-    asm volatile("st.shared.f32 [%0], %1;\n" ::"r"(a + 512 + wt * 4), "f"(l) : "memory");
-    asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(a + 1024), "r"(dead ? 1 : 0) : "memory");
+    t5_sts_u32(xML + wt * 4, __float_as_uint(m_ref_keep));
+    t5_sts_u32(xML + 512 + wt * 4, __float_as_uint(l_keep));
   }
   __syncthreads();
   if (wg == 0) {
-    float m1, l1;
-    uint32_t dead1;
-    asm volatile("ld.shared.f32 %0, [%1];\n" : "=f"(m1) : "r"(xML + wt * 4) : "memory");
-    asm volatile("ld.shared.f32 %0, [%1];\n" : "=f"(l1) : "r"(xML + 512 + wt * 4) : "memory");
-    asm volatile("ld.shared.u32 %0, [%1];\n" : "=r"(dead1) : "r"(xML + 1024) : "memory");
-    dead = dead || dead1;
+    const float m0 = m_ref_keep, l0 = l_keep;
+    const float m1 = __uint_as_float(t5_lds_u32(xML + wt * 4)), l1 = __uint_as_float(t5_lds_u32(xML + 512 + wt * 4));
     if (dead && wt == 0 && status) atomicOr(status, B200KV_S_TIMEOUT);
     if (!dead) {
-      t5_fence_after();
-      const float mm = fmaxf(m_ref, m1);
-      const float a0 = m_ref == -INFINITY ? 0.f : t5_exp2(m_ref - mm), a1 = m1 == -INFINITY ? 0.f : t5_exp2(m1 - mm);
-      const float lt = l * a0 + l1 * a1;
+      const float mm = fmaxf(m0, m1);
+      const float a0 = m0 == -INFINITY ? 0.f : t5_exp2(m0 - mm), a1 = m1 == -INFINITY ? 0.f : t5_exp2(m1 - mm);
+      const float lt = l0 * a0 + l1 * a1;
       const float inv = lt != 0.f ? 1.f / lt : 0.f;  // kernels.py:1118
       const float f0 = a0 * inv, f1 = a1 * inv;
       uint4* dst = reinterpret_cast<uint4*>(out + (long long)my_row * o_sn + hq * o_sh);
@@ -376,11 +406,8 @@ prefill_attn_tc5_kernel(const uint16_t* __restrict__ q, long long q_sn, long lon
         t5_ld32(tO + 32 * c, w);
         float o[32];
 #pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          float o1;
-          asm volatile("ld.shared.f32 %0, [%1];\n" : "=f"(o1) : "r"(xO + ((32 * c + e) * 128 + wt) * 4) : "memory");
-          o[e] = __uint_as_float(w[e]) * f0 + o1 * f1;
-        }
+        for (int e = 0; e < 32; ++e)
+          o[e] = __uint_as_float(w[e]) * f0 + __uint_as_float(t5_lds_u32(xO + ((32 * c + e) * 128 + wt) * 4)) * f1;
         if (my_row < row_end) {
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
