@@ -152,14 +152,16 @@ int b200kv_prefill_attn(const void* q, int64_t q_stride_n, int64_t q_stride_h,
  * variant 0 = automatic (what b200kv_prefill_attn does: the tcgen05 kernel when block_m >= 64,
  * else the mma.sync kernel), 1 = the mma.sync kernel (64-row CTAs, register accumulators),
  * 2 = the tcgen05 kernel (128-row CTAs, accumulators in tensor memory).  Both give results within
- * the attention tolerance of each other; they differ in summation order. */
+ * the attention tolerance of each other; they differ in summation order.  prefix_rows = rows each
+ * kv head of k_prefix / v_prefix holds (their shape[1]); it bounds the tensor-map copies of the
+ * tcgen05 kernel.  0 = unknown: prefix tiles are then fetched with plain asynchronous copies. */
 int b200kv_prefill_attn_variant(const void* q, int64_t q_stride_n, int64_t q_stride_h,
                                 const void* k, int64_t k_stride_n, int64_t k_stride_h,
                                 const void* v, int64_t v_stride_n, int64_t v_stride_h,
                                 const int32_t* seq_ids, const int32_t* cu_seqlens, const int32_t* tile_start,
                                 int32_t num_tiles, int32_t block_m,
                                 const void* k_prefix, const void* v_prefix, int64_t p_stride_h, int64_t p_stride_n,
-                                const int32_t* cu_cached,
+                                int32_t prefix_rows, const int32_t* cu_cached,
                                 void* out, int64_t o_stride_n, int64_t o_stride_h,
                                 int32_t N, int32_t Hq, int32_t Hkv, int32_t D,
                                 int32_t variant, int32_t* status, void* stream);

@@ -53,8 +53,8 @@ SIGNATURES = {
                                       c_void_p]),
     "b200kv_prefill_attn_variant": (c_int32, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_void_p, c_int64,
                                               c_int64, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_void_p, c_void_p,
-                                              c_int64, c_int64, c_void_p, c_void_p, c_int64, c_int64, c_int32, c_int32,
-                                              c_int32, c_int32, c_int32, c_void_p, c_void_p]),
+                                              c_int64, c_int64, c_int32, c_void_p, c_void_p, c_int64, c_int64, c_int32,
+                                              c_int32, c_int32, c_int32, c_int32, c_void_p, c_void_p]),
     "b200kv_decode_attn_workspace_bytes": (c_size_t, [c_int32, c_int32, c_int32, c_int32, c_int32]),
     "b200kv_decode_attn": (c_int32, [c_void_p, c_int64, c_int64, P_CACHE, P_TABLE, c_void_p, c_void_p, c_float, c_void_p,
                                      c_int64, c_int64, c_void_p, c_size_t, c_int32, c_int32, c_int32, c_int32, c_void_p,

@@ -219,20 +219,21 @@ int launch_prefill_attn_tc5(const uint16_t* q, long long q_sn, long long q_sh, c
                             long long k_sh, const uint16_t* v, long long v_sn, long long v_sh, const int32_t* seq_ids,
                             const int32_t* cu_seqlens, const int32_t* tile_start, int num_tiles, int block_m,
                             const uint16_t* k_prefix, const uint16_t* v_prefix, long long p_sh, long long p_sn,
-                            const int32_t* cu_cached, uint16_t* out, long long o_sn, long long o_sh, int N, int Hq,
-                            int Hkv, float scale_log2, int32_t* status, cudaStream_t stream);
+                            int prefix_rows, const int32_t* cu_cached, uint16_t* out, long long o_sn, long long o_sh, int N,
+                            int Hq, int Hkv, float scale_log2, int32_t* status, cudaStream_t stream);
 }
 
 extern "C" int b200kv_prefill_attn_variant(const void* q, int64_t q_sn, int64_t q_sh, const void* k, int64_t k_sn,
                                            int64_t k_sh, const void* v, int64_t v_sn, int64_t v_sh, const int32_t* seq_ids,
                                            const int32_t* cu_seqlens, const int32_t* tile_start, int32_t num_tiles,
                                            int32_t block_m, const void* k_prefix, const void* v_prefix, int64_t p_sh,
-                                           int64_t p_sn, const int32_t* cu_cached, void* out, int64_t o_sn, int64_t o_sh,
-                                           int32_t N, int32_t Hq, int32_t Hkv, int32_t D, int32_t variant, int32_t* status,
-                                           void* stream) {
+                                           int64_t p_sn, int32_t prefix_rows, const int32_t* cu_cached, void* out,
+                                           int64_t o_sn, int64_t o_sh, int32_t N, int32_t Hq, int32_t Hkv, int32_t D,
+                                           int32_t variant, int32_t* status, void* stream) {
   if (!q || !k || !v || !seq_ids || !cu_seqlens || !tile_start || !k_prefix || !v_prefix || !cu_cached || !out)
     return B200KV_E_NULL;
-  if (D != kD || Hq < 1 || Hkv < 1 || Hq % Hkv || N < 0 || num_tiles < 0 || block_m < 1) return B200KV_E_SHAPE;
+  if (D != kD || Hq < 1 || Hkv < 1 || Hq % Hkv || N < 0 || num_tiles < 0 || block_m < 1 || prefix_rows < 0)
+    return B200KV_E_SHAPE;
   if (variant < 0 || variant > 2) return B200KV_E_RANGE;
   if (!aligned(q, 16) || !aligned(k, 16) || !aligned(v, 16) || !aligned(k_prefix, 16) || !aligned(v_prefix, 16) ||
       !aligned(out, 16))
@@ -248,8 +249,8 @@ extern "C" int b200kv_prefill_attn_variant(const void* q, int64_t q_sn, int64_t 
   if (tc5)
     return launch_prefill_attn_tc5((const uint16_t*)q, q_sn, q_sh, (const uint16_t*)k, k_sn, k_sh, (const uint16_t*)v, v_sn,
                                    v_sh, seq_ids, cu_seqlens, tile_start, num_tiles, block_m, (const uint16_t*)k_prefix,
-                                   (const uint16_t*)v_prefix, p_sh, p_sn, cu_cached, (uint16_t*)out, o_sn, o_sh, N, Hq, Hkv,
-                                   scale_log2, status, (cudaStream_t)stream);
+                                   (const uint16_t*)v_prefix, p_sh, p_sn, prefix_rows, cu_cached, (uint16_t*)out, o_sn, o_sh, N,
+                                   Hq, Hkv, scale_log2, status, (cudaStream_t)stream);
   const int subs = (block_m + kPfRows - 1) / kPfRows;
   const size_t smem = 4 * (size_t)kPfTileBytes;
   if (cudaFuncSetAttribute(prefill_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
@@ -267,7 +268,8 @@ extern "C" int b200kv_prefill_attn(const void* q, int64_t q_sn, int64_t q_sh, co
                                    const void* k_prefix, const void* v_prefix, int64_t p_sh, int64_t p_sn,
                                    const int32_t* cu_cached, void* out, int64_t o_sn, int64_t o_sh, int32_t N, int32_t Hq,
                                    int32_t Hkv, int32_t D, void* stream) {
+  // no row count in this signature: 0 = unknown (the tcgen05 kernel then copies prefix tiles with cp.async)
   return b200kv_prefill_attn_variant(q, q_sn, q_sh, k, k_sn, k_sh, v, v_sn, v_sh, seq_ids, cu_seqlens, tile_start, num_tiles,
-                                     block_m, k_prefix, v_prefix, p_sh, p_sn, cu_cached, out, o_sn, o_sh, N, Hq, Hkv, D, 0,
+                                     block_m, k_prefix, v_prefix, p_sh, p_sn, 0, cu_cached, out, o_sn, o_sh, N, Hq, Hkv, D, 0,
                                      nullptr, stream);
 }

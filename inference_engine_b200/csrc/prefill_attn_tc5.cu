@@ -39,6 +39,8 @@
 // Every wait on an mbarrier is bounded: if a completion never arrives the warpgroup records
 // B200KV_S_TIMEOUT in the status word, stops issuing work and skips its stores; the CTA still
 // frees its tensor memory and returns.
+#include <cuda.h>  // CUtensorMap and the cuTensorMapEncodeTiled prototype only; the entry point is fetched at run time
+
 #include "common.cuh"
 #include "tmem_ldst.cuh"
 
@@ -50,7 +52,7 @@ constexpr int kT5Keys = 64;                          // keys per block
 constexpr uint32_t kT5QBytes = kT5Tile * kD * 2;     // Q tile: 32 KB, two 64-channel blocks of 16 KB
 constexpr uint32_t kT5KvBytes = kT5Keys * kD * 2;    // K or V tile: 16 KB, two 64-channel blocks of 8 KB
 constexpr uint32_t kT5WgBytes = 6 * kT5KvBytes;      // per warpgroup: K ring of 3, V ring of 3
-constexpr uint32_t kT5Smem = kT5QBytes + 2 * kT5WgBytes + 1024 /* alignment slack */ + 128 /* barriers, flags */;
+constexpr uint32_t kT5Smem = kT5QBytes + 2 * kT5WgBytes + 1024 /* alignment slack */ + 256 /* barriers, flags */;
 constexpr uint32_t kT5Cols = 512;                    // tensor memory: warpgroup w has S0/P0 at 256w, S1/P1 at 256w+64, O at 256w+128
 constexpr uint32_t kT5SpinLimit = 1u << 20;
 constexpr float kT5Lazy = 8.f;                      // log2 of the growth of the row maximum that forces a rescale
@@ -84,6 +86,17 @@ __device__ __forceinline__ bool t5_mbar_wait(uint32_t bar, uint32_t parity) {
 }
 __device__ __forceinline__ void t5_mbar_arrive(uint32_t bar) {
   asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.shared::cta.b64 st, [%0];\n\t}\n" ::"r"(bar) : "memory");
+}
+// One arrival that also announces `bytes` of bulk-copy traffic the phase has to see before it completes.
+__device__ __forceinline__ void t5_mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1;\n\t}\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+// Tensor-map (TMA) tile load of one box into shared memory; completion is counted in bytes on `bar`.
+// c0 (the channel coordinate) must keep the 16-byte rule: it is 0 or 64 bf16 here.
+__device__ __forceinline__ void t5_tma_3d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];\n"
+      ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(bar) : "memory");
 }
 // Arrive on `bar` when every tcgen05.mma issued so far by this thread has completed.
 __device__ __forceinline__ void t5_mma_commit(uint32_t bar) {
@@ -155,7 +168,9 @@ prefill_attn_tc5_kernel(const uint16_t* __restrict__ q, long long q_sn, long lon
                         const int32_t* __restrict__ tile_start, int block_m, int subs,
                         const uint16_t* __restrict__ k_prefix, const uint16_t* __restrict__ v_prefix, long long p_sh,
                         long long p_sn, const int32_t* __restrict__ cu_cached, uint16_t* __restrict__ out, long long o_sn,
-                        long long o_sh, int N, int G, float scale_log2, int32_t* status) {
+                        long long o_sh, int N, int G, float scale_log2, int32_t* status,
+                        const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+                        const __grid_constant__ CUtensorMap tm_kp, const __grid_constant__ CUtensorMap tm_vp, int prefix_tma) {
   extern __shared__ uint8_t t5_raw[];
   const int tile = blockIdx.x / subs, sub = blockIdx.x - tile * subs;
   const int tile_row = tile_start[tile];
@@ -184,10 +199,14 @@ prefill_attn_tc5_kernel(const uint16_t* __restrict__ q, long long q_sn, long lon
   // two do not share a barrier), ready[2] (one per S buffer, 128 arrivals: P stored, K and V tiles landed)
   auto ring_k = [&](int w) { return base + kT5QBytes + w * kT5WgBytes; };
   auto ring_v = [&](int w) { return ring_k(w) + 3 * kT5KvBytes; };
-  auto bar_s = [&](int w, int buf) { return bars + 48 * w + 8 * buf; };
-  auto bar_o = [&](int w, int which) { return bars + 48 * w + 16 + 8 * which; };
-  auto bar_r = [&](int w, int buf) { return bars + 48 * w + 32 + 8 * buf; };
-  const uint32_t slot = bars + 96, dead_flag = bars + 104;
+  // and kfull[3], vfull[3] (one per ring slot: the tile has landed; one arrival by the thread that started
+  // the fetch, plus the tile's bytes when it is a tensor-map copy)
+  auto bar_s = [&](int w, int buf) { return bars + 96 * w + 8 * buf; };
+  auto bar_o = [&](int w, int which) { return bars + 96 * w + 16 + 8 * which; };
+  auto bar_r = [&](int w, int buf) { return bars + 96 * w + 32 + 8 * buf; };
+  auto bar_kf = [&](int w, int sl) { return bars + 96 * w + 48 + 8 * sl; };
+  auto bar_vf = [&](int w, int sl) { return bars + 96 * w + 72 + 8 * sl; };
+  const uint32_t slot = bars + 192, dead_flag = bars + 200;
 
   if (tid == 0) {
     for (int w = 0; w < 2; ++w)
@@ -195,6 +214,11 @@ prefill_attn_tc5_kernel(const uint16_t* __restrict__ q, long long q_sn, long lon
         t5_mbar_init(bar_s(w, i), 1);
         t5_mbar_init(bar_o(w, i), 1);
         t5_mbar_init(bar_r(w, i), 128);
+      }
+    for (int w = 0; w < 2; ++w)
+      for (int i = 0; i < 3; ++i) {
+        t5_mbar_init(bar_kf(w, i), 1);
+        t5_mbar_init(bar_vf(w, i), 1);
       }
     t5_sts_u32(dead_flag, 0);
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
@@ -208,17 +232,32 @@ prefill_attn_tc5_kernel(const uint16_t* __restrict__ q, long long q_sn, long lon
   const uint16_t* vpre = v_prefix + hk * p_sh + (long long)prefix_start * p_sn;
   const uint16_t* kown = k + (long long)seq_start * k_sn + hk * k_sh;
   const uint16_t* vown = v + (long long)seq_start * v_sn + hk * v_sh;
-  // a warpgroup's block h is block wg + 2h of the tile; it lives in slot h % 3 of that warpgroup's ring
-  auto load_keys = [&](int h, bool is_v) {
-    const int kb = wg + 2 * h;
-    const uint32_t dst = (is_v ? ring_v(wg) : ring_k(wg)) + (h % 3) * kT5KvBytes;
-    if (kb < nb_pre) {
-      const int j0 = kb * kT5Keys;
-      t5_load_tile<128, kT5Keys>(dst, (is_v ? vpre : kpre) + (long long)j0 * p_sn, p_sn, min(kT5Keys, prefix_len - j0), wt);
+  // A warpgroup's block h is block wg + 2h of the tile; it lives in slot h % 3 of that warpgroup's ring.
+  // Full tiles come by tensor-map copies started by the warpgroup's first thread (two boxes of 64 rows x 64
+  // channels, swizzled by the copy engine into the layout described above).  A prefix block that is not full is
+  // copied by all 128 threads with cp.async instead, because the rows behind a prefix may be uninitialised
+  // memory and have to be zero in shared memory (0 x NaN would poison O); so is every prefix block when the
+  // caller gave no row capacity for the prefix tensors, and every tile of the prologue (use_tma = false).
+  auto fetch = [&](int h, bool is_v, bool use_tma) {
+    const int kb = wg + 2 * h, sl = h % 3;
+    const uint32_t dst = (is_v ? ring_v(wg) : ring_k(wg)) + sl * kT5KvBytes;
+    const uint32_t full = is_v ? bar_vf(wg, sl) : bar_kf(wg, sl);
+    const bool pre = kb < nb_pre;
+    const int j0 = pre ? kb * kT5Keys : (kb - nb_pre) * kT5Keys;
+    const int count = min(kT5Keys, (pre ? prefix_len : own_keys) - j0);
+    if (use_tma && (!pre || (prefix_tma && count == kT5Keys))) {
+      if (wt == 0) {
+        t5_mbar_expect_tx(full, kT5KvBytes);
+        const CUtensorMap* map = pre ? (is_v ? &tm_vp : &tm_kp) : (is_v ? &tm_v : &tm_k);
+        const int row = pre ? prefix_start + j0 : seq_start + j0;
+        for (int cb = 0; cb < 2; ++cb)
+          t5_tma_3d(dst + cb * (kT5Keys * 128), map, 64 * cb, pre ? row : hk, pre ? hk : row, full);
+      }
     } else {
-      const int j0 = (kb - nb_pre) * kT5Keys;
-      if (is_v) t5_load_tile<128, kT5Keys>(dst, vown + (long long)j0 * v_sn, v_sn, min(kT5Keys, own_keys - j0), wt);
-      else      t5_load_tile<128, kT5Keys>(dst, kown + (long long)j0 * k_sn, k_sn, min(kT5Keys, own_keys - j0), wt);
+      const uint16_t* src = pre ? (is_v ? vpre : kpre) + (long long)j0 * p_sn
+                                : (is_v ? vown + (long long)j0 * v_sn : kown + (long long)j0 * k_sn);
+      t5_load_tile<128, kT5Keys>(dst, src, pre ? p_sn : (is_v ? v_sn : k_sn), count, wt);
+      if (wt == 0) t5_mbar_arrive(full);  // keeps the slot's phases in step; the data is covered by `ready`
     }
   };
   if (wg < 2) {
@@ -226,8 +265,8 @@ prefill_attn_tc5_kernel(const uint16_t* __restrict__ q, long long q_sn, long lon
     // read and computed but never stored.
     t5_load_tile<256, kT5Tile>(sQ, q + (long long)row0 * q_sn + hq * q_sh, q_sn, min(kT5Tile, N - row0), tid);
     for (int h = 0; h < 3; ++h)
-      if (h < n_mine) load_keys(h, false);
-    if (n_mine > 0) load_keys(0, true);
+      if (h < n_mine) fetch(h, false, false);
+    if (n_mine > 0) fetch(0, true, false);
     t5_commit_group();
     t5_wait_group<0>();
     t5_fence_async_smem();
@@ -241,8 +280,10 @@ prefill_attn_tc5_kernel(const uint16_t* __restrict__ q, long long q_sn, long lon
   if (wg == 2) {
     // ---- the issuing warp: one lane queues every product of the CTA, serving the warpgroups in turn
     if (tid == 256) {
+      bool live = true;
       auto issue_s = [&](int w, int h) {  // S(h) = Q K(h)^T into S buffer h & 1 of warpgroup w, then the arrival
         const uint32_t kt = ring_k(w) + (h % 3) * kT5KvBytes;
+        if (!t5_mbar_wait(bar_kf(w, h % 3), (h / 3) & 1)) { t5_sts_u32(dead_flag, 1); live = false; return; }
 #pragma unroll
         for (int j = 0; j < 8; ++j)  // 16 channels per instruction
           t5_mma_ss(tmem + 256 * w + 64 * (h & 1), t5_desc(sQ + (j >> 2) * (kT5Tile * 128) + (j & 3) * 32, 16, 1024),
@@ -252,12 +293,15 @@ prefill_attn_tc5_kernel(const uint16_t* __restrict__ q, long long q_sn, long lon
       for (int h = 0; h < 2; ++h)
         for (int w = 0; w < 2; ++w)
           if (h < n_blk[w]) issue_s(w, h);
-      bool live = true;
       for (int h = 0; h < n_blk[0] && live; ++h) {
         for (int w = 0; w < 2; ++w) {
           if (h >= n_blk[w]) continue;
           // P(h) is stored and V(h), K(h+2) have landed
-          if (!t5_mbar_wait(bar_r(w, h & 1), (h >> 1) & 1)) { t5_sts_u32(dead_flag, 1); live = false; break; }
+          if (!t5_mbar_wait(bar_r(w, h & 1), (h >> 1) & 1) || !t5_mbar_wait(bar_vf(w, h % 3), (h / 3) & 1)) {
+            t5_sts_u32(dead_flag, 1);
+            live = false;
+            break;
+          }
           t5_fence_after();
           const uint32_t vt = ring_v(w) + (h % 3) * kT5KvBytes, tw = tmem + 256 * w;
 #pragma unroll
@@ -266,6 +310,7 @@ prefill_attn_tc5_kernel(const uint16_t* __restrict__ q, long long q_sn, long lon
                       (h > 0) || (j > 0));
           if (h + 2 < n_blk[w]) issue_s(w, h + 2);  // executes behind P V(h): it overwrites the columns P(h) is read from
           else t5_mma_commit(bar_o(w, h + 1 < n_blk[w] ? 0 : 1));  // the last-but-one / the last P V of the warpgroup
+          if (!live) break;
         }
       }
     }
@@ -282,8 +327,8 @@ prefill_attn_tc5_kernel(const uint16_t* __restrict__ q, long long q_sn, long lon
       ok = t5_mbar_wait(bar_s(wg, h & 1), (h >> 1) & 1);
       t5_fence_after();
       if (ok) {
-        if (h + 3 < n_mine) load_keys(h + 3, false);
-        if (h + 1 < n_mine) load_keys(h + 1, true);
+        if (h + 3 < n_mine) fetch(h + 3, false, true);
+        if (h + 1 < n_mine) fetch(h + 1, true, true);
       }
       t5_commit_group();
 
@@ -427,20 +472,58 @@ prefill_attn_tc5_kernel(const uint16_t* __restrict__ q, long long q_sn, long lon
   if (tid < 32) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(kT5Cols) : "memory");
 }
 
+// cuTensorMapEncodeTiled, fetched from the driver through the runtime (the library links no libcuda).
+typedef CUresult (*t5_encode_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                 const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static t5_encode_fn t5_encoder() {
+  static t5_encode_fn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return (t5_encode_fn)p;
+  }();
+  return fn;
+}
+// A bf16 tensor [d2][d1][128 channels] with element strides (s2, s1, 1), read in boxes of 64 channels x b1 x b2
+// with the 128-byte swizzle; out-of-range rows read as zero.
+static bool t5_make_map(CUtensorMap* map, const void* base, uint64_t d1, uint64_t d2, long long s1, long long s2, uint32_t b1,
+                        uint32_t b2) {
+  t5_encode_fn enc = t5_encoder();
+  if (!enc || d1 == 0 || d2 == 0 || s1 <= 0 || s2 <= 0) return false;
+  const cuuint64_t dims[3] = {(cuuint64_t)kD, d1, d2};
+  const cuuint64_t strides[2] = {(cuuint64_t)s1 * 2, (cuuint64_t)s2 * 2};
+  const cuuint32_t box[3] = {64, b1, b2}, estr[3] = {1, 1, 1};
+  return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// prefix_rows: rows each kv head of k_prefix / v_prefix holds (0 = not known: prefix tiles are then copied with
+// cp.async only).
 int launch_prefill_attn_tc5(const uint16_t* q, long long q_sn, long long q_sh, const uint16_t* k, long long k_sn,
                             long long k_sh, const uint16_t* v, long long v_sn, long long v_sh, const int32_t* seq_ids,
                             const int32_t* cu_seqlens, const int32_t* tile_start, int num_tiles, int block_m,
                             const uint16_t* k_prefix, const uint16_t* v_prefix, long long p_sh, long long p_sn,
-                            const int32_t* cu_cached, uint16_t* out, long long o_sn, long long o_sh, int N, int Hq,
-                            int Hkv, float scale_log2, int32_t* status, cudaStream_t stream) {
+                            int prefix_rows, const int32_t* cu_cached, uint16_t* out, long long o_sn, long long o_sh, int N,
+                            int Hq, int Hkv, float scale_log2, int32_t* status, cudaStream_t stream) {
   // the opt-in is a per-device attribute of the function: set it on every call (it is cheap)
   if (cudaFuncSetAttribute(prefill_attn_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kT5Smem) !=
       cudaSuccess)
     return B200KV_E_LAUNCH;
+  CUtensorMap tm_k, tm_v, tm_kp, tm_vp;
+  // own chunk [N][Hkv][128]: box = 64 rows of one head
+  if (!t5_make_map(&tm_k, k, Hkv, N, k_sh, k_sn, 1, kT5Keys) || !t5_make_map(&tm_v, v, Hkv, N, v_sh, v_sn, 1, kT5Keys))
+    return B200KV_E_LAUNCH;
+  // prefix [Hkv][rows][128]: box = 64 rows of one head; without a row count the maps are placeholders
+  int prefix_tma = prefix_rows > 0 && t5_make_map(&tm_kp, k_prefix, prefix_rows, Hkv, p_sn, p_sh, kT5Keys, 1) &&
+                   t5_make_map(&tm_vp, v_prefix, prefix_rows, Hkv, p_sn, p_sh, kT5Keys, 1);
+  if (!prefix_tma) { tm_kp = tm_k; tm_vp = tm_v; }
   const int subs = (block_m + kT5Tile - 1) / kT5Tile;
   prefill_attn_tc5_kernel<<<dim3(num_tiles * subs, Hq), kT5Threads, kT5Smem, stream>>>(
       q, q_sn, q_sh, k, k_sn, k_sh, v, v_sn, v_sh, seq_ids, cu_seqlens, tile_start, block_m, subs, k_prefix, v_prefix, p_sh,
-      p_sn, cu_cached, out, o_sn, o_sh, N, Hq / Hkv, scale_log2, status);
+      p_sn, cu_cached, out, o_sn, o_sh, N, Hq / Hkv, scale_log2, status, tm_k, tm_v, tm_kp, tm_vp, prefix_tma);
   return cudaGetLastError() == cudaSuccess ? B200KV_OK : B200KV_E_LAUNCH;
 }
 

@@ -323,8 +323,8 @@ def prefill_attention(
     rc = lib.b200kv_prefill_attn_variant(
         q.data_ptr(), q.stride(0), q.stride(1), k.data_ptr(), k.stride(0), k.stride(1), v.data_ptr(), v.stride(0),
         v.stride(1), _i32(seq_ids), _i32(cu_seqlens), _i32(tile_start), tile_start.shape[0], int(PREFILL_BLOCK_M),
-        k_prefix.data_ptr(), v_prefix.data_ptr(), k_prefix.stride(0), k_prefix.stride(1), _i32(cu_cached),
-        out.data_ptr(), out.stride(0), out.stride(1), N, Hq, Hkv, D, int(variant),
+        k_prefix.data_ptr(), v_prefix.data_ptr(), k_prefix.stride(0), k_prefix.stride(1), k_prefix.shape[1],
+        _i32(cu_cached), out.data_ptr(), out.stride(0), out.stride(1), N, Hq, Hkv, D, int(variant),
         status_word(q.device).data_ptr(), _stream())
     _lib.check(rc, "prefill_attention")
     return out

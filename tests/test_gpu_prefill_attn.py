@@ -85,3 +85,28 @@ def test_long_chunk_on_prefix(K, prior, variant):
     assert K.check_status() == 0
     mx, mean = H.attn_errors(H.to_f32(out)[nd:], want[nd:])
     assert mx <= 8e-3 and mean <= 4e-4, (mx, mean)
+
+
+@pytest.mark.parametrize("variant", [1, 2])
+def test_rows_behind_the_prefix_are_never_used(K, variant):
+    """The prefix scratch is uninitialised behind the last entry's rows (the engine allocates it with
+    torch.empty): NaNs there must not reach any output, also when the prefix ends inside a key block."""
+    rng = np.random.default_rng(4242)
+    chunk, prefix, nd = [150, 40], [200, 70], 0
+    N = sum(chunk)
+    cu = np.concatenate([[0], np.cumsum(chunk)]).astype(np.int32)
+    cu_cached = np.concatenate([[0], np.cumsum(prefix)]).astype(np.int32)
+    seq_ids = np.concatenate([np.full(L, b) for b, L in enumerate(chunk)]).astype(np.int32)
+    q, k, v = H.randn_bf16(rng, N, HQ, D), H.randn_bf16(rng, N, HKV, D), H.randn_bf16(rng, N, HKV, D)
+    k_pre, v_pre = H.randn_bf16(rng, HKV, 270 + 200, D), H.randn_bf16(rng, HKV, 270 + 200, D)
+    want = O.prefill_attention(q, k, v, cu, k_pre, v_pre, cu_cached, nd)
+    k_pre[:, 270:], v_pre[:, 270:] = np.nan, np.nan
+    tiles = [r for b in range(len(chunk)) for r in range(cu[b], cu[b + 1], 128)] + [-1]
+    out = K.prefill_attention(H.bf16_tensor(q), H.bf16_tensor(k), H.bf16_tensor(v), H.i32(seq_ids), H.i32(cu),
+                              H.i32(tiles), H.bf16_tensor(k_pre), H.bf16_tensor(v_pre), H.i32(cu_cached), 128,
+                              variant=variant)
+    assert K.check_status() == 0
+    got = H.to_f32(out)
+    assert np.isfinite(got).all()
+    mx, mean = H.attn_errors(got, want)
+    assert mx <= 8e-3 and mean <= 4e-4, (mx, mean)
