@@ -3,42 +3,45 @@
 // attention of the prefilling entries over [dequantized prefix | own chunk], replacing
 // prefill_attention_kernel (qwen3-1.7b/kernels.py:987-1126).
 //
-// One CTA owns 128 query rows of one q head and runs two warpgroups of 128 threads.  The keys of
-// the tile are cut into blocks of 64 and dealt alternately to the two warpgroups; each keeps its
-// own running (offset, sum, O) and the two are merged at the end.  Inside a warpgroup, thread t
-// owns query row t = lane t of tensor memory: every row-wise softmax quantity lives in one
-// thread, no shuffles.  Per key block h of a warpgroup:
-//   S(h) = Q K^T   8 x tcgen05.mma (M128 N64 K16, bf16 -> fp32), Q and K from shared memory, into
-//                  one of the warpgroup's two S buffers (64 tensor-memory columns each)
-//   softmax        one tcgen05.ld of the thread's 64 scores, max, exp2, sum; P rounded to bf16 as
-//                  the reference does (kernels.py:1068,1113) and stored over the first 32 columns
-//                  of the same S buffer
-//   O += P V       4 x tcgen05.mma (M128 N128 K16) with P read from tensor memory and V from
-//                  shared memory (channel-contiguous: N-major B operand), accumulating in the
-//                  warpgroup's 128 O columns
-// The products are software-pipelined against the softmax: right after P(h) is stored, the issuing
-// thread queues P V(h) and then S(h+2) into the buffer P(h) occupies (the tensor core executes one
-// thread's products in issue order), while S(h+1) is already complete or running in the other
-// buffer, so the warpgroup goes from one softmax straight into the next and the tensor core works
-// through the queue meanwhile.  One mbarrier wait per block.
+// One CTA owns 128 query rows of one q head and runs eleven warps in three roles:
+//   warps 0-3 and 4-7   two softmax warpgroups.  The keys of the tile are cut into blocks of 64 and dealt
+//                       alternately to the two; each keeps its own running (offset, sum, O) and the two are
+//                       merged at the end.  Thread t of a warpgroup owns query row t = lane t of tensor
+//                       memory: every row-wise softmax quantity lives in one thread, no shuffles.
+//   warp 8              one lane issues every tcgen05.mma of the CTA.
+//   warps 9 and 10      fetch the K and V tiles of warpgroup 0 and 1 (tensor-map copies started by one lane).
+// Per key block h of a warpgroup:
+//   S(h) = Q K^T   8 x tcgen05.mma (M128 N64 K16, bf16 -> fp32), Q and K from shared memory, into one of the
+//                  warpgroup's two S buffers (64 tensor-memory columns each)
+//   softmax        one tcgen05.ld of the thread's 64 scores, max, exp2, sum; P rounded to bf16 as the
+//                  reference does (kernels.py:1068,1113) and stored over the first 32 columns of the same
+//                  S buffer
+//   O += P V       4 x tcgen05.mma (M128 N128 K16) with P read from tensor memory and V from shared memory
+//                  (channel-contiguous: N-major B operand), accumulating in the warpgroup's 128 O columns
+// The products are software-pipelined against the softmax: when P(h) is stored (128 arrivals on a `ready`
+// barrier), the issuing lane queues P V(h) and then S(h+2) into the buffer P(h) occupies (the tensor core
+// executes one thread's products in issue order), while S(h+1) is already complete or running in the other
+// buffer; the warpgroup goes from one softmax straight into the next.  Completions come back through
+// tcgen05.commit on mbarriers: `s_done` to the softmax threads, `kempty` / `vempty` to the fetching warp,
+// which refills the ring slot (three K and three V tiles of 16 KB per warpgroup) and reports on `kfull` /
+// `vfull`.  Measured on a B200 an M128 N64 K16 product from shared memory takes 49 cycles and an
+// M128 N128 K16 one 65 (the latter is the nominal rate; the former is bound by the 128 B/clk the tensor
+// core reads shared memory at), so one block pair costs the tensor core about 1300 cycles.
 // O stays in tensor memory for the whole tile.  Its rescaling is lazy: the reference offset of the
-// exponentials only moves when the row maximum has grown by more than 2^8 since it was set (then,
-// after waiting for the one P V that may be in flight, O and the sum are multiplied by the
-// correction, a tensor-memory round trip); otherwise P is simply computed against the older
-// offset, which is the same mathematics.
+// exponentials only moves when the row maximum has grown by more than 2^8 since it was set (then, after
+// waiting for the one P V that may be in flight, O and the sum are multiplied by the correction, a
+// tensor-memory round trip); otherwise P is simply computed against the older offset, which is the same
+// mathematics.
 //
-// Q, K and V tiles are laid out in shared memory as the canonical 128-byte-swizzled layout the
-// matrix descriptors name: two blocks of 64 channels, each [row][128 bytes] with the 16-byte
-// chunk index XOR-ed with (row & 7).  K and V use the same physical layout; only their
-// descriptors differ (K: K-major, rows = N; V: N-major, rows = K).  Each warpgroup fills its own
-// rings of three K and three V tiles (64 keys = 16 KB each) with cp.async; rows past the visible
-// range are zero-filled, so uninitialised memory behind a prefix never reaches the tensor core.
-// When S(h) is complete (so is everything queued before it, P V(h-2) included), the slot of K(h)
-// takes K(h+3) and the slot of V(h-2) takes V(h+1): two softmaxes of lead for K, one for V.
+// Q, K and V tiles are laid out in shared memory as the canonical 128-byte-swizzled layout the matrix
+// descriptors name: two blocks of 64 channels, each [row][128 bytes] with the 16-byte chunk index XOR-ed
+// with (row & 7) - which is also what a tensor-map copy with the 128-byte swizzle writes.  K and V use the
+// same physical layout; only their descriptors differ (K: K-major, rows = N; V: N-major, rows = K).
+// A prefix block that is not full is copied with cp.async and zero-filled instead (see the fetching warp).
 //
-// Every wait on an mbarrier is bounded: if a completion never arrives the warpgroup records
-// B200KV_S_TIMEOUT in the status word, stops issuing work and skips its stores; the CTA still
-// frees its tensor memory and returns.
+// Every wait on an mbarrier is bounded: if a completion never arrives the waiting role records it, stops
+// issuing work and the CTA skips its stores, sets B200KV_S_TIMEOUT in the status word, frees its tensor
+// memory and returns.
 #include <cuda.h>  // CUtensorMap and the cuTensorMapEncodeTiled prototype only; the entry point is fetched at run time
 
 #include "common.cuh"
@@ -46,13 +49,13 @@
 
 namespace b200kv {
 
-constexpr int kT5Threads = 288;                       // two softmax warpgroups + one warp that issues the products
+constexpr int kT5Threads = 352;                       // two softmax warpgroups, one warp issuing the products, two fetching tiles
 constexpr int kT5Tile = 128;                         // query rows per CTA
 constexpr int kT5Keys = 64;                          // keys per block
 constexpr uint32_t kT5QBytes = kT5Tile * kD * 2;     // Q tile: 32 KB, two 64-channel blocks of 16 KB
 constexpr uint32_t kT5KvBytes = kT5Keys * kD * 2;    // K or V tile: 16 KB, two 64-channel blocks of 8 KB
 constexpr uint32_t kT5WgBytes = 6 * kT5KvBytes;      // per warpgroup: K ring of 3, V ring of 3
-constexpr uint32_t kT5Smem = kT5QBytes + 2 * kT5WgBytes + 1024 /* alignment slack */ + 256 /* barriers, flags */;
+constexpr uint32_t kT5Smem = kT5QBytes + 2 * kT5WgBytes + 1024 /* alignment slack */ + 384 /* barriers, flags */;
 constexpr uint32_t kT5Cols = 512;                    // tensor memory: warpgroup w has S0/P0 at 256w, S1/P1 at 256w+64, O at 256w+128
 constexpr uint32_t kT5SpinLimit = 1u << 20;
 constexpr float kT5Lazy = 8.f;                      // log2 of the growth of the row maximum that forces a rescale
@@ -188,38 +191,36 @@ prefill_attn_tc5_kernel(const uint16_t* __restrict__ q, long long q_sn, long lon
   const int nb = nb_pre + nb_own;
 
   float m_ref_keep = -INFINITY, l_keep = 0.f;
-  const int tid = threadIdx.x, wg = tid >> 7, wt = tid & 127;  // wg 2 = the issuing warp
-  const int n_blk[2] = {(nb + 1) >> 1, nb >> 1};               // warpgroup w owns blocks w, w + 2, ...
-  const int n_mine = wg < 2 ? n_blk[wg] : 0;
+  // roles: warps 0-3 and 4-7 = softmax warpgroups 0 and 1, warp 8 = issues every product, warps 9 and 10 =
+  // fetch the K and V tiles of warpgroup 0 and 1
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, wg = tid >> 7, wt = tid & 127;
+  const int n_blk[2] = {(nb + 1) >> 1, nb >> 1};  // warpgroup w owns blocks w, w + 2, ...
   const uint32_t base = (t5_smem_u32(t5_raw) + 1023u) & ~1023u;
   const uint32_t sQ = base;
   const uint32_t bars = base + kT5QBytes + 2 * kT5WgBytes;
-  // per warpgroup w at bars + 48 w: s_done[2] (one per S buffer, arrival = tcgen05.commit), o_done[2] (the
-  // last-but-one and the last P V, one phase each: a parity wait must never fall two phases behind, so these
-  // two do not share a barrier), ready[2] (one per S buffer, 128 arrivals: P stored, K and V tiles landed)
+  // per warpgroup w, 18 barriers at bars + 144 w:
+  //   s_done[2]  S buffer b holds a complete S (arrival = tcgen05.commit)
+  //   o_done[2]  the last-but-one and the last P V are complete (one phase each: a parity wait must never fall
+  //              two phases behind, so these two do not share a barrier)
+  //   ready[2]   P is stored in S buffer b (128 arrivals)
+  //   kfull[3], vfull[3]    ring slot holds its tile (one arrival by the fetching warp, plus the tile's bytes
+  //                         when it is a tensor-map copy)
+  //   kempty[3], vempty[3]  the product that read the slot is complete (tcgen05.commit)
   auto ring_k = [&](int w) { return base + kT5QBytes + w * kT5WgBytes; };
   auto ring_v = [&](int w) { return ring_k(w) + 3 * kT5KvBytes; };
-  // and kfull[3], vfull[3] (one per ring slot: the tile has landed; one arrival by the thread that started
-  // the fetch, plus the tile's bytes when it is a tensor-map copy)
-  auto bar_s = [&](int w, int buf) { return bars + 96 * w + 8 * buf; };
-  auto bar_o = [&](int w, int which) { return bars + 96 * w + 16 + 8 * which; };
-  auto bar_r = [&](int w, int buf) { return bars + 96 * w + 32 + 8 * buf; };
-  auto bar_kf = [&](int w, int sl) { return bars + 96 * w + 48 + 8 * sl; };
-  auto bar_vf = [&](int w, int sl) { return bars + 96 * w + 72 + 8 * sl; };
-  const uint32_t slot = bars + 192, dead_flag = bars + 200;
+  auto bar_s = [&](int w, int buf) { return bars + 144 * w + 8 * buf; };
+  auto bar_o = [&](int w, int which) { return bars + 144 * w + 16 + 8 * which; };
+  auto bar_r = [&](int w, int buf) { return bars + 144 * w + 32 + 8 * buf; };
+  auto bar_kf = [&](int w, int sl) { return bars + 144 * w + 48 + 8 * sl; };
+  auto bar_vf = [&](int w, int sl) { return bars + 144 * w + 72 + 8 * sl; };
+  auto bar_ke = [&](int w, int sl) { return bars + 144 * w + 96 + 8 * sl; };
+  auto bar_ve = [&](int w, int sl) { return bars + 144 * w + 120 + 8 * sl; };
+  const uint32_t slot = bars + 288, dead_flag = bars + 296;
 
   if (tid == 0) {
-    for (int w = 0; w < 2; ++w)
-      for (int i = 0; i < 2; ++i) {
-        t5_mbar_init(bar_s(w, i), 1);
-        t5_mbar_init(bar_o(w, i), 1);
-        t5_mbar_init(bar_r(w, i), 128);
-      }
-    for (int w = 0; w < 2; ++w)
-      for (int i = 0; i < 3; ++i) {
-        t5_mbar_init(bar_kf(w, i), 1);
-        t5_mbar_init(bar_vf(w, i), 1);
-      }
+    for (int w = 0; w < 2; ++w) {
+      for (int i = 0; i < 18; ++i) t5_mbar_init(bars + 144 * w + 8 * i, (i == 4 || i == 5) ? 128 : 1);  // 4, 5: ready
+    }
     t5_sts_u32(dead_flag, 0);
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
@@ -227,46 +228,10 @@ prefill_attn_tc5_kernel(const uint16_t* __restrict__ q, long long q_sn, long lon
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(slot), "r"(kT5Cols) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
   }
-
-  const uint16_t* kpre = k_prefix + hk * p_sh + (long long)prefix_start * p_sn;
-  const uint16_t* vpre = v_prefix + hk * p_sh + (long long)prefix_start * p_sn;
-  const uint16_t* kown = k + (long long)seq_start * k_sn + hk * k_sh;
-  const uint16_t* vown = v + (long long)seq_start * v_sn + hk * v_sh;
-  // A warpgroup's block h is block wg + 2h of the tile; it lives in slot h % 3 of that warpgroup's ring.
-  // Full tiles come by tensor-map copies started by the warpgroup's first thread (two boxes of 64 rows x 64
-  // channels, swizzled by the copy engine into the layout described above).  A prefix block that is not full is
-  // copied by all 128 threads with cp.async instead, because the rows behind a prefix may be uninitialised
-  // memory and have to be zero in shared memory (0 x NaN would poison O); so is every prefix block when the
-  // caller gave no row capacity for the prefix tensors, and every tile of the prologue (use_tma = false).
-  auto fetch = [&](int h, bool is_v, bool use_tma) {
-    const int kb = wg + 2 * h, sl = h % 3;
-    const uint32_t dst = (is_v ? ring_v(wg) : ring_k(wg)) + sl * kT5KvBytes;
-    const uint32_t full = is_v ? bar_vf(wg, sl) : bar_kf(wg, sl);
-    const bool pre = kb < nb_pre;
-    const int j0 = pre ? kb * kT5Keys : (kb - nb_pre) * kT5Keys;
-    const int count = min(kT5Keys, (pre ? prefix_len : own_keys) - j0);
-    if (use_tma && (!pre || (prefix_tma && count == kT5Keys))) {
-      if (wt == 0) {
-        t5_mbar_expect_tx(full, kT5KvBytes);
-        const CUtensorMap* map = pre ? (is_v ? &tm_vp : &tm_kp) : (is_v ? &tm_v : &tm_k);
-        const int row = pre ? prefix_start + j0 : seq_start + j0;
-        for (int cb = 0; cb < 2; ++cb)
-          t5_tma_3d(dst + cb * (kT5Keys * 128), map, 64 * cb, pre ? row : hk, pre ? hk : row, full);
-      }
-    } else {
-      const uint16_t* src = pre ? (is_v ? vpre : kpre) + (long long)j0 * p_sn
-                                : (is_v ? vown + (long long)j0 * v_sn : kown + (long long)j0 * k_sn);
-      t5_load_tile<128, kT5Keys>(dst, src, pre ? p_sn : (is_v ? v_sn : k_sn), count, wt);
-      if (wt == 0) t5_mbar_arrive(full);  // keeps the slot's phases in step; the data is covered by `ready`
-    }
-  };
   if (wg < 2) {
     // Q rows past the end of the packed batch are zero-filled; rows of other entries inside the tile are
     // read and computed but never stored.
     t5_load_tile<256, kT5Tile>(sQ, q + (long long)row0 * q_sn + hq * q_sh, q_sn, min(kT5Tile, N - row0), tid);
-    for (int h = 0; h < 3; ++h)
-      if (h < n_mine) fetch(h, false, false);
-    if (n_mine > 0) fetch(0, true, false);
     t5_commit_group();
     t5_wait_group<0>();
     t5_fence_async_smem();
@@ -277,61 +242,107 @@ prefill_attn_tc5_kernel(const uint16_t* __restrict__ q, long long q_sn, long lon
   const uint32_t tmem = t5_lds_u32(slot);
   bool dead = false;
 
-  if (wg == 2) {
-    // ---- the issuing warp: one lane queues every product of the CTA, serving the warpgroups in turn
-    if (tid == 256) {
+  if (warp >= 9) {
+    // ---- a fetching warp: streams the K and V tiles of warpgroup w into its rings.  Block h of the warpgroup
+    // is block w + 2h of the tile and lives in slot h % 3.  Full tiles come by tensor-map copies started by
+    // lane 0 (two boxes of 64 rows x 64 channels, swizzled by the copy engine into the layout described
+    // above).  A prefix block that is not full is copied by the warp's 32 lanes with cp.async instead, because
+    // the rows behind a prefix may be uninitialised memory and have to be zero in shared memory (0 x NaN would
+    // poison O); so is every prefix block when the caller gave no row capacity for the prefix tensors.
+    const int w = warp - 9, n = n_blk[w];
+    const uint16_t* kpre = k_prefix + hk * p_sh + (long long)prefix_start * p_sn;
+    const uint16_t* vpre = v_prefix + hk * p_sh + (long long)prefix_start * p_sn;
+    const uint16_t* kown = k + (long long)seq_start * k_sn + hk * k_sh;
+    const uint16_t* vown = v + (long long)seq_start * v_sn + hk * v_sh;
+    bool live = true;
+    for (int h = 0; h < n && live; ++h) {
+      const int kb = w + 2 * h, sl = h % 3;
+      const bool pre = kb < nb_pre;
+      const int j0 = pre ? kb * kT5Keys : (kb - nb_pre) * kT5Keys;
+      const int count = min(kT5Keys, (pre ? prefix_len : own_keys) - j0);
+      const bool tma = !pre || (prefix_tma && count == kT5Keys);
+      const int row = pre ? prefix_start + j0 : seq_start + j0;
+      for (int is_v = 0; is_v < 2 && live; ++is_v) {
+        const uint32_t dst = (is_v ? ring_v(w) : ring_k(w)) + sl * kT5KvBytes;
+        const uint32_t full = is_v ? bar_vf(w, sl) : bar_kf(w, sl), empty = is_v ? bar_ve(w, sl) : bar_ke(w, sl);
+        // the product that read this slot three blocks ago has completed
+        if (h >= 3 && !t5_mbar_wait(empty, (h / 3 - 1) & 1)) { live = false; break; }
+        if (tma) {
+          if (lane == 0) {
+            t5_mbar_expect_tx(full, kT5KvBytes);
+            const CUtensorMap* map = pre ? (is_v ? &tm_vp : &tm_kp) : (is_v ? &tm_v : &tm_k);
+            t5_tma_3d(dst, map, 0, pre ? row : hk, pre ? hk : row, full);
+            t5_tma_3d(dst + kT5Keys * 128, map, 64, pre ? row : hk, pre ? hk : row, full);
+          }
+        } else {
+          const uint16_t* src = pre ? (is_v ? vpre : kpre) + (long long)j0 * p_sn
+                                    : (is_v ? vown + (long long)j0 * v_sn : kown + (long long)j0 * k_sn);
+          t5_load_tile<32, kT5Keys>(dst, src, pre ? p_sn : (is_v ? v_sn : k_sn), count, lane);
+          t5_commit_group();
+          t5_wait_group<0>();
+          t5_fence_async_smem();
+          __syncwarp();
+          if (lane == 0) t5_mbar_arrive(full);
+        }
+      }
+    }
+    if (!live && lane == 0) t5_sts_u32(dead_flag, 1);
+  } else if (warp == 8) {
+    // ---- the issuing warp: one lane queues every product of the CTA, serving the warpgroups in turn.  The
+    // descriptors are built once; per instruction only the start-address field moves.
+    if (lane == 0) {
+      const uint64_t dq = t5_desc(sQ, 16, 1024);
+      const uint64_t dk[2] = {t5_desc(ring_k(0), 16, 1024), t5_desc(ring_k(1), 16, 1024)};
+      const uint64_t dv[2] = {t5_desc(ring_v(0), kT5Keys * 128, 1024), t5_desc(ring_v(1), kT5Keys * 128, 1024)};
       bool live = true;
-      auto issue_s = [&](int w, int h) {  // S(h) = Q K(h)^T into S buffer h & 1 of warpgroup w, then the arrival
-        const uint32_t kt = ring_k(w) + (h % 3) * kT5KvBytes;
-        if (!t5_mbar_wait(bar_kf(w, h % 3), (h / 3) & 1)) { t5_sts_u32(dead_flag, 1); live = false; return; }
+      auto issue_s = [&](int w, int h) {  // S(h) = Q K(h)^T into S buffer h & 1 of warpgroup w, then the arrivals
+        const int sl = h % 3;
+        if (!t5_mbar_wait(bar_kf(w, sl), (h / 3) & 1)) { live = false; return; }
+        const uint64_t kd = dk[w] + (uint64_t)(sl * (kT5KvBytes >> 4));
+        const uint32_t d = tmem + 256 * w + 64 * (h & 1);
 #pragma unroll
         for (int j = 0; j < 8; ++j)  // 16 channels per instruction
-          t5_mma_ss(tmem + 256 * w + 64 * (h & 1), t5_desc(sQ + (j >> 2) * (kT5Tile * 128) + (j & 3) * 32, 16, 1024),
-                    t5_desc(kt + (j >> 2) * (kT5Keys * 128) + (j & 3) * 32, 16, 1024), kT5IdescQK, j > 0);
+          t5_mma_ss(d, dq + (uint64_t)(((j >> 2) * (kT5Tile * 128) + (j & 3) * 32) >> 4),
+                    kd + (uint64_t)(((j >> 2) * (kT5Keys * 128) + (j & 3) * 32) >> 4), kT5IdescQK, j > 0);
         t5_mma_commit(bar_s(w, h & 1));
+        t5_mma_commit(bar_ke(w, sl));
       };
       for (int h = 0; h < 2; ++h)
         for (int w = 0; w < 2; ++w)
-          if (h < n_blk[w]) issue_s(w, h);
+          if (h < n_blk[w] && live) issue_s(w, h);
       for (int h = 0; h < n_blk[0] && live; ++h) {
-        for (int w = 0; w < 2; ++w) {
+        for (int w = 0; w < 2 && live; ++w) {
           if (h >= n_blk[w]) continue;
-          // P(h) is stored and V(h), K(h+2) have landed
-          if (!t5_mbar_wait(bar_r(w, h & 1), (h >> 1) & 1) || !t5_mbar_wait(bar_vf(w, h % 3), (h / 3) & 1)) {
-            t5_sts_u32(dead_flag, 1);
+          const int sl = h % 3;
+          // P(h) is stored and V(h) has landed
+          if (!t5_mbar_wait(bar_r(w, h & 1), (h >> 1) & 1) || !t5_mbar_wait(bar_vf(w, sl), (h / 3) & 1)) {
             live = false;
             break;
           }
           t5_fence_after();
-          const uint32_t vt = ring_v(w) + (h % 3) * kT5KvBytes, tw = tmem + 256 * w;
+          const uint64_t vd = dv[w] + (uint64_t)(sl * (kT5KvBytes >> 4));
+          const uint32_t tw = tmem + 256 * w;
 #pragma unroll
           for (int j = 0; j < 4; ++j)  // 16 keys per instruction: 8 columns of packed P, 2 KB of V rows
-            t5_mma_ts(tw + 128, tw + 64 * (h & 1) + 8 * j, t5_desc(vt + j * 2048, kT5Keys * 128, 1024), kT5IdescPV,
-                      (h > 0) || (j > 0));
+            t5_mma_ts(tw + 128, tw + 64 * (h & 1) + 8 * j, vd + (uint64_t)(j * (2048 >> 4)), kT5IdescPV, (h > 0) || (j > 0));
+          t5_mma_commit(bar_ve(w, sl));
           if (h + 2 < n_blk[w]) issue_s(w, h + 2);  // executes behind P V(h): it overwrites the columns P(h) is read from
           else t5_mma_commit(bar_o(w, h + 1 < n_blk[w] ? 0 : 1));  // the last-but-one / the last P V of the warpgroup
-          if (!live) break;
         }
       }
+      if (!live) t5_sts_u32(dead_flag, 1);
     }
   } else {
-    const uint32_t lane_base = (uint32_t)(((tid >> 5) & 3) * 32) << 16;
+    const int n_mine = n_blk[wg];
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     const uint32_t tS = tmem + 256 * wg + lane_base, tO = tS + 128;  // this thread's lane
     const int my_keys = min(own_keys, row0 + wt - seq_start + 1);  // own-chunk keys this row may see
     const int first_keys = min(own_keys, row0 - seq_start + 1);    // ... and the tile's first row
     float m_ref = -INFINITY, l = 0.f;  // offset of the exponentials (log2 units, scaled), running sum
     bool ok = true;
     for (int h = 0; h < n_mine && ok; ++h) {
-      // S(h) is complete, and with it everything queued before it, P V(h-2) included: the slots of K(h) and
-      // V(h-2) are free.  Fetch K(h+3) and V(h+1) into them (an empty group keeps the count uniform).
-      ok = t5_mbar_wait(bar_s(wg, h & 1), (h >> 1) & 1);
+      ok = t5_mbar_wait(bar_s(wg, h & 1), (h >> 1) & 1);  // S(h) is complete
       t5_fence_after();
-      if (ok) {
-        if (h + 3 < n_mine) fetch(h + 3, false, true);
-        if (h + 1 < n_mine) fetch(h + 1, true, true);
-      }
-      t5_commit_group();
-
       // ---- softmax of this thread's row
       const int kb = wg + 2 * h;
       const bool pre = kb < nb_pre;
@@ -392,18 +403,12 @@ prefill_attn_tc5_kernel(const uint16_t* __restrict__ q, long long q_sn, long lon
       l += (ps4[0] + ps4[1]) + (ps4[2] + ps4[3]);
       t5_st32(tS + 64 * (h & 1), pk);  // P over the first 32 columns of this S buffer
       asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
-      // V(h) and K(h+2) have landed (only the group issued above may still be in flight): hand over to the
-      // issuing warp
-      t5_wait_group<1>();
-      t5_fence_async_smem();
       t5_fence_before();
-      if (ok) t5_mbar_arrive(bar_r(wg, h & 1));
+      if (ok) t5_mbar_arrive(bar_r(wg, h & 1));  // hand P(h) to the issuing warp
     }
-    t5_wait_group<0>();
     if (n_mine > 0 && ok) ok = t5_mbar_wait(bar_o(wg, 1), 0);  // the last P V
     t5_fence_after();
     if (!ok) t5_sts_u32(dead_flag, 1);
-    // kept for the merge below
     m_ref_keep = m_ref;
     l_keep = l;
   }
@@ -421,7 +426,7 @@ prefill_attn_tc5_kernel(const uint16_t* __restrict__ q, long long q_sn, long lon
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
       uint32_t w[32];
-      if (n_mine > 0 && !dead) {
+      if (n_blk[1] > 0 && !dead) {
         t5_ld32(tO + 32 * c, w);
       } else {
 #pragma unroll
