@@ -3,13 +3,13 @@
 // attention of the prefilling entries over [dequantized prefix | own chunk], replacing
 // prefill_attention_kernel (qwen3-1.7b/kernels.py:987-1126).
 //
-// One CTA owns 128 query rows of one q head and runs eleven warps in three roles:
+// One CTA owns 128 query rows of one q head and runs twelve warps in three roles:
 //   warps 0-3 and 4-7   two softmax warpgroups.  The keys of the tile are cut into blocks of 64 and dealt
 //                       alternately to the two; each keeps its own running (offset, sum, O) and the two are
 //                       merged at the end.  Thread t of a warpgroup owns query row t = lane t of tensor
 //                       memory: every row-wise softmax quantity lives in one thread, no shuffles.
-//   warp 8              one lane issues every tcgen05.mma of the CTA.
-//   warps 9 and 10      fetch the K and V tiles of warpgroup 0 and 1 (tensor-map copies started by one lane).
+//   warps 8 and 9       one lane of each issues every tcgen05.mma of warpgroup 0 and 1.
+//   warps 10 and 11     fetch the K and V tiles of warpgroup 0 and 1 (tensor-map copies started by one lane).
 // Per key block h of a warpgroup:
 //   S(h) = Q K^T   8 x tcgen05.mma (M128 N64 K16, bf16 -> fp32), Q and K from shared memory, into one of the
 //                  warpgroup's two S buffers (64 tensor-memory columns each)
@@ -49,7 +49,7 @@
 
 namespace b200kv {
 
-constexpr int kT5Threads = 352;                       // two softmax warpgroups, one warp issuing the products, two fetching tiles
+constexpr int kT5Threads = 384;                       // two softmax warpgroups, two warps issuing products, two fetching tiles
 constexpr int kT5Tile = 128;                         // query rows per CTA
 constexpr int kT5Keys = 64;                          // keys per block
 constexpr uint32_t kT5QBytes = kT5Tile * kD * 2;     // Q tile: 32 KB, two 64-channel blocks of 16 KB
@@ -191,8 +191,8 @@ prefill_attn_tc5_kernel(const uint16_t* __restrict__ q, long long q_sn, long lon
   const int nb = nb_pre + nb_own;
 
   float m_ref_keep = -INFINITY, l_keep = 0.f;
-  // roles: warps 0-3 and 4-7 = softmax warpgroups 0 and 1, warp 8 = issues every product, warps 9 and 10 =
-  // fetch the K and V tiles of warpgroup 0 and 1
+  // roles: warps 0-3 and 4-7 = softmax warpgroups 0 and 1, warps 8 and 9 = issue the products of warpgroup 0
+  // and 1, warps 10 and 11 = fetch the K and V tiles of warpgroup 0 and 1
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, wg = tid >> 7, wt = tid & 127;
   const int n_blk[2] = {(nb + 1) >> 1, nb >> 1};  // warpgroup w owns blocks w, w + 2, ...
   const uint32_t base = (t5_smem_u32(t5_raw) + 1023u) & ~1023u;
@@ -242,14 +242,14 @@ prefill_attn_tc5_kernel(const uint16_t* __restrict__ q, long long q_sn, long lon
   const uint32_t tmem = t5_lds_u32(slot);
   bool dead = false;
 
-  if (warp >= 9) {
+  if (warp >= 10) {
     // ---- a fetching warp: streams the K and V tiles of warpgroup w into its rings.  Block h of the warpgroup
     // is block w + 2h of the tile and lives in slot h % 3.  Full tiles come by tensor-map copies started by
     // lane 0 (two boxes of 64 rows x 64 channels, swizzled by the copy engine into the layout described
     // above).  A prefix block that is not full is copied by the warp's 32 lanes with cp.async instead, because
     // the rows behind a prefix may be uninitialised memory and have to be zero in shared memory (0 x NaN would
     // poison O); so is every prefix block when the caller gave no row capacity for the prefix tensors.
-    const int w = warp - 9, n = n_blk[w];
+    const int w = warp - 10, n = n_blk[w];
     const uint16_t* kpre = k_prefix + hk * p_sh + (long long)prefix_start * p_sn;
     const uint16_t* vpre = v_prefix + hk * p_sh + (long long)prefix_start * p_sn;
     const uint16_t* kown = k + (long long)seq_start * k_sn + hk * k_sh;
@@ -287,19 +287,22 @@ prefill_attn_tc5_kernel(const uint16_t* __restrict__ q, long long q_sn, long lon
       }
     }
     if (!live && lane == 0) t5_sts_u32(dead_flag, 1);
-  } else if (warp == 8) {
-    // ---- the issuing warp: one lane queues every product of the CTA, serving the warpgroups in turn.  The
-    // descriptors are built once; per instruction only the start-address field moves.
+  } else if (warp >= 8) {
+    // ---- an issuing warp: one lane queues every product of warpgroup w.  The descriptors are built once; per
+    // instruction only the start-address field moves.  The issue of a product blocks while the tensor core's
+    // queue is full, and this lane's waits and commits are not hidden behind its own products; with one
+    // issuing lane per warpgroup the bookkeeping of one overlaps the products of the other.
     if (lane == 0) {
-      const uint64_t dq = t5_desc(sQ, 16, 1024);
-      const uint64_t dk[2] = {t5_desc(ring_k(0), 16, 1024), t5_desc(ring_k(1), 16, 1024)};
-      const uint64_t dv[2] = {t5_desc(ring_v(0), kT5Keys * 128, 1024), t5_desc(ring_v(1), kT5Keys * 128, 1024)};
+      const int w = warp - 8, n = n_blk[w];
+      const uint64_t dq = t5_desc(sQ, 16, 1024), dk = t5_desc(ring_k(w), 16, 1024);
+      const uint64_t dv = t5_desc(ring_v(w), kT5Keys * 128, 1024);
+      const uint32_t tw = tmem + 256 * w;
       bool live = true;
-      auto issue_s = [&](int w, int h) {  // S(h) = Q K(h)^T into S buffer h & 1 of warpgroup w, then the arrivals
+      auto issue_s = [&](int h) {  // S(h) = Q K(h)^T into S buffer h & 1, then the arrivals
         const int sl = h % 3;
         if (!t5_mbar_wait(bar_kf(w, sl), (h / 3) & 1)) { live = false; return; }
-        const uint64_t kd = dk[w] + (uint64_t)(sl * (kT5KvBytes >> 4));
-        const uint32_t d = tmem + 256 * w + 64 * (h & 1);
+        const uint64_t kd = dk + (uint64_t)(sl * (kT5KvBytes >> 4));
+        const uint32_t d = tw + 64 * (h & 1);
 #pragma unroll
         for (int j = 0; j < 8; ++j)  // 16 channels per instruction
           t5_mma_ss(d, dq + (uint64_t)(((j >> 2) * (kT5Tile * 128) + (j & 3) * 32) >> 4),
@@ -308,27 +311,22 @@ prefill_attn_tc5_kernel(const uint16_t* __restrict__ q, long long q_sn, long lon
         t5_mma_commit(bar_ke(w, sl));
       };
       for (int h = 0; h < 2; ++h)
-        for (int w = 0; w < 2; ++w)
-          if (h < n_blk[w] && live) issue_s(w, h);
-      for (int h = 0; h < n_blk[0] && live; ++h) {
-        for (int w = 0; w < 2 && live; ++w) {
-          if (h >= n_blk[w]) continue;
-          const int sl = h % 3;
-          // P(h) is stored and V(h) has landed
-          if (!t5_mbar_wait(bar_r(w, h & 1), (h >> 1) & 1) || !t5_mbar_wait(bar_vf(w, sl), (h / 3) & 1)) {
-            live = false;
-            break;
-          }
-          t5_fence_after();
-          const uint64_t vd = dv[w] + (uint64_t)(sl * (kT5KvBytes >> 4));
-          const uint32_t tw = tmem + 256 * w;
-#pragma unroll
-          for (int j = 0; j < 4; ++j)  // 16 keys per instruction: 8 columns of packed P, 2 KB of V rows
-            t5_mma_ts(tw + 128, tw + 64 * (h & 1) + 8 * j, vd + (uint64_t)(j * (2048 >> 4)), kT5IdescPV, (h > 0) || (j > 0));
-          t5_mma_commit(bar_ve(w, sl));
-          if (h + 2 < n_blk[w]) issue_s(w, h + 2);  // executes behind P V(h): it overwrites the columns P(h) is read from
-          else t5_mma_commit(bar_o(w, h + 1 < n_blk[w] ? 0 : 1));  // the last-but-one / the last P V of the warpgroup
+        if (h < n && live) issue_s(h);
+      for (int h = 0; h < n && live; ++h) {
+        const int sl = h % 3;
+        // P(h) is stored and V(h) has landed
+        if (!t5_mbar_wait(bar_r(w, h & 1), (h >> 1) & 1) || !t5_mbar_wait(bar_vf(w, sl), (h / 3) & 1)) {
+          live = false;
+          break;
         }
+        t5_fence_after();
+        const uint64_t vd = dv + (uint64_t)(sl * (kT5KvBytes >> 4));
+#pragma unroll
+        for (int j = 0; j < 4; ++j)  // 16 keys per instruction: 8 columns of packed P, 2 KB of V rows
+          t5_mma_ts(tw + 128, tw + 64 * (h & 1) + 8 * j, vd + (uint64_t)(j * (2048 >> 4)), kT5IdescPV, (h > 0) || (j > 0));
+        t5_mma_commit(bar_ve(w, sl));
+        if (h + 2 < n) issue_s(h + 2);  // executes behind P V(h): it overwrites the columns P(h) is read from
+        else t5_mma_commit(bar_o(w, h + 1 < n ? 0 : 1));  // the last-but-one / the last P V of the warpgroup
       }
       if (!live) t5_sts_u32(dead_flag, 1);
     }
