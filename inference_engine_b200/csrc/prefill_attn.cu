@@ -71,10 +71,12 @@ prefill_attn_kernel(const uint16_t* __restrict__ q, long long q_sn, long long q_
                     const int32_t* __restrict__ cu_cached, uint16_t* __restrict__ out, long long o_sn, long long o_sh,
                     int N, int G, float scale_log2) {
   extern __shared__ __align__(128) uint8_t pf_smem[];
-  const int tile = blockIdx.x / subs, sub = blockIdx.x - tile * subs;
+  // heads run fastest in the grid: the caller's real tiles come first in tile_start, so every CTA with work
+  // is dispatched before the idle ones behind them
+  const int tile = blockIdx.y / subs, sub = blockIdx.y - tile * subs;
   const int tile_row = tile_start[tile];
   if (tile_row < 0 || tile_row >= N) return;
-  const int hq = blockIdx.y, hk = hq / G;
+  const int hq = blockIdx.x, hk = hq / G;
   const int seq = seq_ids[tile_row];
   const int prefix_start = cu_cached[seq], prefix_len = cu_cached[seq + 1] - prefix_start;
   const int seq_start = cu_seqlens[seq], seq_end = min(cu_seqlens[seq + 1], N);
@@ -242,6 +244,7 @@ extern "C" int b200kv_prefill_attn_variant(const void* q, int64_t q_sn, int64_t 
   for (int64_t s : strides)
     if (s % 8) return B200KV_E_ALIGN;
   if (N == 0 || num_tiles == 0) return B200KV_OK;
+  if ((long long)num_tiles * ((block_m + kPfRows - 1) / kPfRows) > 65535) return B200KV_E_RANGE;  // grid.y
   const float scale_log2 = (1.0f / sqrtf((float)D)) * 1.4426950408889634f;
   // Query tiles of at least 64 rows fill a 128-row tcgen05 tile well enough to pay; smaller ones stay
   // on the 64-row mma.sync kernel.
@@ -255,7 +258,7 @@ extern "C" int b200kv_prefill_attn_variant(const void* q, int64_t q_sn, int64_t 
   const size_t smem = 4 * (size_t)kPfTileBytes;
   if (cudaFuncSetAttribute(prefill_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
     return B200KV_E_LAUNCH;
-  prefill_attn_kernel<<<dim3(num_tiles * subs, Hq), kPfWarps * 32, smem, (cudaStream_t)stream>>>(
+  prefill_attn_kernel<<<dim3(Hq, num_tiles * subs), kPfWarps * 32, smem, (cudaStream_t)stream>>>(
       (const uint16_t*)q, q_sn, q_sh, (const uint16_t*)k, k_sn, k_sh, (const uint16_t*)v, v_sn, v_sh, seq_ids, cu_seqlens,
       tile_start, block_m, subs, (const uint16_t*)k_prefix, (const uint16_t*)v_prefix, p_sh, p_sn, cu_cached,
       (uint16_t*)out, o_sn, o_sh, N, Hq / Hkv, scale_log2);

@@ -175,10 +175,12 @@ prefill_attn_tc5_kernel(const uint16_t* __restrict__ q, long long q_sn, long lon
                         const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                         const __grid_constant__ CUtensorMap tm_kp, const __grid_constant__ CUtensorMap tm_vp, int prefix_tma) {
   extern __shared__ uint8_t t5_raw[];
-  const int tile = blockIdx.x / subs, sub = blockIdx.x - tile * subs;
+  // heads run fastest in the grid: the caller's real tiles come first in tile_start, so every CTA with work
+  // is dispatched before the idle ones behind them
+  const int tile = blockIdx.y / subs, sub = blockIdx.y - tile * subs;
   const int tile_row = tile_start[tile];
   if (tile_row < 0 || tile_row >= N) return;
-  const int hq = blockIdx.y, hk = hq / G;
+  const int hq = blockIdx.x, hk = hq / G;
   const int seq = seq_ids[tile_row];
   const int prefix_start = cu_cached[seq], prefix_len = cu_cached[seq + 1] - prefix_start;
   const int seq_start = cu_seqlens[seq], seq_end = min(cu_seqlens[seq + 1], N);
@@ -215,12 +217,14 @@ prefill_attn_tc5_kernel(const uint16_t* __restrict__ q, long long q_sn, long lon
   auto bar_vf = [&](int w, int sl) { return bars + 144 * w + 72 + 8 * sl; };
   auto bar_ke = [&](int w, int sl) { return bars + 144 * w + 96 + 8 * sl; };
   auto bar_ve = [&](int w, int sl) { return bars + 144 * w + 120 + 8 * sl; };
-  const uint32_t slot = bars + 288, dead_flag = bars + 296;
+  const uint32_t bar_q = bars + 288;  // the Q tile has landed (256 arrivals)
+  const uint32_t slot = bars + 296, dead_flag = bars + 304;
 
   if (tid == 0) {
     for (int w = 0; w < 2; ++w) {
       for (int i = 0; i < 18; ++i) t5_mbar_init(bars + 144 * w + 8 * i, (i == 4 || i == 5) ? 128 : 1);  // 4, 5: ready
     }
+    t5_mbar_init(bar_q, 256);
     t5_sts_u32(dead_flag, 0);
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
@@ -228,19 +232,21 @@ prefill_attn_tc5_kernel(const uint16_t* __restrict__ q, long long q_sn, long lon
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(slot), "r"(kT5Cols) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
   }
+  t5_fence_before();
+  __syncthreads();  // barriers and the tensor-memory base are visible to every role
+  t5_fence_after();
+  const uint32_t tmem = t5_lds_u32(slot);
+  bool dead = false;
   if (wg < 2) {
-    // Q rows past the end of the packed batch are zero-filled; rows of other entries inside the tile are
-    // read and computed but never stored.
+    // The softmax threads copy the Q tile while the fetching warps already stream K and V.  Q rows past the end
+    // of the packed batch are zero-filled; rows of other entries inside the tile are read and computed but
+    // never stored.
     t5_load_tile<256, kT5Tile>(sQ, q + (long long)row0 * q_sn + hq * q_sh, q_sn, min(kT5Tile, N - row0), tid);
     t5_commit_group();
     t5_wait_group<0>();
     t5_fence_async_smem();
+    t5_mbar_arrive(bar_q);
   }
-  t5_fence_before();
-  __syncthreads();
-  t5_fence_after();
-  const uint32_t tmem = t5_lds_u32(slot);
-  bool dead = false;
 
   if (warp >= 10) {
     // ---- a fetching warp: streams the K and V tiles of warpgroup w into its rings.  Block h of the warpgroup
@@ -297,7 +303,7 @@ prefill_attn_tc5_kernel(const uint16_t* __restrict__ q, long long q_sn, long lon
       const uint64_t dq = t5_desc(sQ, 16, 1024), dk = t5_desc(ring_k(w), 16, 1024);
       const uint64_t dv = t5_desc(ring_v(w), kT5Keys * 128, 1024);
       const uint32_t tw = tmem + 256 * w;
-      bool live = true;
+      bool live = t5_mbar_wait(bar_q, 0);
       auto issue_s = [&](int h) {  // S(h) = Q K(h)^T into S buffer h & 1, then the arrivals
         const int sl = h % 3;
         if (!t5_mbar_wait(bar_kf(w, sl), (h / 3) & 1)) { live = false; return; }
@@ -524,7 +530,7 @@ int launch_prefill_attn_tc5(const uint16_t* q, long long q_sn, long long q_sh, c
                    t5_make_map(&tm_vp, v_prefix, prefix_rows, Hkv, p_sn, p_sh, kT5Keys, 1);
   if (!prefix_tma) { tm_kp = tm_k; tm_vp = tm_v; }
   const int subs = (block_m + kT5Tile - 1) / kT5Tile;
-  prefill_attn_tc5_kernel<<<dim3(num_tiles * subs, Hq), kT5Threads, kT5Smem, stream>>>(
+  prefill_attn_tc5_kernel<<<dim3(Hq, num_tiles * subs), kT5Threads, kT5Smem, stream>>>(
       q, q_sn, q_sh, k, k_sn, k_sh, v, v_sn, v_sh, seq_ids, cu_seqlens, tile_start, block_m, subs, k_prefix, v_prefix, p_sh,
       p_sn, cu_cached, out, o_sn, o_sh, N, Hq / Hkv, scale_log2, status, tm_k, tm_v, tm_kp, tm_vp, prefix_tma);
   return cudaGetLastError() == cudaSuccess ? B200KV_OK : B200KV_E_LAUNCH;

@@ -289,43 +289,65 @@ quantize_prefill_kernel(const uint16_t* __restrict__ k, long long k_sn, long lon
 }
 
 // ------------------------------------------------------------------ prefix dequant
-// grid (num_entries, Hkv, ceil(capacity/64)), 256 threads: 8 warps x 8 tokens, one warp per
-// token row.  kernels.py:868-932.
-constexpr int kDequantTile = 64;
+// kernels.py:868-932.  The output rows are packed end to end (cu_cached), so the grid runs over OUTPUT rows: one warp per row, all
+// kv heads (a grid over (entry, token tile) would launch one mostly idle CTA column per entry of the batch).
+// The warp finds the row's entry and page once; the loads of the heads are independent of one another, so they
+// are all in flight together.
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
-dequant_prefix_kernel(CacheView c, const int32_t* __restrict__ cu_cached, uint16_t* __restrict__ k_out,
+dequant_prefix_kernel(CacheView c, const int32_t* __restrict__ cu_cached, int num_entries, uint16_t* __restrict__ k_out,
                       uint16_t* __restrict__ v_out, long long o_sh, long long o_sn, int capacity, int32_t* status) {
-  const int b = blockIdx.x, h = blockIdx.y;
-  const int out_start = cu_cached[b];
-  const int n = cu_cached[b + 1] - out_start;
-  const int t0 = blockIdx.z * kDequantTile;
-  if (t0 >= n) return;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int page0 = lookup_page(c, b, 0, status);
-  if (page0 < 0) return;
-  float cal[4];
-  load4_f32(c.k_cal + page0 * c.cstride_page + h * c.cstride_head, lane, cal);
-  for (int t = t0 + warp; t < min(t0 + kDequantTile, n); t += kWarpsPerBlock) {
-    if (out_start + t >= capacity) break;
-    const int page = lookup_page(c, b, t, status);
-    if (page < 0) continue;
-    const int row = t % c.page_size;
-    const long long coff = page * c.stride_page + h * c.stride_head + row * c.stride_tok + 4 * lane;
-    const long long soff = page * c.sstride_page + h * c.sstride_head + row;
-    const uint32_t kc = *reinterpret_cast<const uint32_t*>(c.k + coff);
-    const uint32_t vc = *reinterpret_cast<const uint32_t*>(c.v + coff);
-    const float ks = c.k_scale[soff], vs = c.v_scale[soff];
-    float ko[4], vo[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      float kf = (float)(int)(int8_t)((kc >> (8 * i)) & 0xFFu);
-      float vf = (float)(int)(int8_t)((vc >> (8 * i)) & 0xFFu);
-      ko[i] = __fmul_rn(__fmul_rn(kf, ks), cal[i]);
-      vo[i] = __fmul_rn(vf, vs);
+  const int r = blockIdx.x * kWarpsPerBlock + warp;
+  if (r >= min(cu_cached[num_entries], capacity)) return;
+  // the entry b with cu_cached[b] <= r < cu_cached[b+1] (entries without a prefix never match)
+  int b = -1, start = 0;
+  for (int e0 = 0; e0 < num_entries && b < 0; e0 += 32) {
+    const int e = e0 + lane;
+    const int lo = e < num_entries ? cu_cached[e] : 0, hi = e < num_entries ? cu_cached[e + 1] : 0;
+    const unsigned hit = __ballot_sync(0xffffffffu, e < num_entries && lo <= r && r < hi);
+    if (hit) {
+      const int src = __ffs(hit) - 1;
+      b = e0 + src;
+      start = __shfl_sync(0xffffffffu, lo, src);
     }
-    const long long ooff = h * o_sh + (long long)(out_start + t) * o_sn;
-    store4_bf16(k_out + ooff, lane, ko);
-    store4_bf16(v_out + ooff, lane, vo);
+  }
+  if (b < 0) return;
+  const int t = r - start;
+  const int page0 = lookup_page(c, b, 0, status);
+  const int page = lookup_page(c, b, t, status);
+  if (page0 < 0 || page < 0) return;
+  const int row = t % c.page_size;
+  constexpr int kHeadsAtOnce = 4;
+  for (int h0 = 0; h0 < c.Hkv; h0 += kHeadsAtOnce) {
+    uint32_t kc[kHeadsAtOnce], vc[kHeadsAtOnce];
+    float ks[kHeadsAtOnce], vs[kHeadsAtOnce], cal[kHeadsAtOnce][4];
+#pragma unroll
+    for (int i = 0; i < kHeadsAtOnce; ++i) {
+      const int h = min(h0 + i, c.Hkv - 1);
+      const long long coff = page * c.stride_page + h * c.stride_head + row * c.stride_tok + 4 * lane;
+      const long long soff = page * c.sstride_page + h * c.sstride_head + row;
+      kc[i] = *reinterpret_cast<const uint32_t*>(c.k + coff);
+      vc[i] = *reinterpret_cast<const uint32_t*>(c.v + coff);
+      ks[i] = c.k_scale[soff];
+      vs[i] = c.v_scale[soff];
+      load4_f32(c.k_cal + page0 * c.cstride_page + h * c.cstride_head, lane, cal[i]);
+    }
+#pragma unroll
+    for (int i = 0; i < kHeadsAtOnce; ++i) {
+      const int h = h0 + i;
+      if (h >= c.Hkv) break;
+      float ko[4], vo[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float kf = (float)(int)(int8_t)((kc[i] >> (8 * j)) & 0xFFu);
+        const float vf = (float)(int)(int8_t)((vc[i] >> (8 * j)) & 0xFFu);
+        ko[j] = __fmul_rn(__fmul_rn(kf, ks[i]), cal[i][j]);
+        vo[j] = __fmul_rn(vf, vs[i]);
+      }
+      const long long ooff = h * o_sh + (long long)r * o_sn;
+      store4_bf16(k_out + ooff, lane, ko);
+      store4_bf16(v_out + ooff, lane, vo);
+    }
   }
 }
 
@@ -416,11 +438,8 @@ extern "C" int b200kv_dequant_prefix(const b200kv_cache* cache, const b200kv_tab
   if (num_entries < 0 || capacity < 0) return B200KV_E_SHAPE;
   if (!aligned(k_out, 8) || !aligned(v_out, 8) || !stride_ok4(o_sh) || !stride_ok4(o_sn)) return B200KV_E_ALIGN;
   if (num_entries == 0 || capacity == 0) return B200KV_OK;
-  long long max_tokens = (long long)table->max_pages * cache->page_size;
-  if (max_tokens > capacity) max_tokens = capacity;
-  dim3 grid(num_entries, cache->num_kv_heads, (unsigned)((max_tokens + kDequantTile - 1) / kDequantTile));
-  if (grid.z > 65535u) return B200KV_E_RANGE;
+  dim3 grid((unsigned)((capacity + kWarpsPerBlock - 1) / kWarpsPerBlock));
   dequant_prefix_kernel<<<grid, kWarpsPerBlock * 32, 0, (cudaStream_t)stream>>>(
-      make_view(cache, table), cu_cached, (uint16_t*)k_out, (uint16_t*)v_out, o_sh, o_sn, capacity, status);
+      make_view(cache, table), cu_cached, num_entries, (uint16_t*)k_out, (uint16_t*)v_out, o_sh, o_sn, capacity, status);
   return launch_status();
 }
