@@ -411,6 +411,87 @@ def run_sharded(args):
         dist.destroy_process_group()
 
 
+def run_path(args):
+    """--path: each op of the mixed step's attention path timed alone (seed 3 shapes: 32 decoding sequences
+    with contexts ~U[128,4096] + one 992-row chunk on a prior context of 0 and of 3072 tokens, 34 entries,
+    1024 packed rows), then all six in the engine's call order.  CUDA graph of 10 calls on 10 distinct layer
+    caches, median of `steps` replays, microseconds per call."""
+    import torch
+
+    from inference_engine_b200 import kernels as K
+    from inference_engine_b200 import scaffold as S
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    n_dec, chunk, n_tokens, reps = 32, 992, 1024, 10
+    for prior in (0, 3072):
+        gen = torch.Generator().manual_seed(3)
+        dgen = torch.Generator(device=dev).manual_seed(3)
+        ctx = torch.randint(128, 4097, (n_dec,), generator=gen).tolist()
+        plan = S.plan_step(ctx, [(prior, chunk)], n_tokens, n_dec + 2)
+        table, pages = S.assign_pages(plan, PAGE, (4096 + PAGE) // PAGE + 1, generator=gen)
+        inp = S.upload_step(plan, table, [0] * n_tokens, dev)
+        caches = []
+        for _ in range(reps):
+            c = K.make_layer_cache(pages, HKV, PAGE, D, device=dev)
+            c.k.copy_(torch.randint(-127, 128, c.k.shape, generator=dgen, device=dev, dtype=torch.int8))
+            c.v.copy_(torch.randint(-127, 128, c.v.shape, generator=dgen, device=dev, dtype=torch.int8))
+            c.k_scale.uniform_(0.01, 0.04, generator=dgen)
+            c.v_scale.uniform_(0.01, 0.04, generator=dgen)
+            caches.append(c)
+        cap = max(prior, 16)
+        prefix = S.PrefixScratch(torch.empty(HKV, cap, D, device=dev, dtype=torch.bfloat16),
+                                 torch.empty(HKV, cap, D, device=dev, dtype=torch.bfloat16), inp.cu_cached)
+        qkv = torch.randn(n_tokens, (HQ + 2 * HKV) * D, generator=dgen, device=dev).to(torch.bfloat16)
+        q, k, v = qkv.split([HQ * D, HKV * D, HKV * D], dim=-1)
+        q, k, v = q.view(-1, HQ, D), k.view(-1, HKV, D), v.view(-1, HKV, D)
+        qw = torch.ones(D, device=dev, dtype=torch.bfloat16)
+        inv = 1e6 ** (-torch.arange(0, D, 2, dtype=torch.float32, device=dev) / D)
+        ang = inp.positions[:, None, None] * inv[None, None, :]
+        cos, sin = ang.cos().to(torch.bfloat16), ang.sin().to(torch.bfloat16)
+        E, tab, cl, nd = inp.block_table.shape[0], inp.block_table, inp.cached_lens, inp.num_decoding
+        q_p, k_p = K.fused_norm_rope_prefill(q, k, qw, qw, cos, sin, 1e-6)
+        out = torch.empty(n_tokens, HQ, D, device=dev, dtype=torch.bfloat16)
+        q_d = K.fused_rope_kv_decode(q[:E], k[:E], v[:E], qw, qw, cos[:E], sin[:E], tab, caches[0], cl, nd, 1e-6)
+        ops = {
+            "fused_norm_rope_prefill": lambda c: K.fused_norm_rope_prefill(q, k, qw, qw, cos, sin, 1e-6),
+            "quantize_kv_prefill": lambda c: K.quantize_kv_prefill(k_p, v, inp.cu_seqlens, tab, cl, nd, c),
+            "dequantize_kv_prefix": lambda c: K.dequantize_kv_prefix(c, prefix.cu_cached, tab, prefix.k, prefix.v),
+            "prefill_attention": lambda c: K.prefill_attention(q_p, k_p, v, inp.seq_ids, inp.cu_seqlens, inp.tile_start,
+                                                               prefix.k, prefix.v, prefix.cu_cached, 128),
+            "fused_rope_kv_decode": lambda c: K.fused_rope_kv_decode(q[:E], k[:E], v[:E], qw, qw, cos[:E], sin[:E], tab, c,
+                                                                     cl, nd, 1e-6),
+            "decode_attention": lambda c: K.decode_attention(q_d, c, cl, tab, nd, D ** -0.5, out=out),
+            "all six in the engine's order": lambda c: S.attention_ops(q, k, v, qw, qw, cos, sin, c, inp, cl, tab, nd, prefix),
+        }
+        line = {"case": "attention path of the mixed step, per op", "prior_context": prior, "us_per_call": {}}
+        for name, fn in ops.items():
+            def call():
+                for c in caches:
+                    fn(c)
+            call()
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                call()
+            for _ in range(3):
+                g.replay()
+            torch.cuda.synchronize()
+            ts = []
+            for _ in range(args.steps):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                g.replay()
+                e1.record()
+                torch.cuda.synchronize()
+                ts.append(e0.elapsed_time(e1) * 1e3 / reps)
+            line["us_per_call"][name] = round(statistics.median(ts), 1)
+        line["status"] = K.check_status(dev)
+        print(json.dumps(line), flush=True)
+        del caches
+        torch.cuda.empty_cache()
+
+
 def run_prefill(args):
     """--prefill: the chunked-prefill attention kernel alone (seed 3 shapes): one 992-row chunk on a
     prior context of 0/1024/2048/3072 tokens, 16 q heads over 8 kv heads, block_m 128, bf16 ~N(0,1).
@@ -632,7 +713,7 @@ def run_write(args):
             us = timed(prefill_flavour)
             print(json.dumps({"case": "fused_norm_rope_prefill + quantize_kv_prefill (first chunk)", "T": T,
                               "us_per_call": round(us, 2), "gbs": round(T * WRITE_BYTES_PER_TOKEN / us / 1e3, 1),
-                              "kernels_per_call": 4}), flush=True)
+                              "kernels_per_call": 3}), flush=True)
 
 
 def run_sweep(args):
@@ -715,6 +796,7 @@ def main():
     ap.add_argument("--no-early-start", action="store_true", help="launch decode attention without programmatic early start")
     ap.add_argument("--sharded", action="store_true", help="sequence-sharded decode over log-uniform contexts (torchrun for N > 1)")
     ap.add_argument("--seqs", type=int, default=2048, help="--sharded: concurrent sequences over all GPUs")
+    ap.add_argument("--path", action="store_true", help="each op of the mixed step's attention path timed alone")
     ap.add_argument("--prefill", action="store_true", help="chunked-prefill attention kernel alone, both kernels")
     ap.add_argument("--mixed", action="store_true", help="chunked-prefill + decode step inside the decoder scaffold")
     ap.add_argument("--write", action="store_true", help="quantize-on-write microbench (T = 1, 64, 1024)")
@@ -728,6 +810,8 @@ def main():
         run_mixed(args)
     elif args.prefill:
         run_prefill(args)
+    elif args.path:
+        run_path(args)
     elif args.sharded:
         run_sharded(args)
     elif args.impl == "reference":

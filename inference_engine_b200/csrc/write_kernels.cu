@@ -210,44 +210,38 @@ __device__ __forceinline__ bool is_first_chunk(int b, int nd, const int32_t* cu,
   return b >= nd && cu[b + 1] > cu[b] && cached_lens[b] == 0;
 }
 
-// Phase 0: calibration rows of first-chunk entries start at the floor 1e-3 (kernels.py:765).
-// grid (num_entries), 256 threads.
-__global__ void calib_init_kernel(CacheView c, const int32_t* __restrict__ cu, const int32_t* __restrict__ cached_lens,
-                                  const int32_t* __restrict__ num_decoding, int32_t* status) {
-  const int b = blockIdx.x;
-  if (!is_first_chunk(b, *num_decoding, cu, cached_lens)) return;
-  const int page0 = lookup_page(c, b, 0, status);
-  if (page0 < 0) return;
-  for (int i = threadIdx.x; i < c.Hkv * kD; i += blockDim.x)
-    c.k_cal[page0 * c.cstride_page + (i / kD) * c.cstride_head + (i % kD)] = 1e-3f;
-}
-
-// Phase 1: per-channel max |k| over each first chunk (kernels.py:766-776).  max is exact and
-// order-independent, and the values are non-negative, so an integer atomicMax on the float
-// bits reproduces the serial result.  grid (ceil(N/32), Hkv), 128 threads (one per channel).
-constexpr int kCalibRows = 32;
-__global__ void __launch_bounds__(kD)
-calib_max_kernel(const uint16_t* __restrict__ k, long long k_sn, long long k_sh, CacheView c,
-                 const int32_t* __restrict__ cu, int num_entries, const int32_t* __restrict__ cached_lens,
+// Phase 1: calibration of first-chunk entries: cal[d] = max(1e-3, max_t |k[t,d]|) over the chunk's rows
+// (kernels.py:764-780).  max is exact and order-independent, so any split of the rows reproduces the serial
+// result.  grid (num_entries, Hkv), 1024 threads: 32 row groups x 32 lanes of 4 channels (8-byte loads, eight
+// rows in flight per thread), reduced through shared memory; entries that are not on their first chunk leave
+// at once.
+constexpr int kCalibGroups = 32;
+__global__ void __launch_bounds__(kCalibGroups * 32)
+calibrate_kernel(const uint16_t* __restrict__ k, long long k_sn, long long k_sh, CacheView c,
+                 const int32_t* __restrict__ cu, const int32_t* __restrict__ cached_lens,
                  const int32_t* __restrict__ num_decoding, int N, int32_t* status) {
-  const int h = blockIdx.y, d = threadIdx.x;
-  const int r0 = blockIdx.x * kCalibRows;
-  const int r1 = min(r0 + kCalibRows, min(N, cu[num_entries]));
-  if (r0 >= r1) return;
-  const int nd = *num_decoding;
-  int b = entry_of_row(cu, num_entries, r0);
-  int r = r0;
-  while (r < r1) {
-    while (cu[b + 1] <= r) ++b;  // skip empty entries; r < cu[num_entries] keeps b in range
-    const int end = min(r1, cu[b + 1]);
-    if (is_first_chunk(b, nd, cu, cached_lens)) {
-      float m = 0.0f;
-      for (int t = r; t < end; ++t) m = fmaxf(m, fabsf(bf16_bits_to_float(k[t * k_sn + h * k_sh + d])));
-      const int page0 = lookup_page(c, b, 0, status);
-      if (page0 >= 0)
-        atomicMax(reinterpret_cast<int*>(c.k_cal + page0 * c.cstride_page + h * c.cstride_head + d), __float_as_int(m));
-    }
-    r = end;
+  const int b = blockIdx.x, h = blockIdx.y;
+  if (!is_first_chunk(b, *num_decoding, cu, cached_lens)) return;
+  const int lane = threadIdx.x & 31, g = threadIdx.x >> 5;
+  const int s0 = cu[b], s1 = min(cu[b + 1], N);
+  float m[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 8
+  for (int t = s0 + g; t < s1; t += kCalibGroups) {
+    float x[4];
+    load4_bf16(k + t * k_sn + h * k_sh, lane, x);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) m[i] = fmaxf(m[i], fabsf(x[i]));
+  }
+  __shared__ float part[kCalibGroups][kD];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) part[g][4 * lane + i] = m[i];
+  __syncthreads();
+  if (threadIdx.x < kD) {
+    float r = 1e-3f;
+#pragma unroll
+    for (int i = 0; i < kCalibGroups; ++i) r = fmaxf(r, part[i][threadIdx.x]);
+    const int page0 = lookup_page(c, b, 0, status);
+    if (page0 >= 0) c.k_cal[page0 * c.cstride_page + h * c.cstride_head + threadIdx.x] = r;
   }
 }
 
@@ -420,9 +414,8 @@ extern "C" int b200kv_quantize_prefill(const void* k, int64_t k_sn, int64_t k_sh
   const int Hkv = cache->num_kv_heads;
   CacheView view = make_view(cache, table);
   cudaStream_t s = (cudaStream_t)stream;
-  calib_init_kernel<<<num_entries, 256, 0, s>>>(view, cu_seqlens, cached_lens, num_decoding, status);
-  calib_max_kernel<<<dim3((N + kCalibRows - 1) / kCalibRows, Hkv), kD, 0, s>>>(
-      (const uint16_t*)k, k_sn, k_sh, view, cu_seqlens, num_entries, cached_lens, num_decoding, N, status);
+  calibrate_kernel<<<dim3(num_entries, Hkv), kCalibGroups * 32, 0, s>>>((const uint16_t*)k, k_sn, k_sh, view, cu_seqlens,
+                                                                        cached_lens, num_decoding, N, status);
   quantize_prefill_kernel<<<dim3(N, (2 * Hkv + kWarpsPerBlock - 1) / kWarpsPerBlock), kWarpsPerBlock * 32, 0, s>>>(
       (const uint16_t*)k, k_sn, k_sh, (const uint16_t*)v, v_sn, v_sh, view, cu_seqlens, num_entries, cached_lens,
       num_decoding, status);
