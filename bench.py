@@ -423,6 +423,7 @@ def run_path(args):
 
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
+    K.set_early_start(not args.no_early_start)
     n_dec, chunk, n_tokens, reps = 32, 992, 1024, 10
     for prior in (0, 3072):
         gen = torch.Generator().manual_seed(3)
@@ -562,6 +563,7 @@ def run_mixed(args):
 
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
+    K.set_early_start(not args.no_early_start)
     gen = torch.Generator().manual_seed(3)
     model = S.DecoderScaffold(dev, seed=3)
     n_dec, chunk, n_tokens = 32, 992, 1024

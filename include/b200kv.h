@@ -166,6 +166,17 @@ int b200kv_prefill_attn_variant(const void* q, int64_t q_stride_n, int64_t q_str
                                 int32_t N, int32_t Hq, int32_t Hkv, int32_t D,
                                 int32_t variant, int32_t* status, void* stream);
 
+/* Chained launches (off by default).  While enabled, every kernel of this library is launched with
+ * programmatic stream serialization: it may be brought up while the kernel launched just before it on
+ * the same stream is still running, reads only caller-provided metadata (cu_seqlens, cu_cached,
+ * cached_lens, num_decoding, block table, tile_start, seq_ids) until that kernel has completed, and
+ * touches everything else afterwards.  Enable it only if no kernel that precedes a call of this
+ * library on its stream writes those metadata arrays - true for the reference engine, which uploads
+ * them once per step before the first layer (engine.py:347-356).  Process-wide; has no counterpart
+ * in the reference. */
+void b200kv_set_chained_launch(int enabled);
+int b200kv_get_chained_launch(void);
+
 /* Bytes of fp32 workspace b200kv_decode_attn needs for a batch of B entries on a device with
  * `sm_count` SMs (replaces the three partial buffers of kernels.py:305-311).
  * Contract: the workspace must be ZERO-filled once when it is allocated.  It holds, besides the

@@ -1,6 +1,16 @@
 // Version and error-string entry points of the b200kv C ABI.
 #include "b200kv.h"
 
+#include <atomic>
+
+namespace b200kv {
+static std::atomic<int> g_chained{0};
+bool chained_launch_enabled() { return g_chained.load(std::memory_order_relaxed) != 0; }
+}  // namespace b200kv
+
+extern "C" void b200kv_set_chained_launch(int enabled) { b200kv::g_chained.store(enabled ? 1 : 0, std::memory_order_relaxed); }
+extern "C" int b200kv_get_chained_launch(void) { return b200kv::chained_launch_enabled() ? 1 : 0; }
+
 extern "C" int b200kv_version(void) { return B200KV_VERSION; }
 
 extern "C" const char* b200kv_error_string(int code) {

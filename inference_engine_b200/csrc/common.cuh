@@ -38,6 +38,38 @@ inline CacheView make_view(const b200kv_cache* c, const b200kv_table* t) {
   return w;
 }
 
+// Chained launches (programmatic dependent launch).  Every kernel of the path (a) waits for the kernel launched
+// before it on the stream (pdl_wait) before it reads anything that kernel may have written or writes global
+// memory itself, having read at most caller-provided metadata by then, and (b) tells the stream when the next
+// kernel may be brought up (pdl_trigger).  Both are no-ops for a kernel launched the ordinary way; the launch
+// attribute is only set while b200kv_set_chained_launch(1) is in force.
+bool chained_launch_enabled();
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+// First statement of every kernel.  The trigger may come this early: the next kernel cannot be brought up before
+// every CTA of this grid has executed it (or exited), so it only ever takes resources this grid has no use for
+// any more.  The first CTA of the grid waits at once, on every path: a grid in which no CTA waited could
+// complete before its predecessor, and the kernel after it only waits for THIS grid.
+__device__ __forceinline__ void pdl_enter() {
+  pdl_trigger();
+  if ((blockIdx.x | blockIdx.y | blockIdx.z) == 0) pdl_wait();
+}
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                  Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = chained_launch_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
 
 // Host-side validation shared by the entry points.  Returns B200KV_OK or an error code.

@@ -698,8 +698,9 @@ decode_attn_kernel(const uint16_t* __restrict__ q, long long q_sb, long long q_s
   int* chunk_prefix = reinterpret_cast<int*>(q_s + (kScalar ? kWarps * (kMaxG * kD + kMaxG * kTile) : 0));
 
   // Let a programmatically-dependent successor be scheduled as SMs free up (it waits for this grid
-  // to complete before it touches anything this grid writes).
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  // to complete before it touches anything this grid writes); the first CTA waits for the predecessor
+  // at once, so that this grid can never complete before it.
+  pdl_enter();
   int* lens_s = chunk_prefix + kWarps * 32 + 1;
   int* cta_arrive = lens_s + kSmemLens;  // how many of this CTA's warps have parked a piece in shared memory
   if (threadIdx.x == 0) *cta_arrive = 0;  // ordered before any use by the barriers inside scan_tiles

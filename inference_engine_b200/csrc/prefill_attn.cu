@@ -71,6 +71,7 @@ prefill_attn_kernel(const uint16_t* __restrict__ q, long long q_sn, long long q_
                     const int32_t* __restrict__ cu_cached, uint16_t* __restrict__ out, long long o_sn, long long o_sh,
                     int N, int G, float scale_log2) {
   extern __shared__ __align__(128) uint8_t pf_smem[];
+  pdl_enter();
   // heads run fastest in the grid: the caller's real tiles come first in tile_start, so every CTA with work
   // is dispatched before the idle ones behind them
   const int tile = blockIdx.y / subs, sub = blockIdx.y - tile * subs;
@@ -90,6 +91,7 @@ prefill_attn_kernel(const uint16_t* __restrict__ q, long long q_sn, long long q_
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
   const uint32_t smem0 = pf_smem_u32(pf_smem);
+  pdl_wait();  // q, k, v and the prefix come from the kernels before this one; only metadata was read so far
   const uint16_t* kpre = k_prefix + hk * p_sh + (long long)prefix_start * p_sn;
   const uint16_t* vpre = v_prefix + hk * p_sh + (long long)prefix_start * p_sn;
   const uint16_t* kown = k + (long long)seq_start * k_sn + hk * k_sh;
@@ -258,7 +260,7 @@ extern "C" int b200kv_prefill_attn_variant(const void* q, int64_t q_sn, int64_t 
   const size_t smem = 4 * (size_t)kPfTileBytes;
   if (cudaFuncSetAttribute(prefill_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
     return B200KV_E_LAUNCH;
-  prefill_attn_kernel<<<dim3(Hq, num_tiles * subs), kPfWarps * 32, smem, (cudaStream_t)stream>>>(
+  launch_chained(prefill_attn_kernel, dim3(Hq, num_tiles * subs), dim3(kPfWarps * 32), smem, (cudaStream_t)stream,
       (const uint16_t*)q, q_sn, q_sh, (const uint16_t*)k, k_sn, k_sh, (const uint16_t*)v, v_sn, v_sh, seq_ids, cu_seqlens,
       tile_start, block_m, subs, (const uint16_t*)k_prefix, (const uint16_t*)v_prefix, p_sh, p_sn, cu_cached,
       (uint16_t*)out, o_sn, o_sh, N, Hq / Hkv, scale_log2);

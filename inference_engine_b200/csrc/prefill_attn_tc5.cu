@@ -175,6 +175,7 @@ prefill_attn_tc5_kernel(const uint16_t* __restrict__ q, long long q_sn, long lon
                         const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                         const __grid_constant__ CUtensorMap tm_kp, const __grid_constant__ CUtensorMap tm_vp, int prefix_tma) {
   extern __shared__ uint8_t t5_raw[];
+  pdl_enter();
   // heads run fastest in the grid: the caller's real tiles come first in tile_start, so every CTA with work
   // is dispatched before the idle ones behind them
   const int tile = blockIdx.y / subs, sub = blockIdx.y - tile * subs;
@@ -235,6 +236,7 @@ prefill_attn_tc5_kernel(const uint16_t* __restrict__ q, long long q_sn, long lon
   t5_fence_before();
   __syncthreads();  // barriers and the tensor-memory base are visible to every role
   t5_fence_after();
+  pdl_wait();  // q, k, v and the prefix come from the kernels before this one; only metadata was read so far
   const uint32_t tmem = t5_lds_u32(slot);
   bool dead = false;
   if (wg < 2) {
@@ -530,10 +532,11 @@ int launch_prefill_attn_tc5(const uint16_t* q, long long q_sn, long long q_sh, c
                    t5_make_map(&tm_vp, v_prefix, prefix_rows, Hkv, p_sn, p_sh, kT5Keys, 1);
   if (!prefix_tma) { tm_kp = tm_k; tm_vp = tm_v; }
   const int subs = (block_m + kT5Tile - 1) / kT5Tile;
-  prefill_attn_tc5_kernel<<<dim3(Hq, num_tiles * subs), kT5Threads, kT5Smem, stream>>>(
-      q, q_sn, q_sh, k, k_sn, k_sh, v, v_sn, v_sh, seq_ids, cu_seqlens, tile_start, block_m, subs, k_prefix, v_prefix, p_sh,
-      p_sn, cu_cached, out, o_sn, o_sh, N, Hq / Hkv, scale_log2, status, tm_k, tm_v, tm_kp, tm_vp, prefix_tma);
-  return cudaGetLastError() == cudaSuccess ? B200KV_OK : B200KV_E_LAUNCH;
+  const cudaError_t le = launch_chained(prefill_attn_tc5_kernel, dim3(Hq, num_tiles * subs), dim3(kT5Threads), kT5Smem, stream,
+                                        q, q_sn, q_sh, k, k_sn, k_sh, v, v_sn, v_sh, seq_ids, cu_seqlens, tile_start, block_m, subs,
+                                        k_prefix, v_prefix, p_sh, p_sn, cu_cached, out, o_sn, o_sh, N, Hq / Hkv, scale_log2, status,
+                                        tm_k, tm_v, tm_kp, tm_vp, prefix_tma);
+  return le == cudaSuccess && cudaGetLastError() == cudaSuccess ? B200KV_OK : B200KV_E_LAUNCH;
 }
 
 }  // namespace b200kv

@@ -120,11 +120,10 @@ write_decode_kernel(const uint16_t* __restrict__ q, long long q_sb, long long q_
                     CacheView c, const int32_t* __restrict__ cached_lens, const int32_t* __restrict__ num_decoding,
                     uint16_t* __restrict__ q_out, long long o_sb, long long o_sh, int Hq, float eps, int32_t* status) {
   __shared__ __align__(16) float sq_all[kWarpsPerBlock][kD];
-  // A successor launched with programmatic stream serialization (decode attention's early start)
-  // may be scheduled now; it waits for this grid to finish before it reads the cache or q_out.
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  pdl_enter();
   const int b = blockIdx.x;
   if (b >= *num_decoding) return;
+  pdl_wait();  // q, k, v come from the kernel before this one
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int job = blockIdx.y * kWarpsPerBlock + warp;
   const int Hkv = c.Hkv;
@@ -179,10 +178,12 @@ norm_rope_prefill_kernel(const uint16_t* __restrict__ q, long long q_sn, long lo
                          uint16_t* __restrict__ k_out, long long ko_sn, long long ko_sh,
                          int Hq, int Hkv, float eps) {
   __shared__ __align__(16) float sq_all[kWarpsPerBlock][kD];
+  pdl_enter();
   const int n = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int job = blockIdx.y * kWarpsPerBlock + warp;
   if (job >= Hq + Hkv) return;
+  pdl_wait();  // q and k come from the kernel before this one
   float r[4];
   if (job < Hq) {
     norm_rope_head(q + n * q_sn + job * q_sh, qw, cosp + n * cos_sn, sinp + n * sin_sn, eps, sq_all[warp], lane, r);
@@ -220,8 +221,10 @@ __global__ void __launch_bounds__(kCalibGroups * 32)
 calibrate_kernel(const uint16_t* __restrict__ k, long long k_sn, long long k_sh, CacheView c,
                  const int32_t* __restrict__ cu, const int32_t* __restrict__ cached_lens,
                  const int32_t* __restrict__ num_decoding, int N, int32_t* status) {
+  pdl_enter();
   const int b = blockIdx.x, h = blockIdx.y;
   if (!is_first_chunk(b, *num_decoding, cu, cached_lens)) return;
+  pdl_wait();  // k comes from the kernel before this one
   const int lane = threadIdx.x & 31, g = threadIdx.x >> 5;
   const int s0 = cu[b], s1 = min(cu[b + 1], N);
   float m[4] = {0.f, 0.f, 0.f, 0.f};
@@ -252,6 +255,7 @@ quantize_prefill_kernel(const uint16_t* __restrict__ k, long long k_sn, long lon
                         const uint16_t* __restrict__ v, long long v_sn, long long v_sh, CacheView c,
                         const int32_t* __restrict__ cu, int num_entries, const int32_t* __restrict__ cached_lens,
                         const int32_t* __restrict__ num_decoding, int32_t* status) {
+  pdl_enter();
   const int r = blockIdx.x;
   if (r >= cu[num_entries]) return;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -259,6 +263,7 @@ quantize_prefill_kernel(const uint16_t* __restrict__ k, long long k_sn, long lon
   if (job >= 2 * c.Hkv) return;
   const int b = entry_of_row(cu, num_entries, r);
   if (b < *num_decoding) return;
+  pdl_wait();  // k, v and the calibration come from the kernels before this one
   const int pos = cached_lens[b] + (r - cu[b]);
   const int page = lookup_page(c, b, pos, status);
   if (page < 0) return;
@@ -290,6 +295,7 @@ quantize_prefill_kernel(const uint16_t* __restrict__ k, long long k_sn, long lon
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 dequant_prefix_kernel(CacheView c, const int32_t* __restrict__ cu_cached, int num_entries, uint16_t* __restrict__ k_out,
                       uint16_t* __restrict__ v_out, long long o_sh, long long o_sn, int capacity, int32_t* status) {
+  pdl_enter();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int r = blockIdx.x * kWarpsPerBlock + warp;
   if (r >= min(cu_cached[num_entries], capacity)) return;
@@ -311,6 +317,7 @@ dequant_prefix_kernel(CacheView c, const int32_t* __restrict__ cu_cached, int nu
   const int page = lookup_page(c, b, t, status);
   if (page0 < 0 || page < 0) return;
   const int row = t % c.page_size;
+  pdl_wait();  // the cache is written by the kernels before this one
   constexpr int kHeadsAtOnce = 4;
   for (int h0 = 0; h0 < c.Hkv; h0 += kHeadsAtOnce) {
     uint32_t kc[kHeadsAtOnce], vc[kHeadsAtOnce];
@@ -371,7 +378,7 @@ extern "C" int b200kv_write_decode(const void* q, int64_t q_sb, int64_t q_sh, co
     return B200KV_E_ALIGN;
   if (B == 0) return B200KV_OK;
   dim3 grid(B, (Hq + 2 * Hkv + kWarpsPerBlock - 1) / kWarpsPerBlock);
-  write_decode_kernel<<<grid, kWarpsPerBlock * 32, 0, (cudaStream_t)stream>>>(
+  launch_chained(write_decode_kernel, grid, dim3(kWarpsPerBlock * 32), 0, (cudaStream_t)stream,
       (const uint16_t*)q, q_sb, q_sh, (const uint16_t*)k, k_sb, k_sh, (const uint16_t*)v, v_sb, v_sh,
       (const uint16_t*)qw, (const uint16_t*)kw, (const uint16_t*)cosp, cos_sb, (const uint16_t*)sinp, sin_sb,
       make_view(cache, table), cached_lens, num_decoding, (uint16_t*)q_out, o_sb, o_sh, Hq, eps, status);
@@ -393,7 +400,7 @@ extern "C" int b200kv_norm_rope_prefill(const void* q, int64_t q_sn, int64_t q_s
     return B200KV_E_ALIGN;
   if (N == 0) return B200KV_OK;
   dim3 grid(N, (Hq + Hkv + kWarpsPerBlock - 1) / kWarpsPerBlock);
-  norm_rope_prefill_kernel<<<grid, kWarpsPerBlock * 32, 0, (cudaStream_t)stream>>>(
+  launch_chained(norm_rope_prefill_kernel, grid, dim3(kWarpsPerBlock * 32), 0, (cudaStream_t)stream,
       (const uint16_t*)q, q_sn, q_sh, (const uint16_t*)k, k_sn, k_sh, (const uint16_t*)qw, (const uint16_t*)kw,
       (const uint16_t*)cosp, cos_sn, (const uint16_t*)sinp, sin_sn, (uint16_t*)q_out, qo_sn, qo_sh, (uint16_t*)k_out,
       ko_sn, ko_sh, Hq, Hkv, eps);
@@ -414,9 +421,9 @@ extern "C" int b200kv_quantize_prefill(const void* k, int64_t k_sn, int64_t k_sh
   const int Hkv = cache->num_kv_heads;
   CacheView view = make_view(cache, table);
   cudaStream_t s = (cudaStream_t)stream;
-  calibrate_kernel<<<dim3(num_entries, Hkv), kCalibGroups * 32, 0, s>>>((const uint16_t*)k, k_sn, k_sh, view, cu_seqlens,
-                                                                        cached_lens, num_decoding, N, status);
-  quantize_prefill_kernel<<<dim3(N, (2 * Hkv + kWarpsPerBlock - 1) / kWarpsPerBlock), kWarpsPerBlock * 32, 0, s>>>(
+  launch_chained(calibrate_kernel, dim3(num_entries, Hkv), dim3(kCalibGroups * 32), 0, s, (const uint16_t*)k, k_sn, k_sh, view,
+                 cu_seqlens, cached_lens, num_decoding, N, status);
+  launch_chained(quantize_prefill_kernel, dim3(N, (2 * Hkv + kWarpsPerBlock - 1) / kWarpsPerBlock), dim3(kWarpsPerBlock * 32), 0, s,
       (const uint16_t*)k, k_sn, k_sh, (const uint16_t*)v, v_sn, v_sh, view, cu_seqlens, num_entries, cached_lens,
       num_decoding, status);
   return launch_status();
@@ -432,7 +439,7 @@ extern "C" int b200kv_dequant_prefix(const b200kv_cache* cache, const b200kv_tab
   if (!aligned(k_out, 8) || !aligned(v_out, 8) || !stride_ok4(o_sh) || !stride_ok4(o_sn)) return B200KV_E_ALIGN;
   if (num_entries == 0 || capacity == 0) return B200KV_OK;
   dim3 grid((unsigned)((capacity + kWarpsPerBlock - 1) / kWarpsPerBlock));
-  dequant_prefix_kernel<<<grid, kWarpsPerBlock * 32, 0, (cudaStream_t)stream>>>(
+  launch_chained(dequant_prefix_kernel, grid, dim3(kWarpsPerBlock * 32), 0, (cudaStream_t)stream,
       make_view(cache, table), cu_cached, num_entries, (uint16_t*)k_out, (uint16_t*)v_out, o_sh, o_sn, capacity, status);
   return launch_status();
 }

@@ -78,13 +78,16 @@ _early_start = False
 
 
 def set_early_start(enabled: bool) -> None:
-    """Allow decode_attention's kernel to be scheduled while the kernel enqueued just before it is
-    still running (it reads only cached_lens, num_decoding and the block table before waiting for
-    that kernel).  Safe when the preceding kernel on the stream does not write those arrays, which
-    holds for the engine's decode path (fused_rope_kv_decode precedes decode_attention,
-    architecture.py:101-123).  Off by default."""
+    """Allow every kernel of this module to be brought up while the kernel enqueued just before it on
+    the stream is still running (programmatic dependent launch).  A kernel reads only the step's
+    metadata (cu_seqlens, cu_cached, cached_lens, num_decoding, block table, tile_start, seq_ids)
+    before it waits for that kernel, and everything else afterwards.  Safe when no kernel that
+    directly precedes one of these ops on its stream writes those arrays, which holds for the engine:
+    it uploads them once per step, before the first layer (engine.py:347-356), and the ops are
+    preceded by GEMMs or by one another (architecture.py:99-198).  Off by default."""
     global _early_start
     _early_start = bool(enabled)
+    _lib.load().b200kv_set_chained_launch(1 if enabled else 0)
 
 
 _workspaces: dict[tuple, torch.Tensor] = {}

@@ -19,8 +19,12 @@ def S():
     return scaffold
 
 
+@pytest.mark.parametrize("chained", [False, True])
 @pytest.mark.parametrize("block_m", [16, 128])
-def test_layer_attention_path_matches_oracle(S, block_m):
+def test_layer_attention_path_matches_oracle(S, block_m, chained):
+    """chained = every kernel of the path launched with programmatic stream serialization (each may be
+    brought up while its predecessor still runs and waits for it before touching its data), run three times
+    back to back so that kernels of consecutive passes chain as well."""
     from inference_engine_b200 import kernels as K
 
     rng = np.random.default_rng(77 + block_m)
@@ -42,9 +46,15 @@ def test_layer_attention_path_matches_oracle(S, block_m):
     inp = S.upload_step(plan, table_t, [0] * N, "cuda", block_m)
     prefix = S.PrefixScratch(torch.zeros(HKV, cu_cached[-1] + 8, D, device="cuda", dtype=torch.bfloat16),
                              torch.zeros(HKV, cu_cached[-1] + 8, D, device="cuda", dtype=torch.bfloat16), inp.cu_cached)
-    out = S.attention_ops(H.bf16_tensor(q), H.bf16_tensor(k), H.bf16_tensor(v), H.bf16_tensor(qw), H.bf16_tensor(kw),
-                          H.bf16_tensor(cos)[:, None, :], H.bf16_tensor(sin)[:, None, :], dev_cache, inp,
-                          inp.cached_lens, inp.block_table, inp.num_decoding, prefix)
+    args = (H.bf16_tensor(q), H.bf16_tensor(k), H.bf16_tensor(v), H.bf16_tensor(qw), H.bf16_tensor(kw),
+            H.bf16_tensor(cos)[:, None, :], H.bf16_tensor(sin)[:, None, :])
+    K.set_early_start(chained)
+    try:
+        for _ in range(3 if chained else 1):  # the step is idempotent: same rows, same values
+            out = S.attention_ops(*args, dev_cache, inp, inp.cached_lens, inp.block_table, inp.num_decoding, prefix)
+        torch.cuda.synchronize()
+    finally:
+        K.set_early_start(False)
     assert K.check_status() == 0
 
     q_p, k_p = O.norm_rope_prefill(q, k, qw, kw, cos, sin, 1e-6)
