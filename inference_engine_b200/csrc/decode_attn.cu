@@ -697,10 +697,11 @@ decode_attn_kernel(const uint16_t* __restrict__ q, long long q_sb, long long q_s
   float* q_s = reinterpret_cast<float*>(ring + kWarps * kStages * kTileBytes);  // scalar variant: kWarps * (G*128 + G*16)
   int* chunk_prefix = reinterpret_cast<int*>(q_s + (kScalar ? kWarps * (kMaxG * kD + kMaxG * kTile) : 0));
 
-  // Let a programmatically-dependent successor be scheduled as SMs free up (it waits for this grid
-  // to complete before it touches anything this grid writes); the first CTA waits for the predecessor
-  // at once, so that this grid can never complete before it.
-  pdl_enter();
+  // The first CTA waits for the predecessor at once, so that this grid can never complete before it.  The
+  // trigger for the successor comes late, when a warp has issued its last tile: the CTAs of a successor that is
+  // brought up while this kernel still streams sit on the SMs waiting and slow the streaming down (measured:
+  // +16 us per call when the trigger was the first statement).
+  if (blockIdx.x == 0) pdl_wait();
   int* lens_s = chunk_prefix + kWarps * 32 + 1;
   int* cta_arrive = lens_s + kSmemLens;  // how many of this CTA's warps have parked a piece in shared memory
   if (threadIdx.x == 0) *cta_arrive = 0;  // ordered before any use by the barriers inside scan_tiles
@@ -766,6 +767,7 @@ decode_attn_kernel(const uint16_t* __restrict__ q, long long q_sb, long long q_s
       if (p_left > 0) {
         issue_tile(c, pc, win, lc, my_ring_s + stage_p * kTileBytes, lane, status);
         if (--p_left > 0) pc.next(lens, c.Hkv, c.page_size);
+        else pdl_trigger();  // this warp has nothing left to fetch
       }
       cp_async_commit();
       cp_async_wait<kStages - 1>();

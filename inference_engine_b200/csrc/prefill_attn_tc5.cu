@@ -175,7 +175,10 @@ prefill_attn_tc5_kernel(const uint16_t* __restrict__ q, long long q_sn, long lon
                         const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                         const __grid_constant__ CUtensorMap tm_kp, const __grid_constant__ CUtensorMap tm_vp, int prefix_tma) {
   extern __shared__ uint8_t t5_raw[];
-  pdl_enter();
+  // The first CTA waits for the predecessor on every path (a grid in which no CTA waited could complete before
+  // it); the trigger for the successor comes late, from the softmax threads when their last block is done: a
+  // successor brought up while this kernel is in full swing would only sit on the SMs.
+  if ((blockIdx.x | blockIdx.y) == 0) pdl_wait();
   // heads run fastest in the grid: the caller's real tiles come first in tile_start, so every CTA with work
   // is dispatched before the idle ones behind them
   const int tile = blockIdx.y / subs, sub = blockIdx.y - tile * subs;
@@ -412,6 +415,7 @@ prefill_attn_tc5_kernel(const uint16_t* __restrict__ q, long long q_sn, long lon
       t5_fence_before();
       if (ok) t5_mbar_arrive(bar_r(wg, h & 1));  // hand P(h) to the issuing warp
     }
+    pdl_trigger();
     if (n_mine > 0 && ok) ok = t5_mbar_wait(bar_o(wg, 1), 0);  // the last P V
     t5_fence_after();
     if (!ok) t5_sts_u32(dead_flag, 1);

@@ -7,7 +7,11 @@ back.  The int8 KV cache itself is device-resident state that persists across st
 as in the reference engine (engine.py:472-492); it is not a per-step input.
 
 Per step and per layer this runs the two calls `AttentionLayer.forward` makes for a pure
-decode step (architecture.py:98-123): fused_rope_kv_decode, then decode_attention."""
+decode step (architecture.py:98-123): fused_rope_kv_decode, then decode_attention.
+
+The host-buffer step is pipelined over groups of layers: while group g computes, the projections
+of group g+1 are copied in on a second stream and the outputs of group g-1 are copied out on a
+third, so the copies of all but the first and last group hide behind the kernels."""
 from __future__ import annotations
 
 import torch
@@ -31,6 +35,9 @@ class HostDecodeStep:
         self.q_w = [torch.ones(D, dtype=torch.bfloat16, device=dev) for _ in range(L)]
         self.k_w = [torch.ones(D, dtype=torch.bfloat16, device=dev) for _ in range(L)]
         self.graph = None
+        self.group_graphs: list[tuple[int, int, torch.cuda.CUDAGraph]] = []  # (first layer, end layer, graph)
+        self.h2d_stream = torch.cuda.Stream(device=dev)
+        self.d2h_stream = torch.cuda.Stream(device=dev)
 
     def set_norm_weights(self, q_w, k_w):
         self.q_w, self.k_w = q_w, k_w
@@ -44,10 +51,12 @@ class HostDecodeStep:
     def d2h_bytes(self) -> int:
         return self.dev_out.numel() * self.dev_out.element_size()
 
-    def device_step(self):
-        """The device part: per layer, quantize-on-write of the new tokens then attention."""
+    def device_step(self, first: int = 0, end: int | None = None):
+        """The device part: per layer in [first, end), quantize-on-write of the new tokens then attention."""
         Hq, Hkv, D = self.Hq, self.Hkv, self.D
-        for l, cache in enumerate(self.caches):
+        end = len(self.caches) if end is None else end
+        for l in range(first, end):
+            cache = self.caches[l]
             q, k, v = self.dev_qkv[l].split([Hq * D, Hkv * D, Hkv * D], dim=-1)
             q = q.view(self.B, Hq, D)
             k = k.view(self.B, Hkv, D)
@@ -56,8 +65,9 @@ class HostDecodeStep:
                                         cache, self.dev_cached, self.dev_nd, self.eps)
             K.decode_attention(qr, cache, self.dev_cached, self.dev_table, self.dev_nd, D ** -0.5, out=self.dev_out[l])
 
-    def capture(self):
-        """Record device_step into a CUDA graph (two eager warm-up runs first, like engine.py:432-449)."""
+    def capture(self, groups: int = 4):
+        """Record device_step into a CUDA graph (two eager warm-up runs first, like engine.py:432-449), and
+        once more as `groups` graphs over consecutive layer ranges for the pipelined host-buffer step."""
         s = torch.cuda.Stream()
         s.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(s):
@@ -67,6 +77,15 @@ class HostDecodeStep:
         self.graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(self.graph):
             self.device_step()
+        L = len(self.caches)
+        groups = max(1, min(groups, L))
+        bounds = [round(i * L / groups) for i in range(groups + 1)]
+        self.group_graphs = []
+        for a, b in zip(bounds[:-1], bounds[1:]):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self.device_step(a, b)
+            self.group_graphs.append((a, b, g))
 
     def run_device(self):
         if self.graph is not None:
@@ -77,11 +96,29 @@ class HostDecodeStep:
     def run_host(self, qkv, cos, sin, cached_lens, table, num_decoding, out):
         """All arguments are pinned host tensors; `out` receives [L, B, Hq, D] bf16.  Enqueues
         H2D copies, the device step and the D2H copy on the current stream (no sync)."""
-        self.dev_qkv.copy_(qkv, non_blocking=True)
         self.dev_cos.copy_(cos, non_blocking=True)
         self.dev_sin.copy_(sin, non_blocking=True)
         self.dev_cached.copy_(cached_lens, non_blocking=True)
         self.dev_table.copy_(table, non_blocking=True)
         self.dev_nd.copy_(num_decoding, non_blocking=True)
-        self.run_device()
-        out.copy_(self.dev_out, non_blocking=True)
+        if not self.group_graphs:
+            self.dev_qkv.copy_(qkv, non_blocking=True)
+            self.run_device()
+            out.copy_(self.dev_out, non_blocking=True)
+            return
+        cur = torch.cuda.current_stream()
+        self.h2d_stream.wait_stream(cur)  # after everything already enqueued (the previous step reads dev_qkv)
+        self.d2h_stream.wait_stream(cur)
+        for a, b, g in self.group_graphs:
+            with torch.cuda.stream(self.h2d_stream):
+                self.dev_qkv[a:b].copy_(qkv[a:b], non_blocking=True)
+                landed = torch.cuda.Event()
+                landed.record(self.h2d_stream)
+            cur.wait_event(landed)
+            g.replay()
+            done = torch.cuda.Event()
+            done.record(cur)
+            with torch.cuda.stream(self.d2h_stream):
+                self.d2h_stream.wait_event(done)
+                out[a:b].copy_(self.dev_out[a:b], non_blocking=True)
+        cur.wait_stream(self.d2h_stream)  # the caller's stream order covers the whole step
