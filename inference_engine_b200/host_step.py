@@ -26,11 +26,25 @@ class HostDecodeStep:
         self.caches, self.B, self.Hq, self.Hkv, self.D, self.eps = caches, B, Hq, Hkv, D, eps
         W = (Hq + 2 * Hkv) * D
         self.dev_qkv = torch.empty(L, B, W, dtype=torch.bfloat16, device=dev)
-        self.dev_cos = torch.empty(B, 1, D // 2, dtype=torch.bfloat16, device=dev)
-        self.dev_sin = torch.empty_like(self.dev_cos)
-        self.dev_cached = torch.empty(B, dtype=torch.int32, device=dev)
-        self.dev_table = torch.empty(table_shape, dtype=torch.int32, device=dev)
-        self.dev_nd = torch.empty(1, dtype=torch.int32, device=dev)
+        # the step's small inputs live in one buffer, so they reach the GPU in one copy (the reference engine
+        # does the same with its metadata, engine.py:72-76): rope rows, cached lengths, block table, num_decoding
+        sizes = [B * (D // 2) * 2, B * (D // 2) * 2, B * 4, int(torch.tensor(table_shape).prod()) * 4, 4]
+        offs, total = [], 0
+        for n in sizes:
+            offs.append(total)
+            total += (n + 255) // 256 * 256
+        self.dev_meta = torch.empty(total, dtype=torch.uint8, device=dev)
+        self.host_meta = [torch.empty(total, dtype=torch.uint8).pin_memory() for _ in range(2)]
+        self.meta_sent = [None, None]  # event after the copy that last read each staging buffer
+        self.meta_turn = 0
+
+        def views(buf):
+            part = lambda i, dt, shape: buf[offs[i] : offs[i] + sizes[i]].view(dt).view(shape)
+            return (part(0, torch.bfloat16, (B, 1, D // 2)), part(1, torch.bfloat16, (B, 1, D // 2)),
+                    part(2, torch.int32, (B,)), part(3, torch.int32, tuple(table_shape)), part(4, torch.int32, (1,)))
+
+        self._views = views
+        self.dev_cos, self.dev_sin, self.dev_cached, self.dev_table, self.dev_nd = views(self.dev_meta)
         self.dev_out = torch.empty(L, B, Hq, D, dtype=torch.bfloat16, device=dev)
         self.q_w = [torch.ones(D, dtype=torch.bfloat16, device=dev) for _ in range(L)]
         self.k_w = [torch.ones(D, dtype=torch.bfloat16, device=dev) for _ in range(L)]
@@ -44,7 +58,7 @@ class HostDecodeStep:
 
     @property
     def h2d_bytes(self) -> int:
-        ts = (self.dev_qkv, self.dev_cos, self.dev_sin, self.dev_cached, self.dev_table, self.dev_nd)
+        ts = (self.dev_qkv, self.dev_meta)
         return sum(t.numel() * t.element_size() for t in ts)
 
     @property
@@ -96,11 +110,15 @@ class HostDecodeStep:
     def run_host(self, qkv, cos, sin, cached_lens, table, num_decoding, out):
         """All arguments are pinned host tensors; `out` receives [L, B, Hq, D] bf16.  Enqueues
         H2D copies, the device step and the D2H copy on the current stream (no sync)."""
-        self.dev_cos.copy_(cos, non_blocking=True)
-        self.dev_sin.copy_(sin, non_blocking=True)
-        self.dev_cached.copy_(cached_lens, non_blocking=True)
-        self.dev_table.copy_(table, non_blocking=True)
-        self.dev_nd.copy_(num_decoding, non_blocking=True)
+        turn = self.meta_turn
+        self.meta_turn ^= 1
+        if self.meta_sent[turn] is not None:
+            self.meta_sent[turn].synchronize()  # the copy that read this staging buffer two steps ago is done
+        for dst, src in zip(self._views(self.host_meta[turn]), (cos, sin, cached_lens, table, num_decoding)):
+            dst.copy_(src)
+        self.dev_meta.copy_(self.host_meta[turn], non_blocking=True)
+        self.meta_sent[turn] = torch.cuda.Event()
+        self.meta_sent[turn].record()
         if not self.group_graphs:
             self.dev_qkv.copy_(qkv, non_blocking=True)
             self.run_device()
