@@ -104,7 +104,7 @@ def rope(pos: torch.Tensor, D: int):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="checkout of kbwal/inference-engine (the unmodified reference)")
     ap.add_argument("--out", default=os.path.join(os.path.dirname(os.path.abspath(__file__)), "reference_interp.npz"))
     args = ap.parse_args()
     sys.path.insert(0, os.path.join(args.reference, "qwen3-1.7b"))
