@@ -453,6 +453,10 @@ def run_path(args):
         E, tab, cl, nd = inp.block_table.shape[0], inp.block_table, inp.cached_lens, inp.num_decoding
         q_p, k_p = K.fused_norm_rope_prefill(q, k, qw, qw, cos, sin, 1e-6)
         out = torch.empty(n_tokens, HQ, D, device=dev, dtype=torch.bfloat16)
+        hid = torch.randn(n_tokens, 2048, generator=dgen, device=dev).to(torch.bfloat16)
+        hid2 = torch.randn(n_tokens, 2048, generator=dgen, device=dev).to(torch.bfloat16)
+        lnw = torch.ones(2048, device=dev, dtype=torch.bfloat16)
+        gate_up = torch.randn(n_tokens, 12288, generator=dgen, device=dev).to(torch.bfloat16)
         q_d = K.fused_rope_kv_decode(q[:E], k[:E], v[:E], qw, qw, cos[:E], sin[:E], tab, caches[0], cl, nd, 1e-6)
         ops = {
             "fused_norm_rope_prefill": lambda c: K.fused_norm_rope_prefill(q, k, qw, qw, cos, sin, 1e-6),
@@ -464,6 +468,9 @@ def run_path(args):
                                                                      cl, nd, 1e-6),
             "decode_attention": lambda c: K.decode_attention(q_d, c, cl, tab, nd, D ** -0.5, out=out),
             "all six in the engine's order": lambda c: S.attention_ops(q, k, v, qw, qw, cos, sin, c, inp, cl, tab, nd, prefix),
+            # the block's two element-wise ops at this step's sizes (hidden 2048, FFN 6144)
+            "add_rms_norm [1024 x 2048]": lambda c: K.add_rms_norm(hid, hid2, lnw, 1e-6),
+            "silu_mul [1024 x 12288]": lambda c: K.silu_mul(gate_up),
         }
         line = {"case": "attention path of the mixed step, per op", "prior_context": prior, "us_per_call": {}}
         for name, fn in ops.items():

@@ -166,6 +166,19 @@ int b200kv_prefill_attn_variant(const void* q, int64_t q_stride_n, int64_t q_str
                                 int32_t N, int32_t Hq, int32_t Hkv, int32_t D,
                                 int32_t variant, int32_t* status, void* stream);
 
+/* The two element-wise ops of the decoder block around the attention path (first of the "next" rows).
+ * b200kv_silu_mul replaces silu_mul (kernels.py:1178-1212): out[n, d] = bf16((g * sigmoid(g)) * u) with
+ * g = gate_up[n, d], u = gate_up[n, D + d], fp32 arithmetic.  bf16 [N, 2D] -> bf16 [N, D]; D a multiple
+ * of 8, rows 16-byte aligned.
+ * b200kv_add_rms_norm replaces add_rms_norm (kernels.py:1215-1285): new_residual = bf16(residual + delta);
+ * normed = bf16((new_residual * rsqrt(mean(new_residual^2) + eps)) * weight), the mean over the rounded new
+ * residual.  bf16 [N, D] each, D a multiple of 8 and at most 8192. */
+int b200kv_silu_mul(const void* gate_up, int64_t in_stride, void* out, int64_t out_stride,
+                    int32_t N, int32_t D, void* stream);
+int b200kv_add_rms_norm(const void* residual, int64_t r_stride, const void* delta, int64_t d_stride,
+                        const void* weight, void* new_residual, int64_t nr_stride,
+                        void* normed, int64_t nn_stride, int32_t N, int32_t D, float eps, void* stream);
+
 /* Chained launches (off by default).  While enabled, every kernel of this library is launched with
  * programmatic stream serialization: it may be brought up while the kernel launched just before it on
  * the same stream is still running, reads only caller-provided metadata (cu_seqlens, cu_cached,

@@ -55,6 +55,9 @@ SIGNATURES = {
                                               c_int64, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_void_p, c_void_p,
                                               c_int64, c_int64, c_int32, c_void_p, c_void_p, c_int64, c_int64, c_int32,
                                               c_int32, c_int32, c_int32, c_int32, c_void_p, c_void_p]),
+    "b200kv_silu_mul": (c_int32, [c_void_p, c_int64, c_void_p, c_int64, c_int32, c_int32, c_void_p]),
+    "b200kv_add_rms_norm": (c_int32, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_void_p, c_int64,
+                                      c_int32, c_int32, c_float, c_void_p]),
     "b200kv_set_chained_launch": (None, [c_int32]),
     "b200kv_get_chained_launch": (c_int32, []),
     "b200kv_decode_attn_workspace_bytes": (c_size_t, [c_int32, c_int32, c_int32, c_int32, c_int32]),

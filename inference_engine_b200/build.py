@@ -28,6 +28,7 @@ UNITS = {
     "decode_attn.cu": [],
     "prefill_attn.cu": [],
     "prefill_attn_tc5.cu": [],
+    "block_ops.cu": [],
     "host_step.cu": [],
 }
 

@@ -333,21 +333,38 @@ def prefill_attention(
     return out
 
 
+# ----------------------------------------------------------------------------- decoder-block ops
+# The two element-wise ops between the attention path and the GEMMs, as CUDA kernels behind the same C ABI.
+def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
+    """kernels.py:1204-1212: bf16 [N, 2D] -> bf16 [N, D] = silu(gate) * up."""
+    _require_cuda(gate_up)
+    assert gate_up.dim() == 2 and gate_up.stride(-1) == 1 and gate_up.dtype == torch.bfloat16
+    N, two_d = gate_up.shape
+    out = torch.empty(N, two_d // 2, device=gate_up.device, dtype=gate_up.dtype)
+    rc = _lib.load().b200kv_silu_mul(gate_up.data_ptr(), gate_up.stride(0), out.data_ptr(), out.stride(0), N, two_d // 2,
+                                     _stream())
+    _lib.check(rc, "silu_mul")
+    return out
+
+
+def add_rms_norm(residual: torch.Tensor, delta: torch.Tensor, rms_norm: torch.Tensor, eps: float):
+    """kernels.py:1261-1285: (residual + delta, rmsnorm(residual + delta) * weight), bf16 [N, D] each."""
+    _require_cuda(residual, delta, rms_norm)
+    assert residual.dim() == 2 and residual.shape == delta.shape and residual.dtype == torch.bfloat16
+    assert residual.stride(-1) == 1 and delta.stride(-1) == 1 and rms_norm.is_contiguous()
+    N, D = residual.shape
+    new_residual = torch.empty_like(residual)
+    normed = torch.empty_like(residual)
+    rc = _lib.load().b200kv_add_rms_norm(residual.data_ptr(), residual.stride(0), delta.data_ptr(), delta.stride(0),
+                                         rms_norm.data_ptr(), new_residual.data_ptr(), new_residual.stride(0),
+                                         normed.data_ptr(), normed.stride(0), N, D, ctypes.c_float(eps), _stream())
+    _lib.check(rc, "add_rms_norm")
+    return new_residual, normed
+
+
 # ----------------------------------------------------------------------------- scaffold ops
 # The remaining names the reference's architecture.py / engine.py import from kernels.py.  They
 # are outside the attention path; plain PyTorch keeps a model built on this module runnable.
-def silu_mul(x: torch.Tensor) -> torch.Tensor:  # kernels.py:1204: [N, 2D] -> silu(gate) * up
-    gate, up = x.chunk(2, dim=-1)
-    return F.silu(gate) * up
-
-
-def add_rms_norm(residual, x, weight, eps):  # kernels.py:1261: residual += x; return (residual, rmsnorm(residual) * w)
-    residual = x if residual is None else residual + x
-    r = residual.float()
-    y = r * torch.rsqrt(r.pow(2).mean(-1, keepdim=True) + eps)
-    return residual, (y * weight.float()).to(x.dtype)
-
-
 def sample(logits: torch.Tensor, tau: float, seed: torch.Tensor) -> torch.Tensor:  # kernels.py:1341, tau = 0 only
     if tau != 0:
         raise NotImplementedError("only greedy sampling (tau = 0) is provided by this scaffold")

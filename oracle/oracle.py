@@ -359,3 +359,26 @@ def rope_tables(positions, D: int = 128, base: float = 1e6):
     cos = ang.cos().to(torch.bfloat16).to(torch.float32).numpy()
     sin = ang.sin().to(torch.bfloat16).to(torch.float32).numpy()
     return cos, sin
+
+
+# --------------------------------------------------------------------------- decoder-block element-wise ops
+def silu_mul(gate_up) -> np.ndarray:
+    """silu_mul, kernels.py:1178-1212: [N, 2D] bf16 -> [N, D]: bf16((gate * sigmoid(gate)) * up), all in fp32,
+    gate = columns [0, D), up = columns [D, 2D)."""
+    x = np.asarray(gate_up, np.float32)
+    d = x.shape[-1] // 2
+    gate, up = x[..., :d], x[..., d:]
+    sig = (F32(1.0) / (F32(1.0) + np.exp(-gate, dtype=np.float32))).astype(np.float32)
+    return bf16_round(((gate * sig).astype(np.float32) * up).astype(np.float32))
+
+
+def add_rms_norm(residual, delta, weight, eps: float):
+    """add_rms_norm, kernels.py:1215-1285: new_residual = bf16(residual + delta) (fp32 add); normed =
+    bf16((new_residual * rsqrt(sum(new_residual^2) / D + eps)) * weight), the sum over the bf16-rounded
+    new residual in fp32.  Returns (new_residual, normed) as fp32 arrays holding bf16 values."""
+    r = bf16_round((np.asarray(residual, np.float32) + np.asarray(delta, np.float32)).astype(np.float32))
+    D = r.shape[-1]
+    ss = np.sum((r * r).astype(np.float32), axis=-1, keepdims=True, dtype=np.float32)
+    inv = (F32(1.0) / np.sqrt(ss / F32(D) + F32(eps), dtype=np.float32)).astype(np.float32)
+    normed = ((r * inv).astype(np.float32) * np.asarray(weight, np.float32)).astype(np.float32)
+    return r, bf16_round(normed)
