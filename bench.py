@@ -411,6 +411,80 @@ def run_sharded(args):
         dist.destroy_process_group()
 
 
+def run_decode_model(args):
+    """--decode-model: one pure-decode step of the random-init Qwen3-1.7B-shaped decoder at the headline shape
+    (B sequences of ctx cached tokens, one new token each, 28 layers, int8 paged cache, random block table):
+    embedding -> 28 x (norm, qkv GEMM, quantize-on-write, decode attention, o GEMM, norm, SwiGLU MLP) -> norm ->
+    tied lm_head -> argmax, captured as one CUDA graph.  Reports step time, tokens/s and the attention path's
+    share (a second graph with only the write + attention ops on the same caches)."""
+    import torch
+
+    from inference_engine_b200 import kernels as K
+    from inference_engine_b200 import scaffold as S
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    K.set_early_start(not args.no_early_start)
+    B, n = args.batch, args.ctx
+    model = S.DecoderScaffold(dev, seed=4)
+    gen = torch.Generator(device=dev).manual_seed(4)
+    pages_per_seq = (n + PAGE) // PAGE  # room for the new token
+    num_pages = B * pages_per_seq
+    caches = []
+    for _ in range(S.LAYERS):
+        c = K.make_layer_cache(num_pages, HKV, PAGE, D, device=dev)
+        c.k.copy_(torch.randint(-127, 128, c.k.shape, generator=gen, device=dev, dtype=torch.int8))
+        c.v.copy_(torch.randint(-127, 128, c.v.shape, generator=gen, device=dev, dtype=torch.int8))
+        c.k_scale.uniform_(0.01, 0.04, generator=gen)
+        c.v_scale.uniform_(0.01, 0.04, generator=gen)
+        caches.append(c)
+    table = torch.randperm(num_pages, generator=gen, device=dev).to(torch.int32).reshape(B, pages_per_seq)
+    cached = torch.full((B,), n - 1, dtype=torch.int32, device=dev)  # the new token is the ctx-th
+    nd = torch.tensor([B], dtype=torch.int32, device=dev)
+    ids = torch.randint(0, S.VOCAB, (B,), generator=gen, device=dev, dtype=torch.int32)
+    qkv = torch.randn(B, (HQ + 2 * HKV) * D, generator=gen, device=dev).to(torch.bfloat16)
+    q, k, v = qkv.split([HQ * D, HKV * D, HKV * D], dim=-1)
+    q, k, v = q.view(B, HQ, D), k.view(B, HKV, D), v.view(B, HKV, D)
+    cos, sin = model.rope(cached)
+
+    def step():
+        return model.forward(caches, None, ids, cached, table, nd)
+
+    def path_only():
+        for L, c in zip(model.layers, caches):
+            S.attention_ops(q, k, v, L["qn"], L["kn"], cos, sin, c, None, cached, table, nd, None)
+
+    def graph_ms(fn):
+        with torch.inference_mode():
+            fn()
+            fn()
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                res = fn()
+        for _ in range(max(args.warmup, 3)):
+            g.replay()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(args.steps):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            g.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        return statistics.median(ts), res
+
+    step_ms, toks = graph_ms(step)
+    path_ms, _ = graph_ms(path_only)
+    kv_bytes = S.LAYERS * (B * n * 2112 + B * WRITE_BYTES_PER_TOKEN)
+    print(json.dumps({
+        "case": "pure decode step of the random-init decoder", "batch": B, "ctx": n, "layers": S.LAYERS,
+        "step_ms": round(step_ms, 3), "tokens_per_s": round(B / step_ms * 1e3), "attention_path_ms": round(path_ms, 3),
+        "attention_path_share": round(path_ms / step_ms, 3), "attention_path_gbs": round(kv_bytes / path_ms / 1e6, 1),
+        "status": K.check_status(dev), "sampled_head": toks[:4].tolist(), "data": "synthetic ids, random-init weights"}), flush=True)
+
+
 def run_path(args):
     """--path: each op of the mixed step's attention path timed alone (seed 3 shapes: 32 decoding sequences
     with contexts ~U[128,4096] + one 992-row chunk on a prior context of 0 and of 3072 tokens, 34 entries,
@@ -805,6 +879,7 @@ def main():
     ap.add_argument("--no-early-start", action="store_true", help="launch decode attention without programmatic early start")
     ap.add_argument("--sharded", action="store_true", help="sequence-sharded decode over log-uniform contexts (torchrun for N > 1)")
     ap.add_argument("--seqs", type=int, default=2048, help="--sharded: concurrent sequences over all GPUs")
+    ap.add_argument("--decode-model", action="store_true", help="pure decode step of the random-init decoder (B, ctx)")
     ap.add_argument("--path", action="store_true", help="each op of the mixed step's attention path timed alone")
     ap.add_argument("--prefill", action="store_true", help="chunked-prefill attention kernel alone, both kernels")
     ap.add_argument("--mixed", action="store_true", help="chunked-prefill + decode step inside the decoder scaffold")
@@ -821,6 +896,8 @@ def main():
         run_prefill(args)
     elif args.path:
         run_path(args)
+    elif args.decode_model:
+        run_decode_model(args)
     elif args.sharded:
         run_sharded(args)
     elif args.impl == "reference":
