@@ -16,6 +16,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import math
 import os
 import statistics
 import subprocess
@@ -409,6 +410,55 @@ def run_sharded(args):
             "aggregate_gbs": round(sum(p["gbs"] for p in per), 1), "per_gpu": per, "all_sequences_served_once": ok}))
     if world > 1:
         dist.destroy_process_group()
+
+
+def run_serve(args):
+    """--serve: offline serving run of the step loop (inference_engine_b200/engine.py) on the random-init
+    Qwen3-1.7B-shaped decoder: 128 requests submitted at once, prompt lengths log-uniform in [32, 1024]
+    (synthetic ids), 128 new tokens each (no stop token), at most 64 running requests, 1024 tokens per step,
+    rows of 2048 tokens, paged int8 cache.  Wall-clock times (the loop reads the sampled tokens back every
+    step, like the reference engine)."""
+    import time
+
+    import torch
+
+    from inference_engine_b200 import kernels as K
+    from inference_engine_b200 import scaffold as S
+    from inference_engine_b200.engine import Engine
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    K.set_early_start(not args.no_early_start)
+    model = S.DecoderScaffold(dev, seed=5)
+    t0 = time.perf_counter()
+    eng = Engine(model, max_batch_size=64, max_len=2048, stop_token_id=-1, max_tokens_per_step=1024, min_first_chunk=64,
+                 max_graph_tokens=512)
+    torch.cuda.synchronize()
+    t_capture = time.perf_counter() - t0
+    g = torch.Generator().manual_seed(5)
+    n_req, new = 128, 128
+    lens = torch.exp(torch.empty(n_req).uniform_(math.log(32), math.log(1024), generator=g)).long().tolist()
+    prompts = [torch.randint(0, S.VOCAB, (n,), generator=g).tolist() for n in lens]
+    for warm in (True, False):
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        reqs = [eng.submit_request(p, new) for p in (prompts[:8] if warm else prompts)]
+        steps = 0
+        while not eng.sched.idle():
+            eng.step()
+            steps += 1
+        torch.cuda.synchronize()
+        wall = time.perf_counter() - t0
+    out_tokens = sum(len(r.output) for r in reqs)
+    ttft = sorted(r.t_first_token - r.t_submit for r in reqs)
+    print(json.dumps({
+        "case": "offline serving run of the step loop", "requests": n_req, "prompt_tokens": sum(lens),
+        "output_tokens": out_tokens, "steps": steps, "wall_s": round(wall, 3),
+        "output_tokens_per_s": round(out_tokens / wall), "total_tokens_per_s": round((out_tokens + sum(lens)) / wall),
+        "ttft_s": {"median": round(ttft[len(ttft) // 2], 3), "max": round(ttft[-1], 3)},
+        "steps_by_kind": eng.steps_run, "graph_capture_s": round(t_capture, 2),
+        "pages": {"pool": eng.pool.capacity, "free_at_end": eng.pool.uncommitted()}, "status": K.check_status(dev),
+        "data": "synthetic ids, random-init weights"}), flush=True)
 
 
 def run_decode_model(args):
@@ -879,6 +929,7 @@ def main():
     ap.add_argument("--no-early-start", action="store_true", help="launch decode attention without programmatic early start")
     ap.add_argument("--sharded", action="store_true", help="sequence-sharded decode over log-uniform contexts (torchrun for N > 1)")
     ap.add_argument("--seqs", type=int, default=2048, help="--sharded: concurrent sequences over all GPUs")
+    ap.add_argument("--serve", action="store_true", help="offline serving run of the step loop on the random-init decoder")
     ap.add_argument("--decode-model", action="store_true", help="pure decode step of the random-init decoder (B, ctx)")
     ap.add_argument("--path", action="store_true", help="each op of the mixed step's attention path timed alone")
     ap.add_argument("--prefill", action="store_true", help="chunked-prefill attention kernel alone, both kernels")
@@ -898,6 +949,8 @@ def main():
         run_path(args)
     elif args.decode_model:
         run_decode_model(args)
+    elif args.serve:
+        run_serve(args)
     elif args.sharded:
         run_sharded(args)
     elif args.impl == "reference":
