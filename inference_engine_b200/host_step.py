@@ -79,7 +79,7 @@ class HostDecodeStep:
                                         cache, self.dev_cached, self.dev_nd, self.eps)
             K.decode_attention(qr, cache, self.dev_cached, self.dev_table, self.dev_nd, D ** -0.5, out=self.dev_out[l])
 
-    def capture(self, groups: int = 4):
+    def capture(self, groups: int = 7):
         """Record device_step into a CUDA graph (two eager warm-up runs first, like engine.py:432-449), and
         once more as `groups` graphs over consecutive layer ranges for the pipelined host-buffer step."""
         s = torch.cuda.Stream()
