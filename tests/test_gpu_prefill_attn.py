@@ -110,3 +110,40 @@ def test_rows_behind_the_prefix_are_never_used(K, variant):
     assert np.isfinite(got).all()
     mx, mean = H.attn_errors(got, want)
     assert mx <= 8e-3 and mean <= 4e-4, (mx, mean)
+
+
+@pytest.mark.parametrize("seed", range(24))
+def test_tcgen05_kernel_agrees_with_mma_kernel_on_random_batches(K, seed):
+    """Random packed batches (chunk lengths 1..700, prefixes 0..900, 1..5 prefilling entries, decoding rows and a
+    padding entry in front / behind, block_m 64 / 128 / 256, GQA groups of 1, 2, 4 and 8): the tcgen05 kernel
+    against the mma.sync kernel, which the oracle tests pin.  Exercises every count of key blocks per warpgroup
+    (0, 1, 2, 3, many), ragged last tiles and prefixes that end inside a key block."""
+    rng = np.random.default_rng(1000 + seed)
+    block_m = int(rng.choice([64, 128, 256]))
+    hkv = int(rng.choice([1, 2, 4, 8]))
+    hq = hkv * int(rng.choice([1, 2, 4, 8]))
+    while hq > 16:
+        hq //= 2
+    nd = int(rng.integers(0, 3))
+    npf = int(rng.integers(1, 6))
+    small = seed % 3 == 0  # every third case: only short chunks and prefixes (few key blocks)
+    chunk = [1] * nd + [int(rng.integers(1, 60 if small else 700)) for _ in range(npf)] + [int(rng.integers(0, 40))]
+    prefix = [0] * nd + [int(rng.choice([0, rng.integers(1, 130 if small else 900)])) for _ in range(npf)] + [0]
+    N = sum(chunk)
+    cu = np.concatenate([[0], np.cumsum(chunk)]).astype(np.int32)
+    cu_cached = np.concatenate([[0], np.cumsum(prefix)]).astype(np.int32)
+    seq_ids = np.concatenate([np.full(L, b) for b, L in enumerate(chunk)]).astype(np.int32)
+    q, k, v = H.randn_bf16(rng, N, hq, D), H.randn_bf16(rng, N, hkv, D), H.randn_bf16(rng, N, hkv, D)
+    cap = int(cu_cached[-1]) + int(rng.integers(1, 70))
+    k_pre, v_pre = H.randn_bf16(rng, hkv, cap, D), H.randn_bf16(rng, hkv, cap, D)
+    tiles = [r for b in range(nd, len(chunk)) for r in range(cu[b], cu[b + 1], block_m)] + [-1] * int(rng.integers(0, 4))
+    args = (H.bf16_tensor(q), H.bf16_tensor(k), H.bf16_tensor(v), H.i32(seq_ids), H.i32(cu), H.i32(tiles),
+            H.bf16_tensor(k_pre), H.bf16_tensor(v_pre), H.i32(cu_cached), block_m)
+    a = K.prefill_attention(*args, variant=1)
+    b = K.prefill_attention(*args, variant=2)
+    assert K.check_status() == 0
+    lo = int(cu[nd])
+    ga, gb = H.to_f32(a)[lo:], H.to_f32(b)[lo:]
+    assert np.isfinite(gb).all()
+    mx, mean = H.attn_errors(gb, ga)
+    assert mx <= 1.6e-2 and mean <= 6e-4, (mx, mean)  # two bf16 roundings of the same fp32 value: one step apart at most
