@@ -465,7 +465,7 @@ def run_decode_model(args):
     """--decode-model: one pure-decode step of the random-init Qwen3-1.7B-shaped decoder at the headline shape
     (B sequences of ctx cached tokens, one new token each, 28 layers, int8 paged cache, random block table):
     embedding -> 28 x (norm, qkv GEMM, quantize-on-write, decode attention, o GEMM, norm, SwiGLU MLP) -> norm ->
-    tied lm_head -> argmax, captured as one CUDA graph.  Reports step time, tokens/s and the attention path's
+    tied lm_head -> sampler (greedy), captured as one CUDA graph.  Reports step time, tokens/s and the attention path's
     share (a second graph with only the write + attention ops on the same caches)."""
     import torch
 
@@ -685,7 +685,7 @@ def run_mixed(args):
     32 decoding sequences (contexts ~U[128,4096]) + one 992-token chunk on a prior context of
     0/1024/2048/3072 tokens = 1024 tokens per step, int8 paged cache (16-token pages, random block
     table).  The step is captured as one CUDA graph (embedding -> 28 layers -> final norm -> tied
-    lm_head -> argmax) and replayed; a second graph holds only the attention-path ops of the 28
+    lm_head -> sampler) and replayed; a second graph holds only the attention-path ops of the 28
     layers on the same metadata, to state their share of the step.  One JSON line per prior."""
     import torch
 

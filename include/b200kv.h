@@ -179,6 +179,17 @@ int b200kv_add_rms_norm(const void* residual, int64_t r_stride, const void* delt
                         const void* weight, void* new_residual, int64_t nr_stride,
                         void* normed, int64_t nn_stride, int32_t N, int32_t D, float eps, void* stream);
 
+/* Replaces sample (kernels.py:1286-1370): Gumbel-max sampling, two kernels.  token[b] = the first index
+ * attaining max_v (logits[b,v] + tau * -log(-log(u))), u = clamp(U(seed, b*V + v), 1e-10, 1 - 1e-7) with the
+ * Philox-4x32-10 uniform of the reference; tau = 0 is greedy argmax.  logits bf16 (elem_bytes 2) or fp32 (4),
+ * row stride in elements; seed = device int64, advanced by one by the call; out = device int64 [B] with stride
+ * out_stride; workspace = b200kv_sample_workspace_bytes(B, V) bytes of device memory (the reference's two
+ * partial buffers). */
+size_t b200kv_sample_workspace_bytes(int32_t B, int32_t V);
+int b200kv_sample(const void* logits, int64_t stride, int32_t elem_bytes, int64_t* seed, float tau,
+                  void* workspace, size_t workspace_bytes, int64_t* out, int64_t out_stride,
+                  int32_t B, int32_t V, void* stream);
+
 /* Chained launches (off by default).  While enabled, every kernel of this library is launched with
  * programmatic stream serialization: it may be brought up while the kernel launched just before it on
  * the same stream is still running, reads only caller-provided metadata (cu_seqlens, cu_cached,

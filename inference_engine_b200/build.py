@@ -29,6 +29,7 @@ UNITS = {
     "prefill_attn.cu": [],
     "prefill_attn_tc5.cu": [],
     "block_ops.cu": [],
+    "sampler.cu": ["-fmad=false"],
     "host_step.cu": [],
 }
 

@@ -21,7 +21,8 @@ need are still uncommitted, so a running request can never run out.  The first p
 scratch run no request owns: padded entries of a graph replay write there.
 
 `Scheduler` is host-only (no torch, no GPU) so that the policy is testable on its own; `Engine` adds the
-device side.  The model is the random-init decoder of scaffold.py; sampling is greedy.
+device side.  The model is the random-init decoder of scaffold.py; sampling is the library's Gumbel-max sampler
+(greedy at tau = 0).
 """
 from __future__ import annotations
 
@@ -177,7 +178,7 @@ class Engine:
 
     def __init__(self, model, max_batch_size: int, max_len: int, stop_token_id: int, page_size: int = 16,
                  num_pages: int | None = None, max_tokens_per_step: int = 1024, min_first_chunk: int = 64,
-                 max_graph_tokens: int = 512, use_graphs: bool = True, block_m: int = 128):
+                 max_graph_tokens: int = 512, use_graphs: bool = True, block_m: int = 128, tau: float = 0.0, seed: int = 0):
         import torch
 
         from . import kernels as K
@@ -185,6 +186,8 @@ class Engine:
 
         self.torch, self.K, self.S = torch, K, S
         self.model, self.device = model, model.device
+        model.tau = float(tau)  # baked into the graphs at capture, like the reference's (engine.py:399)
+        model.seed.fill_(seed)
         self.page_size, self.max_len, self.block_m = page_size, max_len, block_m
         self.max_batch_size = max_batch_size
         self.num_entries = max_batch_size + 1  # every request plus one padding entry

@@ -365,10 +365,21 @@ def add_rms_norm(residual: torch.Tensor, delta: torch.Tensor, rms_norm: torch.Te
 # ----------------------------------------------------------------------------- scaffold ops
 # The remaining names the reference's architecture.py / engine.py import from kernels.py.  They
 # are outside the attention path; plain PyTorch keeps a model built on this module runnable.
-def sample(logits: torch.Tensor, tau: float, seed: torch.Tensor) -> torch.Tensor:  # kernels.py:1341, tau = 0 only
-    if tau != 0:
-        raise NotImplementedError("only greedy sampling (tau = 0) is provided by this scaffold")
-    return logits.argmax(dim=-1, keepdim=True)
+def sample(logits: torch.Tensor, tau: float, seed: torch.Tensor) -> torch.Tensor:
+    """kernels.py:1341-1370: Gumbel-max sampling (tau = 0: greedy argmax), int64 [B, 1]; `seed` (int64 [1] on
+    the device) advances by one."""
+    _require_cuda(logits, seed)
+    assert logits.dim() == 2 and logits.stride(-1) == 1, "kernel assumes contiguous vocab dim"
+    assert logits.dtype in (torch.bfloat16, torch.float32) and seed.dtype == torch.int64
+    B, V = logits.shape
+    lib = _lib.load()
+    nbytes = lib.b200kv_sample_workspace_bytes(B, V)
+    ws = torch.empty(max(nbytes, 8), dtype=torch.uint8, device=logits.device)
+    out = torch.empty(B, 1, dtype=torch.int64, device=logits.device)
+    rc = lib.b200kv_sample(logits.data_ptr(), logits.stride(0), logits.element_size(), seed.data_ptr(), ctypes.c_float(tau),
+                           ws.data_ptr(), nbytes, out.data_ptr(), out.stride(0), B, V, _stream())
+    _lib.check(rc, "sample")
+    return out
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:  # kernels.py:1465

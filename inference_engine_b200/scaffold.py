@@ -179,6 +179,8 @@ class DecoderScaffold:
             for _ in range(layers)
         ]
         self.norm = torch.ones(hidden, device=device, dtype=torch.bfloat16)
+        self.tau = 0.0  # sampling temperature (0 = greedy) and the sampler's seed, advanced by every step
+        self.seed = torch.zeros(1, dtype=torch.int64, device=device)
         self.inv_freq = ROPE_BASE ** (-torch.arange(0, D, 2, dtype=torch.float32, device=device) / D)
 
     def rope(self, positions: torch.Tensor):
@@ -188,7 +190,7 @@ class DecoderScaffold:
     @torch.inference_mode()
     def forward(self, caches, inp: StepInputs | None, ids, cached_lens, slot_ids, num_decoding,
                 prefix: PrefixScratch | None = None):
-        """One step: token ids [N] -> greedy next token per entry [entries] (int64).
+        """One step: token ids [N] -> sampled next token per entry [entries] (int64; greedy while tau = 0).
         `inp is None` = pure decode (ids has one token per entry, position = cached length)."""
         x = self.embed[ids.long()]
         cos, sin = self.rope(cached_lens if inp is None else inp.positions)
@@ -210,4 +212,4 @@ class DecoderScaffold:
         if inp is not None:
             x = x[(inp.cu_seqlens[1:] - 1).long()]  # each entry's last row; junk for entries without tokens
         logits = K.linear(x, self.embed)
-        return logits.argmax(dim=-1)
+        return K.sample(logits, self.tau, self.seed).view(-1)

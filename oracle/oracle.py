@@ -382,3 +382,42 @@ def add_rms_norm(residual, delta, weight, eps: float):
     inv = (F32(1.0) / np.sqrt(ss / F32(D) + F32(eps), dtype=np.float32)).astype(np.float32)
     normed = ((r * inv).astype(np.float32) * np.asarray(weight, np.float32)).astype(np.float32)
     return r, bf16_round(normed)
+
+
+# --------------------------------------------------------------------------- sampler
+def philox4x32_10(c0: np.ndarray, key_lo: int, key_hi: int) -> np.ndarray:
+    """First output word of Philox-4x32 with ten rounds (Salmon et al., "Parallel random numbers: as easy as
+    1, 2, 3", SC'11) for counters (c0, 0, 0, 0) and key (key_lo, key_hi): the generator behind Triton's
+    tl.rand(seed, offset), which the reference's sampler calls with offset = row * V + column
+    (kernels.py:1310) and the 64-bit seed split into the two key words."""
+    M0, M1, W0, W1 = np.uint64(0xD2511F53), np.uint64(0xCD9E8D57), 0x9E3779B9, 0xBB67AE85
+    mask = np.uint64(0xFFFFFFFF)
+    c0 = c0.astype(np.uint64) & mask
+    c1 = np.zeros_like(c0)
+    c2 = np.zeros_like(c0)
+    c3 = np.zeros_like(c0)
+    k0, k1 = key_lo & 0xFFFFFFFF, key_hi & 0xFFFFFFFF
+    for _ in range(10):
+        p0, p1 = M0 * c0, M1 * c2  # 32 x 32 -> 64-bit products
+        c0, c1, c2, c3 = ((p1 >> np.uint64(32)) ^ c1 ^ np.uint64(k0)) & mask, p1 & mask, \
+                         ((p0 >> np.uint64(32)) ^ c3 ^ np.uint64(k1)) & mask, p0 & mask
+        k0, k1 = (k0 + W0) & 0xFFFFFFFF, (k1 + W1) & 0xFFFFFFFF
+    return c0.astype(np.uint32)
+
+
+def sample(logits, tau: float, seed: int) -> np.ndarray:
+    """sample, kernels.py:1286-1370 (Gumbel-max; tau = 0 is argmax): token[b] = the FIRST index attaining
+    max_v (logits[b, v] + tau * -log(-log(u))), u = clamp(uniform(seed, b * V + v), 1e-10, 1 - 1e-7), fp32
+    throughout, products and sums rounded separately.  The uniform is Triton's: the Philox word as a signed
+    int32 x, folded to non-negative (x < 0 -> -x - 1), converted to fp32 and multiplied by 4.6566127342e-10.
+    Returns int64 [B]; the caller's seed advances by one per call (kernels.py:1369)."""
+    z = np.asarray(logits, np.float32)
+    B, V = z.shape
+    off = (np.arange(B, dtype=np.int64)[:, None] * V + np.arange(V, dtype=np.int64)[None, :]).astype(np.uint32)
+    x = philox4x32_10(off, seed & 0xFFFFFFFF, (seed >> 32) & 0xFFFFFFFF).view(np.int32).astype(np.int64)
+    x = np.where(x < 0, -x - 1, x)
+    u = (x.astype(np.float32) * F32(4.6566127342e-10)).astype(np.float32)
+    u = np.clip(u, F32(1e-10), F32(1.0 - 1e-7))
+    gumbel = (-np.log(-np.log(u, dtype=np.float32), dtype=np.float32)).astype(np.float32)
+    z = (z + (F32(tau) * gumbel).astype(np.float32)).astype(np.float32)
+    return np.argmax(z, axis=1).astype(np.int64)  # numpy's argmax returns the first maximum

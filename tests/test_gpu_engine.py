@@ -64,3 +64,12 @@ def test_requests_arriving_while_others_decode():
     assert [len(r.output) for r in first] == [8, 8] and len(late.output) == 5
     assert late.t_first_token >= first[1].t_first_token
     assert eng.pool.uncommitted() == eng.pool.capacity
+
+
+def test_sampling_with_temperature_is_reproducible_from_the_seed():
+    p = prompts()[:4]
+    a = build(True, tau=0.8, seed=11).generate(p, max_new_tokens=5)
+    b = build(True, tau=0.8, seed=11).generate(p, max_new_tokens=5)
+    c = build(True, tau=0.8, seed=12).generate(p, max_new_tokens=5)
+    assert [r.output for r in a] == [r.output for r in b]
+    assert [r.output for r in a] != [r.output for r in c]
