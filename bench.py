@@ -332,6 +332,10 @@ def run_sharded(args):
     pages_per = (lens + PAGE - 1) // PAGE
     num_pages = int(pages_per.sum()) + 1
     max_pages = int(pages_per.max())
+    # never ask for more resident layer caches than fit: one layer of this shard is num_pages x 8 heads x 16 tokens
+    # x (2 x 128 code bytes + 2 x 4 scale bytes); keep them within 60 % of the device's memory
+    layer_bytes = num_pages * HKV * PAGE * (2 * D + 8)
+    L = max(1, min(L, int(0.6 * torch.cuda.get_device_properties(dev).total_memory // layer_bytes)))
     table_np = np.full((B, max_pages), 0, np.int32)
     perm = np.random.default_rng(40 + rank).permutation(num_pages - 1).astype(np.int32)
     at = 0
