@@ -179,12 +179,13 @@ class Engine:
     def __init__(self, model, max_batch_size: int, max_len: int, stop_token_id: int, page_size: int = 16,
                  num_pages: int | None = None, max_tokens_per_step: int = 1024, min_first_chunk: int = 64,
                  max_graph_tokens: int = 512, use_graphs: bool = True, block_m: int = 128, tau: float = 0.0, seed: int = 0):
+        import numpy as np
         import torch
 
         from . import kernels as K
         from . import scaffold as S
 
-        self.torch, self.K, self.S = torch, K, S
+        self.torch, self.K, self.S, self.np = torch, K, S, np
         self.model, self.device = model, model.device
         model.tau = float(tau)  # baked into the graphs at capture, like the reference's (engine.py:399)
         model.seed.fill_(seed)
@@ -213,6 +214,10 @@ class Engine:
         capd = sum(self.decode_layout())
         self.host_decode = torch.empty(capd, dtype=torch.int32).pin_memory()
         self.dev_decode = torch.zeros(capd, dtype=torch.int32, device=self.device)
+        self.np_mixed, self.np_decode = self.host_mixed.numpy(), self.host_decode.numpy()  # same memory
+        self.rows: dict[int, tuple] = {}  # request id -> (pages copied so far, its block-table row as an array)
+        self.scratch_row = self.np.zeros(self.max_pages, self.np.int32)
+        self.scratch_row[: self.scratch_pages] = self.np.arange(self.scratch_pages)
         self.prefix_capacity = 2 * max_len
         self.prefix_k = torch.empty(S.HKV, self.prefix_capacity, S.D, device=self.device, dtype=torch.bfloat16)
         self.prefix_v = torch.empty_like(self.prefix_k)
@@ -220,6 +225,7 @@ class Engine:
         self.decode_graphs: dict[int, tuple] = {}
         self.mixed_graphs: dict[int, tuple] = {}
         self.steps_run = {"decode_graph": 0, "mixed_graph": 0, "eager": 0}
+        self.seconds = {"plan": 0.0, "run (inputs, launch, read-back)": 0.0, "commit": 0.0, "inputs": 0.0}
         if use_graphs:
             self.capture()
 
@@ -234,11 +240,20 @@ class Engine:
         return reqs
 
     def step(self) -> list[Request]:
+        t0 = time.perf_counter()
         step = self.sched.plan()
         if step is None:
             return []
+        t1 = time.perf_counter()
         tokens = self.run_decode(step) if step.decode_only else self.run_mixed(step)
-        return self.sched.commit(step, tokens)
+        t2 = time.perf_counter()
+        finished = self.sched.commit(step, tokens)
+        for r in finished:
+            self.rows.pop(r.id, None)
+        self.seconds["plan"] += t1 - t0
+        self.seconds["run (inputs, launch, read-back)"] += t2 - t1
+        self.seconds["commit"] += time.perf_counter() - t2
+        return finished
 
     # ------------------------------------------------------------------ input buffers
     def mixed_layout(self, n_tokens: int) -> list[int]:
@@ -254,8 +269,15 @@ class Engine:
         B = self.max_batch_size
         return [B, B, 1, B * self.max_pages]
 
-    def table_row(self, pages: list[int]) -> list[int]:
-        return pages + [0] * (self.max_pages - len(pages))
+    def table_row(self, r: Request):
+        """The request's block-table row as an int32 array, extended in place as pages are appended."""
+        n, row = self.rows.get(r.id, (0, None))
+        if row is None:
+            row = self.np.zeros(self.max_pages, self.np.int32)
+        if n < len(r.pages):
+            row[n : len(r.pages)] = r.pages[n:]
+            self.rows[r.id] = (len(r.pages), row)
+        return row
 
     def fill_mixed(self, step: Step, n_pad: int):
         """Build the step's metadata on the host (scaffold.plan_step = the reference's fill_inputs), one copy."""
@@ -263,18 +285,24 @@ class Engine:
         nd = step.num_decoding
         plan = S.plan_step([r.cached_len for r, _ in step.entries[:nd]],
                            [(r.cached_len, len(t)) for r, t in step.entries[nd:]], n_pad, self.num_entries, self.block_m)
-        ids = [tok for _, toks in step.entries for tok in toks]
-        ids += [0] * (n_pad - len(ids))
-        table = [self.table_row(r.pages) for r, _ in step.entries]
-        table.append(self.table_row(list(range(self.scratch_pages))))  # the padding entry lives on the scratch run
-        table += [self.table_row([])] * (self.num_entries - len(table))
-        fields = [ids, plan["positions"], plan["seq_ids"], plan["cu_seqlens"], plan["cached"], plan["cu_cached"],
-                  plan["tile_start"], plan["num_decoding"], [p for row in table for p in row]]
+        np = self.np
         sizes = self.mixed_layout(n_pad)
-        assert [len(f) for f in fields] == sizes
-        flat = [x for f in fields for x in f]
-        self.host_mixed[: len(flat)].copy_(torch.tensor(flat, dtype=torch.int32))
-        self.dev_mixed[: len(flat)].copy_(self.host_mixed[: len(flat)], non_blocking=True)
+        buf = self.np_mixed[: sum(sizes)]
+        offs = [0]
+        for n in sizes:
+            offs.append(offs[-1] + n)
+        ids = [tok for _, toks in step.entries for tok in toks]
+        buf[offs[0] : offs[0] + len(ids)] = ids
+        buf[offs[0] + len(ids) : offs[1]] = 0
+        for i, key in enumerate(("positions", "seq_ids", "cu_seqlens", "cached", "cu_cached", "tile_start", "num_decoding"), 1):
+            assert len(plan[key]) == sizes[i]
+            buf[offs[i] : offs[i + 1]] = plan[key]
+        table = buf[offs[8] : offs[9]].reshape(self.num_entries, self.max_pages)
+        for i, (r, _) in enumerate(step.entries):
+            table[i] = self.table_row(r)
+        table[len(step.entries)] = self.scratch_row  # the padding entry lives on the scratch run
+        table[len(step.entries) + 1 :] = 0
+        self.dev_mixed[: len(buf)].copy_(self.host_mixed[: len(buf)], non_blocking=True)
         return plan["cu_cached"][-1]
 
     def mixed_views(self, n_pad: int, prefix_tokens: int = 0):
@@ -332,15 +360,21 @@ class Engine:
 
     def run_decode(self, step: Step) -> list[int]:
         torch = self.torch
+        t_in = time.perf_counter()
         B = len(step.entries)
         b = next(x for x in self.graph_buckets if x >= B)
-        Bm = self.max_batch_size
-        ids = [t[0] for _, t in step.entries] + [0] * (Bm - B)
-        cached = [r.cached_len for r, _ in step.entries] + [0] * (Bm - B)
-        table = [p for r, _ in step.entries for p in self.table_row(r.pages)] + [0] * ((Bm - B) * self.max_pages)
-        flat = ids + cached + [B] + table
-        self.host_decode.copy_(torch.tensor(flat, dtype=torch.int32))
+        Bm, buf = self.max_batch_size, self.np_decode
+        buf[:B] = [t[0] for _, t in step.entries]
+        buf[Bm : Bm + B] = [r.cached_len for r, _ in step.entries]
+        buf[B:Bm] = 0
+        buf[Bm + B : 2 * Bm] = 0
+        buf[2 * Bm] = B
+        table = buf[2 * Bm + 1 :].reshape(Bm, self.max_pages)
+        for i, (r, _) in enumerate(step.entries):
+            table[i] = self.table_row(r)
+        table[B:] = 0
         self.dev_decode.copy_(self.host_decode, non_blocking=True)
+        self.seconds["inputs"] += time.perf_counter() - t_in
         if b in self.decode_graphs:
             g, out = self.decode_graphs[b]
             g.replay()
@@ -355,7 +389,9 @@ class Engine:
         torch = self.torch
         N = step.num_tokens
         n_pad = next((x for x in self.token_buckets if x >= N), N)
+        t_in = time.perf_counter()
         prefix_tokens = self.fill_mixed(step, n_pad)
+        self.seconds["inputs"] += time.perf_counter() - t_in
         if n_pad in self.mixed_graphs and prefix_tokens <= self.prefix_capacity:
             g, out = self.mixed_graphs[n_pad]
             g.replay()
