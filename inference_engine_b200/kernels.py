@@ -1,11 +1,13 @@
-"""Drop-in replacement for the attention ops of the reference engine's `kernels.py`.
+"""Drop-in replacement for the ops of the reference engine's `kernels.py`.
 
 Same names, positional signatures and semantics as kbwal/inference-engine
 qwen3-1.7b/kernels.py (LayerKVCache :11-17, decode_attention :272-361, fused_rope_kv_decode
 :483-544, fused_norm_rope_prefill :673-714, quantize_kv_prefill :826-865,
-dequantize_kv_prefix :935-970, prefill_attention :1129-1175), backed by hand-written sm_100a
-CUDA kernels reached through the C ABI in include/b200kv.h.  There is no Triton, no other
-backend and no CPU fallback: without a CUDA device and the built library every op raises.
+dequantize_kv_prefix :935-970, prefill_attention :1129-1175, silu_mul :1204-1212,
+add_rms_norm :1261-1285, sample :1341-1370), backed by hand-written sm_100a CUDA kernels
+reached through the C ABI in include/b200kv.h.  There is no Triton, no other backend and no
+CPU fallback: without a CUDA device and the built library every op raises.  `linear` and
+`tune_linear` (:1465-1485) stay plain PyTorch (cuBLAS through F.linear).
 
 One generalisation: wherever the reference takes `slot_ids [B]` (one contiguous cache row per
 sequence), a 2-D int32 block table `[B, max_pages]` is accepted as well, in which case the
