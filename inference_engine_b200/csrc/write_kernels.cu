@@ -196,15 +196,17 @@ norm_rope_prefill_kernel(const uint16_t* __restrict__ q, long long q_sn, long lo
 }
 
 // ------------------------------------------------------------------ prefill quantize
-// Entry of packed row r: the last b with cu_seqlens[b] <= r (empty entries share a start with
-// their successor and are skipped by taking the last).
-__device__ __forceinline__ int entry_of_row(const int32_t* cu, int num_entries, int r) {
-  int lo = 0, hi = num_entries;  // answer in [lo, hi)
-  while (hi - lo > 1) {
-    int mid = (lo + hi) >> 1;
-    if (cu[mid] <= r) lo = mid; else hi = mid;
+// Entry of packed row r, found by a whole warp: every lane tests one entry per round, so the answer costs one or
+// two rounds of memory latency instead of log2(entries) dependent ones.  The entry holding row r is the one
+// with cu[e] <= r < cu[e+1] (an empty entry never matches).  Returns -1 when r is past the last entry.
+__device__ __forceinline__ int entry_of_row_warp(const int32_t* cu, int num_entries, int r, int lane) {
+  for (int e0 = 0; e0 < num_entries; e0 += 32) {
+    const int e = e0 + lane;
+    const bool hit = e < num_entries && cu[e] <= r && r < cu[e + 1];
+    const unsigned m = __ballot_sync(0xffffffffu, hit);
+    if (m) return e0 + __ffs(m) - 1;
   }
-  return lo;
+  return -1;
 }
 
 __device__ __forceinline__ bool is_first_chunk(int b, int nd, const int32_t* cu, const int32_t* cached_lens) {
@@ -261,19 +263,20 @@ quantize_prefill_kernel(const uint16_t* __restrict__ k, long long k_sn, long lon
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int job = blockIdx.y * kWarpsPerBlock + warp;
   if (job >= 2 * c.Hkv) return;
-  const int b = entry_of_row(cu, num_entries, r);
-  if (b < *num_decoding) return;
+  const int b = entry_of_row_warp(cu, num_entries, r, lane);
+  if (b < 0 || b < *num_decoding) return;
   pdl_wait();  // k, v and the calibration come from the kernels before this one
+  float x[4];
+  if (job < c.Hkv) load4_bf16(k + r * k_sn + job * k_sh, lane, x);  // in flight during the page lookups
+  else load4_bf16(v + r * v_sn + (job - c.Hkv) * v_sh, lane, x);
   const int pos = cached_lens[b] + (r - cu[b]);
   const int page = lookup_page(c, b, pos, status);
   if (page < 0) return;
   const int row = pos % c.page_size;
-  float x[4];
   if (job < c.Hkv) {
     const int page0 = lookup_page(c, b, 0, status);
     if (page0 < 0) return;
     float cal[4];
-    load4_bf16(k + r * k_sn + job * k_sh, lane, x);
     load4_f32(c.k_cal + page0 * c.cstride_page + job * c.cstride_head, lane, cal);
 #pragma unroll
     for (int i = 0; i < 4; ++i) x[i] = __fdiv_rn(x[i], cal[i]);
@@ -281,7 +284,6 @@ quantize_prefill_kernel(const uint16_t* __restrict__ k, long long k_sn, long lon
                    c.k_scale + page * c.sstride_page + job * c.sstride_head + row, lane);
   } else {
     const int j = job - c.Hkv;
-    load4_bf16(v + r * v_sn + j * v_sh, lane, x);
     quantize_store(x, c.v + page * c.stride_page + j * c.stride_head + row * c.stride_tok,
                    c.v_scale + page * c.sstride_page + j * c.sstride_head + row, lane);
   }
