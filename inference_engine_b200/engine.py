@@ -281,11 +281,9 @@ class Engine:
 
     def fill_mixed(self, step: Step, n_pad: int):
         """Build the step's metadata on the host (scaffold.plan_step = the reference's fill_inputs), one copy."""
-        torch, S = self.torch, self.S
         nd = step.num_decoding
-        plan = S.plan_step([r.cached_len for r, _ in step.entries[:nd]],
+        plan = self.S.plan_step([r.cached_len for r, _ in step.entries[:nd]],
                            [(r.cached_len, len(t)) for r, t in step.entries[nd:]], n_pad, self.num_entries, self.block_m)
-        np = self.np
         sizes = self.mixed_layout(n_pad)
         buf = self.np_mixed[: sum(sizes)]
         offs = [0]
