@@ -14,6 +14,8 @@
  *     enqueued on it; no entry point synchronises, allocates, frees or keeps a pointer after
  *     it returns, and every grid is a function of the shape arguments only, so calls may be
  *     captured in a CUDA graph (the reference engine does: engine.py:376-449).
+ *   - An empty batch (zero entries / zero rows) is valid: the call returns B200KV_OK at once, whatever the
+ *     pointers are (empty tensors have no storage).
  *   - Return value: B200KV_OK, or a negative B200KV_E_* code, in which case NOTHING was
  *     launched.  `status` (optional, may be NULL) is a device int32 the kernels OR error bits
  *     into when device-side data is inconsistent (a page id or token position out of range):

@@ -97,6 +97,8 @@ using namespace b200kv;
 
 extern "C" int b200kv_silu_mul(const void* gate_up, int64_t in_stride, void* out, int64_t out_stride, int32_t N, int32_t D,
                                void* stream) {
+  // an empty batch is valid and has nothing to launch (its tensors have no storage, so their pointers are NULL)
+  if (N == 0) return B200KV_OK;
   if (!gate_up || !out) return B200KV_E_NULL;
   if (N < 0 || D < 1 || D % kBoVec) return B200KV_E_SHAPE;
   if (!aligned(gate_up, 16) || !aligned(out, 16) || in_stride % kBoVec || out_stride % kBoVec) return B200KV_E_ALIGN;
@@ -111,6 +113,8 @@ extern "C" int b200kv_silu_mul(const void* gate_up, int64_t in_stride, void* out
 extern "C" int b200kv_add_rms_norm(const void* residual, int64_t r_stride, const void* delta, int64_t d_stride,
                                    const void* weight, void* new_residual, int64_t nr_stride, void* normed,
                                    int64_t nn_stride, int32_t N, int32_t D, float eps, void* stream) {
+  // an empty batch is valid and has nothing to launch (its tensors have no storage, so their pointers are NULL)
+  if (N == 0) return B200KV_OK;
   if (!residual || !delta || !weight || !new_residual || !normed) return B200KV_E_NULL;
   if (N < 0 || D < 1 || D % kBoVec) return B200KV_E_SHAPE;
   if (D > kBoThreads * kBoVec * kBoMaxChunks) return B200KV_E_RANGE;

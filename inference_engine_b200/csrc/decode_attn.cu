@@ -964,6 +964,8 @@ extern "C" int b200kv_decode_attn(const void* q, int64_t q_sb, int64_t q_sh, con
                                   float scale, void* out, int64_t o_sb, int64_t o_sh, void* workspace,
                                   size_t workspace_bytes, int32_t B, int32_t Hq, int32_t sm_count, int32_t variant,
                                   int32_t* status, void* stream) {
+  // an empty batch is valid and has nothing to launch (its tensors have no storage, so their pointers are NULL)
+  if (B == 0) return B200KV_OK;
   if (!q || !cached_lens || !num_decoding || !out || !workspace) return B200KV_E_NULL;
   int rc = check_cache(cache, table);
   if (rc) return rc;

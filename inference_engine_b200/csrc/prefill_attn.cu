@@ -234,6 +234,8 @@ extern "C" int b200kv_prefill_attn_variant(const void* q, int64_t q_sn, int64_t 
                                            int64_t p_sn, int32_t prefix_rows, const int32_t* cu_cached, void* out,
                                            int64_t o_sn, int64_t o_sh, int32_t N, int32_t Hq, int32_t Hkv, int32_t D,
                                            int32_t variant, int32_t* status, void* stream) {
+  // an empty batch is valid and has nothing to launch (its tensors have no storage, so their pointers are NULL)
+  if (N == 0 || num_tiles == 0) return B200KV_OK;
   if (!q || !k || !v || !seq_ids || !cu_seqlens || !tile_start || !k_prefix || !v_prefix || !cu_cached || !out)
     return B200KV_E_NULL;
   if (D != kD || Hq < 1 || Hkv < 1 || Hq % Hkv || N < 0 || num_tiles < 0 || block_m < 1 || prefix_rows < 0)

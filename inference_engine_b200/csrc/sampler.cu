@@ -111,6 +111,8 @@ extern "C" size_t b200kv_sample_workspace_bytes(int32_t B, int32_t V) {
 
 extern "C" int b200kv_sample(const void* logits, int64_t stride, int32_t elem_bytes, int64_t* seed, float tau, void* workspace,
                              size_t workspace_bytes, int64_t* out, int64_t out_stride, int32_t B, int32_t V, void* stream) {
+  // an empty batch is valid and has nothing to launch (its tensors have no storage, so their pointers are NULL)
+  if (B == 0) return B200KV_OK;
   if (!logits || !seed || !workspace || !out) return B200KV_E_NULL;
   if (B < 0 || V < 1 || (elem_bytes != 2 && elem_bytes != 4)) return B200KV_E_SHAPE;
   if ((long long)B * V > 0x7FFFFFFFll) return B200KV_E_RANGE;  // the counter b * V + v is 32-bit, as in the reference

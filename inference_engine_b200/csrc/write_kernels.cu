@@ -367,6 +367,8 @@ extern "C" int b200kv_write_decode(const void* q, int64_t q_sb, int64_t q_sh, co
                                    const b200kv_cache* cache, const b200kv_table* table, const int32_t* cached_lens,
                                    const int32_t* num_decoding, void* q_out, int64_t o_sb, int64_t o_sh, int32_t B,
                                    int32_t Hq, float eps, int32_t* status, void* stream) {
+  // an empty batch is valid and has nothing to launch (its tensors have no storage, so their pointers are NULL)
+  if (B == 0) return B200KV_OK;
   if (!q || !k || !v || !qw || !kw || !cosp || !sinp || !cached_lens || !num_decoding || !q_out) return B200KV_E_NULL;
   int rc = check_cache(cache, table);
   if (rc) return rc;
@@ -392,6 +394,8 @@ extern "C" int b200kv_norm_rope_prefill(const void* q, int64_t q_sn, int64_t q_s
                                         const void* sinp, int64_t sin_sn, void* q_out, int64_t qo_sn, int64_t qo_sh,
                                         void* k_out, int64_t ko_sn, int64_t ko_sh, int32_t N, int32_t Hq, int32_t Hkv,
                                         int32_t D, float eps, void* stream) {
+  // an empty batch is valid and has nothing to launch (its tensors have no storage, so their pointers are NULL)
+  if (N == 0) return B200KV_OK;
   if (!q || !k || !qw || !kw || !cosp || !sinp || !q_out || !k_out) return B200KV_E_NULL;
   if (D != kD || Hq < 1 || Hkv < 1 || N < 0) return B200KV_E_SHAPE;
   if (!aligned(q, 8) || !aligned(k, 8) || !aligned(qw, 8) || !aligned(kw, 8) || !aligned(cosp, 8) || !aligned(sinp, 8) ||
@@ -413,6 +417,8 @@ extern "C" int b200kv_quantize_prefill(const void* k, int64_t k_sn, int64_t k_sh
                                        int64_t v_sh, const int32_t* cu_seqlens, int32_t num_entries,
                                        const b200kv_cache* cache, const b200kv_table* table, const int32_t* cached_lens,
                                        const int32_t* num_decoding, int32_t N, int32_t* status, void* stream) {
+  // an empty batch is valid and has nothing to launch (its tensors have no storage, so their pointers are NULL)
+  if (N == 0 || num_entries == 0) return B200KV_OK;
   if (!k || !v || !cu_seqlens || !cached_lens || !num_decoding) return B200KV_E_NULL;
   int rc = check_cache(cache, table);
   if (rc) return rc;
@@ -434,6 +440,8 @@ extern "C" int b200kv_quantize_prefill(const void* k, int64_t k_sn, int64_t k_sh
 extern "C" int b200kv_dequant_prefix(const b200kv_cache* cache, const b200kv_table* table, const int32_t* cu_cached,
                                      int32_t num_entries, void* k_out, void* v_out, int64_t o_sh, int64_t o_sn,
                                      int32_t capacity, int32_t* status, void* stream) {
+  // an empty batch is valid and has nothing to launch (its tensors have no storage, so their pointers are NULL)
+  if (num_entries == 0 || capacity == 0) return B200KV_OK;
   if (!cu_cached || !k_out || !v_out) return B200KV_E_NULL;
   int rc = check_cache(cache, table);
   if (rc) return rc;
