@@ -154,7 +154,10 @@ int b200kv_prefill_attn(const void* q, int64_t q_stride_n, int64_t q_stride_h,
  * variant 0 = automatic (what b200kv_prefill_attn does: the tcgen05 kernel when block_m >= 64,
  * else the mma.sync kernel), 1 = the mma.sync kernel (64-row CTAs, register accumulators),
  * 2 = the tcgen05 kernel (128-row CTAs, accumulators in tensor memory).  Both give results within
- * the attention tolerance of each other; they differ in summation order.  prefix_rows = rows each
+ * the attention tolerance of each other; they differ in summation order.  3 = a test mode of the tcgen05
+ * kernel: its issuing warps stay idle and every wait gives up after a few thousand polls, so all of the
+ * kernel's bounded waits run out; the call must come back with B200KV_S_TIMEOUT in the status word and
+ * no output row written (the time-out path, exercised without faulting the GPU).  prefix_rows = rows each
  * kv head of k_prefix / v_prefix holds (their shape[1]); it bounds the tensor-map copies of the
  * tcgen05 kernel.  0 = unknown: prefix tiles are then fetched with plain asynchronous copies. */
 int b200kv_prefill_attn_variant(const void* q, int64_t q_stride_n, int64_t q_stride_h,

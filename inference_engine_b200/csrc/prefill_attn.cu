@@ -224,7 +224,7 @@ int launch_prefill_attn_tc5(const uint16_t* q, long long q_sn, long long q_sh, c
                             const int32_t* cu_seqlens, const int32_t* tile_start, int num_tiles, int block_m,
                             const uint16_t* k_prefix, const uint16_t* v_prefix, long long p_sh, long long p_sn,
                             int prefix_rows, const int32_t* cu_cached, uint16_t* out, long long o_sn, long long o_sh, int N,
-                            int Hq, int Hkv, float scale_log2, int32_t* status, cudaStream_t stream);
+                            int Hq, int Hkv, float scale_log2, int32_t* status, int idle_issuers, cudaStream_t stream);
 }
 
 extern "C" int b200kv_prefill_attn_variant(const void* q, int64_t q_sn, int64_t q_sh, const void* k, int64_t k_sn,
@@ -240,7 +240,7 @@ extern "C" int b200kv_prefill_attn_variant(const void* q, int64_t q_sn, int64_t 
     return B200KV_E_NULL;
   if (D != kD || Hq < 1 || Hkv < 1 || Hq % Hkv || N < 0 || num_tiles < 0 || block_m < 1 || prefix_rows < 0)
     return B200KV_E_SHAPE;
-  if (variant < 0 || variant > 2) return B200KV_E_RANGE;
+  if (variant < 0 || variant > 3) return B200KV_E_RANGE;
   if (!aligned(q, 16) || !aligned(k, 16) || !aligned(v, 16) || !aligned(k_prefix, 16) || !aligned(v_prefix, 16) ||
       !aligned(out, 16))
     return B200KV_E_ALIGN;
@@ -252,12 +252,12 @@ extern "C" int b200kv_prefill_attn_variant(const void* q, int64_t q_sn, int64_t 
   const float scale_log2 = (1.0f / sqrtf((float)D)) * 1.4426950408889634f;
   // Query tiles of at least 64 rows fill a 128-row tcgen05 tile well enough to pay; smaller ones stay
   // on the 64-row mma.sync kernel.
-  const bool tc5 = variant == 2 || (variant == 0 && block_m >= 64);
+  const bool tc5 = variant >= 2 || (variant == 0 && block_m >= 64);
   if (tc5)
     return launch_prefill_attn_tc5((const uint16_t*)q, q_sn, q_sh, (const uint16_t*)k, k_sn, k_sh, (const uint16_t*)v, v_sn,
                                    v_sh, seq_ids, cu_seqlens, tile_start, num_tiles, block_m, (const uint16_t*)k_prefix,
                                    (const uint16_t*)v_prefix, p_sh, p_sn, prefix_rows, cu_cached, (uint16_t*)out, o_sn, o_sh, N,
-                                   Hq, Hkv, scale_log2, status, (cudaStream_t)stream);
+                                   Hq, Hkv, scale_log2, status, variant == 3 ? 1 : 0, (cudaStream_t)stream);
   const int subs = (block_m + kPfRows - 1) / kPfRows;
   const size_t smem = 4 * (size_t)kPfTileBytes;
   if (cudaFuncSetAttribute(prefill_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)

@@ -75,8 +75,8 @@ __device__ __forceinline__ void t5_mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count) : "memory");
 }
 // Bounded wait for the phase with the given parity; false when the limit ran out.
-__device__ __forceinline__ bool t5_mbar_wait(uint32_t bar, uint32_t parity) {
-  for (uint32_t spin = 0; spin < kT5SpinLimit; ++spin) {
+__device__ __forceinline__ bool t5_mbar_wait(uint32_t bar, uint32_t parity, uint32_t limit) {
+  for (uint32_t spin = 0; spin < limit; ++spin) {
     uint32_t done;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
@@ -173,8 +173,12 @@ prefill_attn_tc5_kernel(const uint16_t* __restrict__ q, long long q_sn, long lon
                         long long p_sn, const int32_t* __restrict__ cu_cached, uint16_t* __restrict__ out, long long o_sn,
                         long long o_sh, int N, int G, float scale_log2, int32_t* status,
                         const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
-                        const __grid_constant__ CUtensorMap tm_kp, const __grid_constant__ CUtensorMap tm_vp, int prefix_tma) {
+                        const __grid_constant__ CUtensorMap tm_kp, const __grid_constant__ CUtensorMap tm_vp, int prefix_tma,
+                        int idle_issuers) {
   extern __shared__ uint8_t t5_raw[];
+  // idle_issuers (a test mode): the issuing warps do nothing and every wait gives up after a few thousand polls,
+  // so that all bounded waits of the kernel run out and the time-out path is exercised without a fault
+  const uint32_t spin = idle_issuers ? 4096u : kT5SpinLimit;
   // The first CTA waits for the predecessor on every path (a grid in which no CTA waited could complete before
   // it); the trigger for the successor comes late, from the softmax threads when their last block is done: a
   // successor brought up while this kernel is in full swing would only sit on the SMs.
@@ -277,7 +281,7 @@ prefill_attn_tc5_kernel(const uint16_t* __restrict__ q, long long q_sn, long lon
         const uint32_t dst = (is_v ? ring_v(w) : ring_k(w)) + sl * kT5KvBytes;
         const uint32_t full = is_v ? bar_vf(w, sl) : bar_kf(w, sl), empty = is_v ? bar_ve(w, sl) : bar_ke(w, sl);
         // the product that read this slot three blocks ago has completed
-        if (h >= 3 && !t5_mbar_wait(empty, (h / 3 - 1) & 1)) { live = false; break; }
+        if (h >= 3 && !t5_mbar_wait(empty, (h / 3 - 1) & 1, spin)) { live = false; break; }
         if (tma) {
           if (lane == 0) {
             t5_mbar_expect_tx(full, kT5KvBytes);
@@ -303,15 +307,15 @@ prefill_attn_tc5_kernel(const uint16_t* __restrict__ q, long long q_sn, long lon
     // instruction only the start-address field moves.  The issue of a product blocks while the tensor core's
     // queue is full, and this lane's waits and commits are not hidden behind its own products; with one
     // issuing lane per warpgroup the bookkeeping of one overlaps the products of the other.
-    if (lane == 0) {
+    if (lane == 0 && !idle_issuers) {
       const int w = warp - 8, n = n_blk[w];
       const uint64_t dq = t5_desc(sQ, 16, 1024), dk = t5_desc(ring_k(w), 16, 1024);
       const uint64_t dv = t5_desc(ring_v(w), kT5Keys * 128, 1024);
       const uint32_t tw = tmem + 256 * w;
-      bool live = t5_mbar_wait(bar_q, 0);
+      bool live = t5_mbar_wait(bar_q, 0, spin);
       auto issue_s = [&](int h) {  // S(h) = Q K(h)^T into S buffer h & 1, then the arrivals
         const int sl = h % 3;
-        if (!t5_mbar_wait(bar_kf(w, sl), (h / 3) & 1)) { live = false; return; }
+        if (!t5_mbar_wait(bar_kf(w, sl), (h / 3) & 1, spin)) { live = false; return; }
         const uint64_t kd = dk + (uint64_t)(sl * (kT5KvBytes >> 4));
         const uint32_t d = tw + 64 * (h & 1);
 #pragma unroll
@@ -326,7 +330,7 @@ prefill_attn_tc5_kernel(const uint16_t* __restrict__ q, long long q_sn, long lon
       for (int h = 0; h < n && live; ++h) {
         const int sl = h % 3;
         // P(h) is stored and V(h) has landed
-        if (!t5_mbar_wait(bar_r(w, h & 1), (h >> 1) & 1) || !t5_mbar_wait(bar_vf(w, sl), (h / 3) & 1)) {
+        if (!t5_mbar_wait(bar_r(w, h & 1), (h >> 1) & 1, spin) || !t5_mbar_wait(bar_vf(w, sl), (h / 3) & 1, spin)) {
           live = false;
           break;
         }
@@ -350,7 +354,7 @@ prefill_attn_tc5_kernel(const uint16_t* __restrict__ q, long long q_sn, long lon
     float m_ref = -INFINITY, l = 0.f;  // offset of the exponentials (log2 units, scaled), running sum
     bool ok = true;
     for (int h = 0; h < n_mine && ok; ++h) {
-      ok = t5_mbar_wait(bar_s(wg, h & 1), (h >> 1) & 1);  // S(h) is complete
+      ok = t5_mbar_wait(bar_s(wg, h & 1), (h >> 1) & 1, spin);  // S(h) is complete
       t5_fence_after();
       // ---- softmax of this thread's row
       const int kb = wg + 2 * h;
@@ -377,7 +381,7 @@ prefill_attn_tc5_kernel(const uint16_t* __restrict__ q, long long q_sn, long lon
           // O must be at rest: P V(h-1) may still be queued.  Its completion is what S(h+1)'s barrier (or, for
           // the last block, the barrier of the last-but-one P V) reports; waiting for that phase here and again
           // at the top of the next block is harmless.
-          ok = ok && (h + 1 < n_mine ? t5_mbar_wait(bar_s(wg, (h + 1) & 1), ((h + 1) >> 1) & 1) : t5_mbar_wait(bar_o(wg, 0), 0));
+          ok = ok && (h + 1 < n_mine ? t5_mbar_wait(bar_s(wg, (h + 1) & 1), ((h + 1) >> 1) & 1, spin) : t5_mbar_wait(bar_o(wg, 0), 0, spin));
           t5_fence_after();
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
@@ -416,7 +420,7 @@ prefill_attn_tc5_kernel(const uint16_t* __restrict__ q, long long q_sn, long lon
       if (ok) t5_mbar_arrive(bar_r(wg, h & 1));  // hand P(h) to the issuing warp
     }
     pdl_trigger();
-    if (n_mine > 0 && ok) ok = t5_mbar_wait(bar_o(wg, 1), 0);  // the last P V
+    if (n_mine > 0 && ok) ok = t5_mbar_wait(bar_o(wg, 1), 0, spin);  // the last P V
     t5_fence_after();
     if (!ok) t5_sts_u32(dead_flag, 1);
     m_ref_keep = m_ref;
@@ -522,7 +526,7 @@ int launch_prefill_attn_tc5(const uint16_t* q, long long q_sn, long long q_sh, c
                             const int32_t* cu_seqlens, const int32_t* tile_start, int num_tiles, int block_m,
                             const uint16_t* k_prefix, const uint16_t* v_prefix, long long p_sh, long long p_sn,
                             int prefix_rows, const int32_t* cu_cached, uint16_t* out, long long o_sn, long long o_sh, int N,
-                            int Hq, int Hkv, float scale_log2, int32_t* status, cudaStream_t stream) {
+                            int Hq, int Hkv, float scale_log2, int32_t* status, int idle_issuers, cudaStream_t stream) {
   // the opt-in is a per-device attribute of the function: set it on every call (it is cheap)
   if (cudaFuncSetAttribute(prefill_attn_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kT5Smem) !=
       cudaSuccess)
@@ -539,7 +543,7 @@ int launch_prefill_attn_tc5(const uint16_t* q, long long q_sn, long long q_sh, c
   const cudaError_t le = launch_chained(prefill_attn_tc5_kernel, dim3(Hq, num_tiles * subs), dim3(kT5Threads), kT5Smem, stream,
                                         q, q_sn, q_sh, k, k_sn, k_sh, v, v_sn, v_sh, seq_ids, cu_seqlens, tile_start, block_m, subs,
                                         k_prefix, v_prefix, p_sh, p_sn, cu_cached, out, o_sn, o_sh, N, Hq / Hkv, scale_log2, status,
-                                        tm_k, tm_v, tm_kp, tm_vp, prefix_tma);
+                                        tm_k, tm_v, tm_kp, tm_vp, prefix_tma, idle_issuers);
   return le == cudaSuccess && cudaGetLastError() == cudaSuccess ? B200KV_OK : B200KV_E_LAUNCH;
 }
 

@@ -147,3 +147,39 @@ def test_tcgen05_kernel_agrees_with_mma_kernel_on_random_batches(K, seed):
     assert np.isfinite(gb).all()
     mx, mean = H.attn_errors(gb, ga)
     assert mx <= 1.6e-2 and mean <= 6e-4, (mx, mean)  # two bf16 roundings of the same fp32 value: one step apart at most
+
+
+def test_bounded_waits_run_out_cleanly(K):
+    """variant 3: the tcgen05 kernel with idle issuing warps and short wait limits.  Every wait inside the kernel
+    gives up; the call must return, report B200KV_S_TIMEOUT (4) in the status word, write no output row and leave
+    the GPU in a state where the next call works."""
+    from inference_engine_b200 import _lib
+
+    rng = np.random.default_rng(77)
+    chunk, prefix = [300, 0], [200, 0]
+    N = sum(chunk)
+    cu = np.concatenate([[0], np.cumsum(chunk)]).astype(np.int32)
+    cu_cached = np.concatenate([[0], np.cumsum(prefix)]).astype(np.int32)
+    q, k, v = H.randn_bf16(rng, N, HQ, D), H.randn_bf16(rng, N, HKV, D), H.randn_bf16(rng, N, HKV, D)
+    k_pre, v_pre = H.randn_bf16(rng, HKV, 208, D), H.randn_bf16(rng, HKV, 208, D)
+    tiles = list(range(0, N, 128)) + [-1]
+    tq, tk, tv = H.bf16_tensor(q), H.bf16_tensor(k), H.bf16_tensor(v)
+    tkp, tvp = H.bf16_tensor(k_pre), H.bf16_tensor(v_pre)
+    out = torch.full((N, HQ, D), 7.0, dtype=torch.bfloat16, device="cuda")
+    status = K.status_word(torch.device("cuda", 0))
+    rc = _lib.load().b200kv_prefill_attn_variant(
+        tq.data_ptr(), tq.stride(0), tq.stride(1), tk.data_ptr(), tk.stride(0), tk.stride(1), tv.data_ptr(), tv.stride(0),
+        tv.stride(1), H.i32(np.zeros(N)).data_ptr(), H.i32(cu).data_ptr(), H.i32(tiles).data_ptr(), len(tiles), 128,
+        tkp.data_ptr(), tvp.data_ptr(), tkp.stride(0), tkp.stride(1), 208, H.i32(cu_cached).data_ptr(), out.data_ptr(),
+        out.stride(0), out.stride(1), N, HQ, HKV, D, 3, status.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert K.check_status() == 4  # B200KV_S_TIMEOUT, and the word is cleared by the read
+    assert torch.all(out == 7.0)
+    # the same inputs through the working kernel
+    want = O.prefill_attention(q, k, v, cu, k_pre, v_pre, cu_cached, 0)
+    good = K.prefill_attention(tq, tk, tv, H.i32(np.zeros(N)), H.i32(cu), H.i32(tiles), tkp, tvp, H.i32(cu_cached), 128,
+                               variant=2)
+    assert K.check_status() == 0
+    mx, mean = H.attn_errors(H.to_f32(good), want)
+    assert mx <= 8e-3 and mean <= 4e-4, (mx, mean)
