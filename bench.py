@@ -395,6 +395,42 @@ def run_sharded(args):
         dist.all_gather(parts, stats)
     else:
         parts = [stats]
+    full = None
+    if args.model:
+        # the same shard through the whole random-init decoder (28 layers, GEMMs, sampler): the L resident layer
+        # caches are used in turn by the 28 layers (each is far larger than L2, so every layer still streams its
+        # KV bytes from HBM; only their contents repeat)
+        from inference_engine_b200 import scaffold as S
+
+        model = S.DecoderScaffold(dev, seed=4)
+        cyc = [caches[i % L] for i in range(S.LAYERS)]
+        ids = torch.randint(0, S.VOCAB, (B,), generator=gen, device=dev, dtype=torch.int32)
+        d_cached, d_table, d_nd = cached_h.to(dev), table_h.to(dev), nd_h.to(dev)
+        with torch.inference_mode():
+            for _ in range(2):
+                toks = model.forward(cyc, None, ids, d_cached, d_table, d_nd)
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                toks = model.forward(cyc, None, ids, d_cached, d_table, d_nd)
+        for _ in range(max(args.warmup, 3)):
+            g.replay()
+        barrier()
+        f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        f0.record()
+        for _ in range(args.steps):
+            g.replay()
+        f1.record()
+        barrier()
+        fms = torch.tensor([f0.elapsed_time(f1)], device=dev)
+        if world > 1:
+            dist.all_reduce(fms, op=dist.ReduceOp.MAX)
+        all_toks = gather_outputs(toks.float()[:, None], plan, rank)  # the sampled ids of all sequences, by NCCL
+        full = {"layers": S.LAYERS, "ms_per_step": round(float(fms.item()) / args.steps, 4),
+                "output_tokens_per_s": round(args.seqs * args.steps / (float(fms.item()) * 1e-3), 1),
+                "tokens_gathered": int(all_toks.shape[0]),
+                "tokens_in_vocabulary": bool(((all_toks >= 0) & (all_toks < S.VOCAB)).all().item())}
+        del model, g
     # verification gather, off the timed path: one output row per sequence, every sequence exactly once
     marker = torch.from_numpy(np.asarray(mine, dtype=np.int64)).to(dev).float()[:, None]
     got = gather_outputs(marker, plan, rank)
@@ -411,7 +447,8 @@ def run_sharded(args):
                                                         f"sharded by KV bytes over {world} GPU(s), {L} resident layer caches per step "
                                                         f"(attention path only: write + decode attention)",
                                             "plan_imbalance": round(plan.imbalance(), 4)},
-            "aggregate_gbs": round(sum(p["gbs"] for p in per), 1), "per_gpu": per, "all_sequences_served_once": ok}))
+            "aggregate_gbs": round(sum(p["gbs"] for p in per), 1), "per_gpu": per, "all_sequences_served_once": ok,
+            "full_decoder": full}))
     if world > 1:
         dist.destroy_process_group()
 
@@ -933,6 +970,7 @@ def main():
     ap.add_argument("--traffic", type=float, default=NCU_TRAFFIC_BYTES, help="ncu DRAM bytes per decode_attention call, if known")
     ap.add_argument("--no-early-start", action="store_true", help="launch decode attention without programmatic early start")
     ap.add_argument("--sharded", action="store_true", help="sequence-sharded decode over log-uniform contexts (torchrun for N > 1)")
+    ap.add_argument("--model", action="store_true", help="--sharded: also time the whole random-init decoder on each shard")
     ap.add_argument("--seqs", type=int, default=2048, help="--sharded: concurrent sequences over all GPUs")
     ap.add_argument("--serve", action="store_true", help="offline serving run of the step loop on the random-init decoder")
     ap.add_argument("--decode-model", action="store_true", help="pure decode step of the random-init decoder (B, ctx)")
