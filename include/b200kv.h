@@ -39,7 +39,7 @@
 extern "C" {
 #endif
 
-#define B200KV_VERSION 1
+#define B200KV_VERSION 2
 
 enum {
   B200KV_OK = 0,
@@ -56,7 +56,9 @@ enum {
 enum {
   B200KV_S_BAD_PAGE = 1,    /* block-table entry outside [0, num_pages) */
   B200KV_S_BAD_POSITION = 2, /* token position outside the entry's table (>= max_pages*page_size) */
-  B200KV_S_TIMEOUT = 4       /* a bounded wait inside a kernel ran out; that CTA's output rows are not written */
+  B200KV_S_TIMEOUT = 4,      /* a bounded wait inside a kernel ran out; that CTA's output rows are not written */
+  B200KV_S_BAD_PLAN = 8      /* b200kv_decode_attn_planned: the plan was not made for this batch (other lengths, head
+                                counts, page size or SM count); the warps that saw it wrote nothing */
 };
 
 /* One layer's cache, by value.  Mirrors LayerKVCache (kernels.py:11-17). */
@@ -171,7 +173,7 @@ int b200kv_prefill_attn_variant(const void* q, int64_t q_stride_n, int64_t q_str
                                 int32_t N, int32_t Hq, int32_t Hkv, int32_t D,
                                 int32_t variant, int32_t* status, void* stream);
 
-/* The two element-wise ops of the decoder block around the attention path (first of the "next" rows).
+/* The two element-wise ops of the decoder block either side of the attention path.
  * b200kv_silu_mul replaces silu_mul (kernels.py:1178-1212): out[n, d] = bf16((g * sigmoid(g)) * u) with
  * g = gate_up[n, d], u = gate_up[n, D + d], fp32 arithmetic.  bf16 [N, 2D] -> bf16 [N, D]; D a multiple
  * of 8, rows 16-byte aligned.
@@ -195,8 +197,9 @@ int b200kv_sample(const void* logits, int64_t stride, int32_t elem_bytes, int64_
                   void* workspace, size_t workspace_bytes, int64_t* out, int64_t out_stride,
                   int32_t B, int32_t V, void* stream);
 
-/* Chained launches (off by default).  While enabled, every kernel of this library is launched with
- * programmatic stream serialization: it may be brought up while the kernel launched just before it on
+/* Chained launches (off by default).  While enabled, every kernel of this library except decode attention
+ * (which is chained per call, through bit 2 of its `variant`) and b200kv_decode_plan (never chained) is launched
+ * with programmatic stream serialization: it may be brought up while the kernel launched just before it on
  * the same stream is still running, reads only caller-provided metadata (cu_seqlens, cu_cached,
  * cached_lens, num_decoding, block table, tile_start, seq_ids) until that kernel has completed, and
  * touches everything else afterwards.  Enable it only if no kernel that precedes a call of this
@@ -235,6 +238,36 @@ int b200kv_decode_attn(const void* q, int64_t q_stride_b, int64_t q_stride_h,
                        void* workspace, size_t workspace_bytes,
                        int32_t B, int32_t Hq, int32_t sm_count, int32_t variant,
                        int32_t* status, void* stream);
+
+/* Per-step plan of decode attention.  No counterpart in the reference, whose kernel re-derives its work split
+ * from cached_lens in every program of every layer (compute_piece / assign_work, kernels.py:20-70).
+ *
+ * The work split of b200kv_decode_attn depends only on cached_lens, *num_decoding and the block table, which a
+ * decoder step uploads once and then uses for all of its layers (engine.py:347-356, 451-470).
+ * b200kv_decode_plan computes the split once (one small kernel on `stream`) into `plan`
+ * (b200kv_decode_plan_bytes(sm_count) bytes of device memory, 16-byte aligned): for every warp of the persistent
+ * grid the position of its first tile and the page ids of its first tiles.  b200kv_decode_attn_planned is
+ * b200kv_decode_attn reading that plan: same arguments, same result bit for bit, but each CTA starts its copies
+ * after one round of loads instead of a length scan, a search and a dependent page-table read.
+ * Contract: between b200kv_decode_plan and the last planned call that uses the plan, cached_lens, *num_decoding
+ * and the table must not change, and B, Hkv, page_size and sm_count must be the ones the plan was made with.  A
+ * plan that does not fit (checked per warp against the header and the lengths) sets B200KV_S_BAD_PLAN in the
+ * status word and the warps that saw it write nothing; zero-fill the workspace again after that.
+ * `variant` as for b200kv_decode_attn, except bit 1 (the two-kernel reduction), which is refused.  With bit 2
+ * (early start) the plan counts as metadata: it is read before the wait, which is safe because the plan kernel
+ * never releases a chained successor before it has finished. */
+size_t b200kv_decode_plan_bytes(int32_t sm_count);
+int b200kv_decode_plan(const b200kv_table* table, const int32_t* cached_lens, const int32_t* num_decoding,
+                       int32_t B, int32_t num_kv_heads, int32_t page_size, int32_t sm_count,
+                       void* plan, size_t plan_bytes, void* stream);
+int b200kv_decode_attn_planned(const void* q, int64_t q_stride_b, int64_t q_stride_h,
+                               const b200kv_cache* cache, const b200kv_table* table,
+                               const int32_t* cached_lens, const int32_t* num_decoding, float scale,
+                               void* out, int64_t o_stride_b, int64_t o_stride_h,
+                               void* workspace, size_t workspace_bytes,
+                               const void* plan, size_t plan_bytes,
+                               int32_t B, int32_t Hq, int32_t sm_count, int32_t variant,
+                               int32_t* status, void* stream);
 
 /* b200kv_decode_attn for callers that must not allocate.  It has no counterpart in the reference
  * (whose wrapper allocates three partial buffers per call, kernels.py:305-311).

@@ -67,6 +67,12 @@ SIGNATURES = {
     "b200kv_decode_attn": (c_int32, [c_void_p, c_int64, c_int64, P_CACHE, P_TABLE, c_void_p, c_void_p, c_float, c_void_p,
                                      c_int64, c_int64, c_void_p, c_size_t, c_int32, c_int32, c_int32, c_int32, c_void_p,
                                      c_void_p]),
+    "b200kv_decode_plan_bytes": (c_size_t, [c_int32]),
+    "b200kv_decode_plan": (c_int32, [P_TABLE, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32, c_void_p, c_size_t,
+                                     c_void_p]),
+    "b200kv_decode_attn_planned": (c_int32, [c_void_p, c_int64, c_int64, P_CACHE, P_TABLE, c_void_p, c_void_p, c_float,
+                                             c_void_p, c_int64, c_int64, c_void_p, c_size_t, c_void_p, c_size_t, c_int32,
+                                             c_int32, c_int32, c_int32, c_void_p, c_void_p]),
     "b200kv_decode_attn_static_limit": (c_size_t, []),
     "b200kv_decode_attn_static": (c_int32, [c_void_p, c_int64, c_int64, P_CACHE, P_TABLE, c_void_p, c_void_p, c_float,
                                             c_void_p, c_int64, c_int64, c_int32, c_int32, c_int32, c_void_p, c_void_p]),
@@ -79,6 +85,18 @@ class B200KVError(RuntimeError):
     pass
 
 
+_path_override = None
+
+
+def use_library(path: str) -> None:
+    """Load this build of the library instead of the default one (the instrumented build of bench.py --phases).
+    Must be called before the first op."""
+    global _path_override
+    if _lib is not None:
+        raise B200KVError("a library is already loaded")
+    _path_override = path
+
+
 def load(build_if_needed: bool = True) -> C.CDLL:
     """Load (building first if sources are newer) the CUDA library.  Raises if impossible."""
     global _lib
@@ -87,6 +105,8 @@ def load(build_if_needed: bool = True) -> C.CDLL:
     path = _build.LIB
     if build_if_needed and _build.needs_build():
         path = _build.build()
+    if _path_override is not None:
+        path = _path_override
     if not os.path.exists(path):
         raise B200KVError(f"{path} is missing: the CUDA extension is required, there is no fallback path")
     lib = C.CDLL(path)

@@ -30,8 +30,10 @@ UNITS = {
     "prefill_attn_tc5.cu": [],
     "block_ops.cu": [],
     "sampler.cu": ["-fmad=false"],
-    "host_step.cu": [],
 }
+# The same library with per-warp timestamps compiled into the decode-attention kernel (bench.py --phases);
+# never loaded by the product path.
+STAMPS_LIB = os.path.join(PKG, "libb200kv_stamps.so")
 
 
 def _nvcc() -> str:
@@ -61,8 +63,6 @@ def build(force: bool = False, verbose: bool = False) -> str:
     objs = []
     for unit, extra in UNITS.items():
         src = os.path.join(CSRC, unit)
-        if not os.path.exists(src):
-            continue
         obj = os.path.join(OBJ_DIR, unit.replace(".cu", ".o"))
         cmd = [nvcc, *ARCH, *COMMON, *extra, "-c", src, "-o", obj]
         if verbose:
@@ -72,7 +72,19 @@ def build(force: bool = False, verbose: bool = False) -> str:
     tmp = LIB + ".tmp"
     subprocess.run([nvcc, *ARCH, "-shared", "-cudart", "static", "-o", tmp, *objs], check=True)
     os.replace(tmp, LIB)
+    build_stamps(nvcc, objs)
     return LIB
+
+
+def build_stamps(nvcc: str, objs: list[str]) -> str:
+    """libb200kv_stamps.so = the library with decode_attn.cu recompiled under -DB200KV_STAMPS."""
+    obj = os.path.join(OBJ_DIR, "decode_attn_stamps.o")
+    subprocess.run([nvcc, *ARCH, *COMMON, "-DB200KV_STAMPS", "-c", os.path.join(CSRC, "decode_attn.cu"), "-o", obj], check=True)
+    rest = [o for o in objs if os.path.basename(o) != "decode_attn.o"]
+    tmp = STAMPS_LIB + ".tmp"
+    subprocess.run([nvcc, *ARCH, "-shared", "-cudart", "static", "-o", tmp, *rest, obj], check=True)
+    os.replace(tmp, STAMPS_LIB)
+    return STAMPS_LIB
 
 
 if __name__ == "__main__":

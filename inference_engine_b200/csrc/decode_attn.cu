@@ -30,6 +30,7 @@
 //                    minus 1152); P' = p * v_scale.
 // Softmax state is fp32 in registers; scores use exp2 with log2(e) folded into the scale.
 // Variant 1 does the same with fp32 FMAs on the CUDA cores and exists for cross-checking.
+#include <algorithm>
 #include <type_traits>
 
 #include "common.cuh"
@@ -259,20 +260,26 @@ __device__ __forceinline__ LaneCopy make_lane_copy(const CacheView& c, int lane)
   return lc;
 }
 
-__device__ __forceinline__ void issue_tile(const CacheView& c, const Cursor& cur, PageWindow& win, const LaneCopy& lc,
+// Page id of the cursor's tile from the lane-distributed window of the entry's table row (reloaded when the
+// cursor leaves it); -2 when the tile lies beyond the table.
+__device__ __forceinline__ void load_window(const CacheView& c, int b, int slot, PageWindow& win, int lane) {
+  win.b = b;
+  win.base = slot & ~31;
+  const int idx = win.base + lane;
+  win.reg = (idx < c.max_pages) ? c.table[(long long)b * c.table_stride + idx] : -2;
+}
+__device__ __forceinline__ int window_page(const CacheView& c, const Cursor& cur, PageWindow& win, int lane) {
+  const int slot = cur.slot;
+  if (cur.b != win.b || slot < win.base || slot >= win.base + 32) load_window(c, cur.b, slot, win, lane);
+  return __shfl_sync(0xffffffffu, win.reg, slot - win.base);
+}
+
+__device__ __forceinline__ void issue_tile(const CacheView& c, const Cursor& cur, int page, const LaneCopy& lc,
                                            uint32_t sbase, int lane, int32_t* status) {
   const int nvalid = cur.n - cur.tile * kTile;  // >= 1; >= 16 for every tile but a sequence's last
-  const int slot = cur.slot;
-  if (cur.b != win.b || slot < win.base || slot >= win.base + 32) {
-    win.b = cur.b;
-    win.base = slot & ~31;
-    const int idx = win.base + lane;
-    win.reg = (idx < c.max_pages) ? c.table[(long long)cur.b * c.table_stride + idx] : -1;
-  }
-  int page = __shfl_sync(0xffffffffu, win.reg, slot - win.base);
-  const bool ok = slot < c.max_pages && page >= 0 && page < c.num_pages;
+  const bool ok = page >= 0 && page < c.num_pages;
   if (!ok) {
-    if (lane == 0 && status) atomicOr(status, slot < c.max_pages ? B200KV_S_BAD_PAGE : B200KV_S_BAD_POSITION);
+    if (lane == 0 && status) atomicOr(status, page == -2 ? B200KV_S_BAD_POSITION : B200KV_S_BAD_PAGE);
     page = 0;
   }
   const long long code_off = page * c.stride_page + cur.h * c.stride_head + cur.row0 * c.stride_tok + lc.g_off;
@@ -686,16 +693,90 @@ __device__ __forceinline__ void merge_partials(const float* __restrict__ ws_ml, 
 
 __host__ __device__ inline size_t ws_ml_bytes(int W, int G) { return (((size_t)W * 2 * G * 2 * 4 + 255) / 256) * 256; }
 
+// ------------------------------------------------------------------ per-step plan
+// The partition depends only on the step's metadata (cached_lens, num_decoding, the block table), which is
+// the same for every layer of a decoder step.  decode_plan_kernel computes it once: a header and, for every
+// warp of the persistent grid, the cursor of its first tile and the page ids of its first kStages-1 tiles.
+// A planned decode_attn_kernel then needs one round of loads (its plan entry, the lengths, num_decoding)
+// before its first copies are in flight, instead of the length scan, a binary search and a dependent
+// page-table read in each of its CTAs in each layer.
+constexpr int kPlanMagic = 0x6b765031;  // "kvP1"
+constexpr int kPlanHeaderInts = 8;      // magic, B, Hkv, W, U, per, num_decoding, page_size
+constexpr int kPlanEntryInts = 16;      // b, h, tile, T, n, base, page[0..2], reserved
+constexpr int kPlanThreads = 1024;
+__host__ __device__ inline size_t plan_bytes(int W) { return ((size_t)kPlanHeaderInts + (size_t)W * kPlanEntryInts) * 4; }
+
+__global__ void __launch_bounds__(kPlanThreads)
+decode_plan_kernel(const int32_t* __restrict__ cached_lens, const int32_t* __restrict__ num_decoding,
+                   const int32_t* __restrict__ table, int table_stride, int max_pages, int page_size, int B, int Hkv,
+                   int W, int* __restrict__ plan) {
+  __shared__ int chunk_prefix[kPlanThreads + 1];
+  __shared__ int lens_s[kSmemLens];
+  // No early trigger here: a kernel chained behind this one is only brought up when every thread of this
+  // grid has exited, i.e. after the fence below, so it may read the plan before its own wait.
+  pdl_wait();
+  const int chunk = (B + kPlanThreads - 1) / kPlanThreads;
+  int nd;
+  scan_tiles(cached_lens, B, num_decoding, chunk, chunk_prefix, lens_s, nullptr, nd);
+  const Lens lens{cached_lens, lens_s, nd};
+  const Partition part = make_partition(chunk_prefix[kPlanThreads], Hkv, W, nd);
+  if (threadIdx.x == 0) {
+    plan[0] = kPlanMagic; plan[1] = B; plan[2] = Hkv; plan[3] = W;
+    plan[4] = part.U; plan[5] = part.per; plan[6] = nd; plan[7] = page_size;
+  }
+  for (int w = threadIdx.x; w < W; w += kPlanThreads) {
+    int* e = plan + kPlanHeaderInts + (size_t)w * kPlanEntryInts;
+    const long long u_begin = (long long)w * part.per;
+    if (u_begin >= part.U) {
+      e[0] = -1;
+      continue;
+    }
+    Cursor cur;
+    cur.seek(chunk_prefix, kPlanThreads, chunk, lens, Hkv, page_size, (int)u_begin);
+    e[0] = cur.b; e[1] = cur.h; e[2] = cur.tile; e[3] = cur.T; e[4] = cur.n; e[5] = cur.base;
+    int left = min(part.per, part.U - (int)u_begin);
+    for (int i = 0; i < kStages - 1; ++i) {
+      int page = -1;
+      if (left > 0) {
+        page = cur.slot < max_pages ? table[(long long)cur.b * table_stride + cur.slot] : -2;
+        if (--left > 0) cur.next(lens, Hkv, page_size);
+      }
+      e[6 + i] = page;
+    }
+  }
+  __threadfence();
+}
+
+#ifdef B200KV_STAMPS
+// Instrumented build only: per warp of the persistent grid {kernel entry, smid, first copy issued, first tile
+// landed, last tile consumed, exit, tiles, pieces merged} with %globaltimer nanoseconds.
+constexpr int kStampWarps = 4096;
+__device__ unsigned long long g_stamps[kStampWarps * 8];
+__device__ __forceinline__ unsigned long long gtime() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+#define STAMP(i, v) do { if (lane == 0 && w < kStampWarps) g_stamps[8 * w + (i)] = (v); } while (0)
+#else
+#define STAMP(i, v) do { } while (0)
+#endif
+
 template <bool kScalar>
 __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm)
 decode_attn_kernel(const uint16_t* __restrict__ q, long long q_sb, long long q_sh, CacheView c,
                    const int32_t* __restrict__ cached_lens, const int32_t* __restrict__ num_decoding, float scale_log2,
                    uint16_t* __restrict__ out, long long o_sb, long long o_sh, uint8_t* __restrict__ workspace, int B,
-                   int G, int fused, int early, int32_t* status) {
+                   int G, int W, int fused, int early, const int* __restrict__ plan, int32_t* status) {
   extern __shared__ __align__(128) uint8_t smem[];
   uint8_t* ring = smem;                                                       // kWarps * kStages * kTileBytes
   float* q_s = reinterpret_cast<float*>(ring + kWarps * kStages * kTileBytes);  // scalar variant: kWarps * (G*128 + G*16)
   int* chunk_prefix = reinterpret_cast<int*>(q_s + (kScalar ? kWarps * (kMaxG * kD + kMaxG * kTile) : 0));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int w = blockIdx.x * kWarps + warp;
+#ifdef B200KV_STAMPS
+  const unsigned long long t_entry = gtime();
+#endif
 
   // The first CTA waits for the predecessor at once, so that this grid can never complete before it.  The
   // trigger for the successor comes late, when a warp has issued its last tile: the CTAs of a successor that is
@@ -704,20 +785,68 @@ decode_attn_kernel(const uint16_t* __restrict__ q, long long q_sb, long long q_s
   if (blockIdx.x == 0) pdl_wait();
   int* lens_s = chunk_prefix + kWarps * 32 + 1;
   int* cta_arrive = lens_s + kSmemLens;  // how many of this CTA's warps have parked a piece in shared memory
-  if (threadIdx.x == 0) *cta_arrive = 0;  // ordered before any use by the barriers inside scan_tiles
-  const int nchunks = blockDim.x, chunk = (B + nchunks - 1) / nchunks;
+  if (threadIdx.x == 0) *cta_arrive = 0;  // ordered before any use by the barriers below
   int nd;
-  scan_tiles(cached_lens, B, num_decoding, chunk, chunk_prefix, lens_s,
-             (blockIdx.x == 0 && !fused) ? reinterpret_cast<int*>(workspace) : nullptr, nd);
+  Partition part;
+  Cursor pc;  // producer position (runs kStages-1 tiles ahead of the consumer)
+  int first_page = -1;  // planned: lane i < kStages-1 holds the page id of the warp's i-th tile
+  if (plan != nullptr) {
+    // One round of independent loads: the warp's plan entry (lanes 0-15), the header (lanes 16-23),
+    // num_decoding and this thread's share of the lengths.
+    int pe = 0;
+    if (lane < kPlanEntryInts) pe = __ldcg(plan + kPlanHeaderInts + (size_t)w * kPlanEntryInts + lane);
+    else if (lane < kPlanEntryInts + kPlanHeaderInts) pe = __ldcg(plan + (lane - kPlanEntryInts));
+    const int nd_raw = __ldcg(num_decoding);
+    int cl[kSmemLens / (kWarps * 32)];
+#pragma unroll
+    for (int i = 0; i < kSmemLens / (kWarps * 32); ++i) {
+      const int b = threadIdx.x + i * kWarps * 32;
+      cl[i] = b < B ? __ldcg(cached_lens + b) : 0;
+    }
+    nd = min(nd_raw, B);
+#pragma unroll
+    for (int i = 0; i < kSmemLens / (kWarps * 32); ++i) {
+      const int b = threadIdx.x + i * kWarps * 32;
+      if (b < B) lens_s[b] = b < nd ? cl[i] + 1 : 0;
+    }
+    __syncthreads();
+    const bool hdr_ok = __shfl_sync(0xffffffffu, pe, 16) == kPlanMagic && __shfl_sync(0xffffffffu, pe, 17) == B &&
+                        __shfl_sync(0xffffffffu, pe, 18) == c.Hkv && __shfl_sync(0xffffffffu, pe, 19) == W &&
+                        __shfl_sync(0xffffffffu, pe, 22) == nd && __shfl_sync(0xffffffffu, pe, 23) == c.page_size;
+    part.U = __shfl_sync(0xffffffffu, pe, 20);
+    part.per = __shfl_sync(0xffffffffu, pe, 21);
+    part.W = W;
+    pc.b = __shfl_sync(0xffffffffu, pe, 0);
+    pc.h = __shfl_sync(0xffffffffu, pe, 1);
+    pc.tile = __shfl_sync(0xffffffffu, pe, 2);
+    pc.T = __shfl_sync(0xffffffffu, pe, 3);
+    pc.n = __shfl_sync(0xffffffffu, pe, 4);
+    pc.base = __shfl_sync(0xffffffffu, pe, 5);
+    first_page = __shfl_sync(0xffffffffu, pe, 6 + (lane < kStages - 1 ? lane : 0));
+    if (!hdr_ok) {  // not a plan of this batch on this grid: nothing is read or written through it
+      if (lane == 0 && status) atomicOr(status, B200KV_S_BAD_PLAN);
+      return;
+    }
+    if (pc.b < 0) return;  // no work for this warp
+    const Lens probe{cached_lens, lens_s, nd};
+    if (pc.b >= B || pc.h < 0 || pc.h >= c.Hkv || pc.n != probe.n(pc.b) || pc.T != probe.tiles(pc.b) || pc.tile < 0 ||
+        pc.tile >= pc.T || (long long)w * part.per >= part.U) {  // the plan was made from other lengths
+      if (lane == 0 && status) atomicOr(status, B200KV_S_BAD_PLAN);
+      return;
+    }
+    pc.slot = (pc.tile * kTile) / c.page_size;
+    pc.row0 = pc.tile * kTile - pc.slot * c.page_size;
+  } else {
+    const int nchunks = blockDim.x, chunk = (B + nchunks - 1) / nchunks;
+    scan_tiles(cached_lens, B, num_decoding, chunk, chunk_prefix, lens_s,
+               (blockIdx.x == 0 && !fused) ? reinterpret_cast<int*>(workspace) : nullptr, nd);
+    part = make_partition(chunk_prefix[nchunks], c.Hkv, W, nd);
+    if ((long long)w * part.per >= part.U) return;
+    const Lens probe{cached_lens, lens_s, nd};
+    pc.seek(chunk_prefix, nchunks, chunk, probe, c.Hkv, c.page_size, w * part.per);
+  }
   const Lens lens{cached_lens, lens_s, nd};
-  const int W = gridDim.x * kWarps;
-  const Partition part = make_partition(chunk_prefix[nchunks], c.Hkv, W, nd);
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int w = blockIdx.x * kWarps + warp;
-  const long long u_begin = (long long)w * part.per;
-  if (u_begin >= part.U) return;
-  const int u0 = (int)u_begin;
+  const int u0 = w * part.per;
   const int ntiles = min(part.per, part.U - u0);
 
   int* ws_count = reinterpret_cast<int*>(workspace + ws_prefix_bytes(B));
@@ -727,8 +856,6 @@ decode_attn_kernel(const uint16_t* __restrict__ q, long long q_sb, long long q_s
   const uint32_t my_ring_s = smem_u32(my_ring);
   float* my_q = q_s + warp * (kMaxG * kD + kMaxG * kTile);
 
-  Cursor pc;  // producer position (runs kStages-1 tiles ahead of the consumer)
-  pc.seek(chunk_prefix, nchunks, chunk, lens, c.Hkv, c.page_size, u0);
   Cursor cc = pc;  // consumer position, advanced segment by segment
   PageWindow win{-1, 0, -1};
   const LaneCopy lc = make_lane_copy(c, lane);
@@ -746,11 +873,15 @@ decode_attn_kernel(const uint16_t* __restrict__ q, long long q_sb, long long q_s
         asm volatile("griddepcontrol.wait;" ::: "memory");
         must_wait = false;
       }
-      issue_tile(c, pc, win, lc, my_ring_s + i * kTileBytes, lane, status);
+      const int page = plan != nullptr ? __shfl_sync(0xffffffffu, first_page, i) : window_page(c, pc, win, lane);
+      issue_tile(c, pc, page, lc, my_ring_s + i * kTileBytes, lane, status);
       if (--p_left > 0) pc.next(lens, c.Hkv, c.page_size);
     }
     cp_async_commit();
   }
+  STAMP(2, gtime());
+  // planned: the table row of the next tile is requested now and is there when the main loop wants it
+  if (plan != nullptr && p_left > 0) load_window(c, pc.b, pc.slot, win, lane);
   if (must_wait) asm volatile("griddepcontrol.wait;" ::: "memory");
 
   typename std::conditional<kScalar, ScalarState, MmaState>::type st;
@@ -765,13 +896,16 @@ decode_attn_kernel(const uint16_t* __restrict__ q, long long q_sb, long long q_s
     int remaining = cc.n - cc.tile * kTile;  // tokens from this tile to the end of the sequence
     for (int k = 0; k < seg; ++k) {
       if (p_left > 0) {
-        issue_tile(c, pc, win, lc, my_ring_s + stage_p * kTileBytes, lane, status);
+        issue_tile(c, pc, window_page(c, pc, win, lane), lc, my_ring_s + stage_p * kTileBytes, lane, status);
         if (--p_left > 0) pc.next(lens, c.Hkv, c.page_size);
         else pdl_trigger();  // this warp has nothing left to fetch
       }
       cp_async_commit();
       cp_async_wait<kStages - 1>();
       __syncwarp();
+#ifdef B200KV_STAMPS
+      if (done == 0 && k == 0) STAMP(3, gtime());
+#endif
       const uint8_t* stage = my_ring + stage_c * kTileBytes;
       if constexpr (kScalar) scalar_tile(st, my_q, my_q + kMaxG * kD, stage, min(remaining, kTile), G, lane);
       else mma_tile(st, stage, remaining, lane);
@@ -780,6 +914,9 @@ decode_attn_kernel(const uint16_t* __restrict__ q, long long q_sb, long long q_s
       stage_c = (stage_c + 1) & (kStages - 1);
       stage_p = (stage_p + 1) & (kStages - 1);
     }
+#ifdef B200KV_STAMPS
+    if (done + seg >= ntiles) STAMP(4, gtime());
+#endif
     // whole iff the segment began at the sequence's first tile and reached its last one
     const bool whole = cc.tile == 0 && seg == cc.T;
     const int slot = done == 0 ? 0 : 1;
@@ -856,12 +993,22 @@ decode_attn_kernel(const uint16_t* __restrict__ q, long long q_sb, long long q_s
         __threadfence();
         merge_partials(ws_ml, ws_o, pieces, G, out_row, o_sh, lane);
         if (lane == 0) ws_count[cc.b * c.Hkv + cc.h] = 0;  // leave the counter zero for the next call
+#ifdef B200KV_STAMPS
+        STAMP(7, (unsigned long long)pieces.n);
+#endif
       }
     }
     done += seg;
     if (done < ntiles) cc.next_segment(lens, c.Hkv);
   }
   cp_async_wait<0>();
+#ifdef B200KV_STAMPS
+  {
+    unsigned sm;
+    asm volatile("mov.u32 %0, %%smid;" : "=r"(sm));
+    STAMP(0, t_entry); STAMP(1, (unsigned long long)sm); STAMP(5, gtime()); STAMP(6, (unsigned long long)ntiles);
+  }
+#endif
 }
 
 // ------------------------------------------------------------------ cross-split reduction
@@ -959,13 +1106,11 @@ extern "C" size_t b200kv_decode_attn_workspace_bytes(int32_t B, int32_t Hq, int3
   return ws_head_bytes(B, Hkv) + ws_ml_bytes(W, G) + (size_t)W * 2 * G * kD * 4;
 }
 
-extern "C" int b200kv_decode_attn(const void* q, int64_t q_sb, int64_t q_sh, const b200kv_cache* cache,
-                                  const b200kv_table* table, const int32_t* cached_lens, const int32_t* num_decoding,
-                                  float scale, void* out, int64_t o_sb, int64_t o_sh, void* workspace,
-                                  size_t workspace_bytes, int32_t B, int32_t Hq, int32_t sm_count, int32_t variant,
-                                  int32_t* status, void* stream) {
-  // an empty batch is valid and has nothing to launch (its tensors have no storage, so their pointers are NULL)
-  if (B == 0) return B200KV_OK;
+// Argument checks shared by the three decode-attention entry points; nothing is enqueued before they pass.
+static int check_decode_args(const void* q, int64_t q_sb, int64_t q_sh, const b200kv_cache* cache,
+                             const b200kv_table* table, const int32_t* cached_lens, const int32_t* num_decoding,
+                             const void* out, int64_t o_sb, int64_t o_sh, const void* workspace, size_t workspace_bytes,
+                             int32_t B, int32_t Hq, int32_t sm_count, int32_t variant) {
   if (!q || !cached_lens || !num_decoding || !out || !workspace) return B200KV_E_NULL;
   int rc = check_cache(cache, table);
   if (rc) return rc;
@@ -975,23 +1120,34 @@ extern "C" int b200kv_decode_attn(const void* q, int64_t q_sb, int64_t q_sh, con
   if (!aligned(q, 16) || !aligned(out, 16) || !aligned(workspace, 256) || (q_sb % 8) || (q_sh % 8) || (o_sb % 8) || (o_sh % 8))
     return B200KV_E_ALIGN;
   if (workspace_bytes < b200kv_decode_attn_workspace_bytes(B, Hq, Hkv, kD, sm_count)) return B200KV_E_WORKSPACE;
-  if (B == 0) return B200KV_OK;
+  return B200KV_OK;
+}
+
+// Launch (arguments already checked).  `clear_bytes` > 0: that many bytes at the head of the workspace are
+// zeroed on the stream first (the built-in scratch keeps the previous call's contents).
+static int launch_decode(const void* q, int64_t q_sb, int64_t q_sh, const b200kv_cache* cache, const b200kv_table* table,
+                         const int32_t* cached_lens, const int32_t* num_decoding, float scale, void* out, int64_t o_sb,
+                         int64_t o_sh, void* workspace, size_t clear_bytes, int32_t B, int32_t Hq, int32_t sm_count,
+                         int32_t variant, const void* plan, int32_t* status, void* stream) {
+  const int Hkv = cache->num_kv_heads;
   const int G = Hq / Hkv;
-  const int grid = sm_count * kCtasPerSm;
-  const int W = grid * kWarps;
+  const int W = sm_count * kCtasPerSm * kWarps;
+  // Only CTAs that can have work are launched: a warp never takes fewer than 4 tiles, and no entry has
+  // more tiles than its table row can address.
+  const long long max_tiles = (long long)B * Hkv * (((long long)table->max_pages * cache->page_size + kTile - 1) / kTile);
+  const long long want = (max_tiles + 4 * kWarps - 1) / (4 * kWarps);
+  const int grid = (int)std::max<long long>(1, std::min<long long>(sm_count * kCtasPerSm, want));
   const float scale_log2 = scale * 1.4426950408889634f;
   cudaStream_t s = (cudaStream_t)stream;
   const bool scalar = (variant & 1) != 0;
   const int fused = (variant & 2) ? 0 : 1;
   const int early = ((variant & 4) && fused) ? 1 : 0;  // the separate reduction kernel's prefix array is written before the wait
   const size_t smem = main_smem_bytes(B, scalar);
-  static bool attr_set[2] = {false, false};  // the opt-in to > 48 KB of dynamic shared memory is per function
-  if (!attr_set[variant & 1]) {
-    cudaError_t e = scalar ? cudaFuncSetAttribute(decode_attn_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
-                           : cudaFuncSetAttribute(decode_attn_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return B200KV_E_LAUNCH;
-    attr_set[variant & 1] = true;
-  }
+  // the opt-in to more than 48 KB of dynamic shared memory is per function AND per device: set on every call
+  cudaError_t e = scalar ? cudaFuncSetAttribute(decode_attn_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
+                         : cudaFuncSetAttribute(decode_attn_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return B200KV_E_LAUNCH;
+  if (clear_bytes && cudaMemsetAsync(workspace, 0, clear_bytes, s) != cudaSuccess) return B200KV_E_LAUNCH;
   CacheView view = make_view(cache, table);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);
@@ -1006,7 +1162,7 @@ extern "C" int b200kv_decode_attn(const void* q, int64_t q_sb, int64_t q_sh, con
   cudaError_t le = cudaLaunchKernelEx(&cfg, scalar ? decode_attn_kernel<true> : decode_attn_kernel<false>,
                                       (const uint16_t*)q, (long long)q_sb, (long long)q_sh, view, cached_lens, num_decoding,
                                       scale_log2, (uint16_t*)out, (long long)o_sb, (long long)o_sh, (uint8_t*)workspace,
-                                      (int)B, G, fused, early, status);
+                                      (int)B, G, W, fused, early, (const int*)plan, status);
   if (le != cudaSuccess) return B200KV_E_LAUNCH;
   if (cudaGetLastError() != cudaSuccess) return B200KV_E_LAUNCH;
   if (fused) return B200KV_OK;
@@ -1014,6 +1170,69 @@ extern "C" int b200kv_decode_attn(const void* q, int64_t q_sb, int64_t q_sh, con
                                                     Hkv, G, W);
   return cudaGetLastError() == cudaSuccess ? B200KV_OK : B200KV_E_LAUNCH;
 }
+
+extern "C" int b200kv_decode_attn(const void* q, int64_t q_sb, int64_t q_sh, const b200kv_cache* cache,
+                                  const b200kv_table* table, const int32_t* cached_lens, const int32_t* num_decoding,
+                                  float scale, void* out, int64_t o_sb, int64_t o_sh, void* workspace,
+                                  size_t workspace_bytes, int32_t B, int32_t Hq, int32_t sm_count, int32_t variant,
+                                  int32_t* status, void* stream) {
+  // an empty batch is valid and has nothing to launch (its tensors have no storage, so their pointers are NULL)
+  if (B == 0) return B200KV_OK;
+  const int rc = check_decode_args(q, q_sb, q_sh, cache, table, cached_lens, num_decoding, out, o_sb, o_sh, workspace,
+                                   workspace_bytes, B, Hq, sm_count, variant);
+  if (rc) return rc;
+  return launch_decode(q, q_sb, q_sh, cache, table, cached_lens, num_decoding, scale, out, o_sb, o_sh, workspace, 0, B, Hq,
+                       sm_count, variant, nullptr, status, stream);
+}
+
+extern "C" size_t b200kv_decode_plan_bytes(int32_t sm_count) {
+  return sm_count < 1 ? 0 : plan_bytes(sm_count * kCtasPerSm * kWarps);
+}
+
+extern "C" int b200kv_decode_plan(const b200kv_table* table, const int32_t* cached_lens, const int32_t* num_decoding,
+                                  int32_t B, int32_t Hkv, int32_t page_size, int32_t sm_count, void* plan,
+                                  size_t plan_bytes_given, void* stream) {
+  if (!table || !table->ids || !cached_lens || !num_decoding || !plan) return B200KV_E_NULL;
+  if (B < 0 || Hkv < 1 || page_size < 1 || sm_count < 1 || table->max_pages < 1 || table->stride < 0) return B200KV_E_SHAPE;
+  if (table->max_pages > 1 && (page_size % kTile) != 0) return B200KV_E_SHAPE;
+  if (B > kMaxB) return B200KV_E_RANGE;
+  if (!aligned(plan, 16)) return B200KV_E_ALIGN;
+  if (plan_bytes_given < b200kv_decode_plan_bytes(sm_count)) return B200KV_E_WORKSPACE;
+  const int W = sm_count * kCtasPerSm * kWarps;
+  decode_plan_kernel<<<1, kPlanThreads, 0, (cudaStream_t)stream>>>(cached_lens, num_decoding, table->ids, table->stride,
+                                                                   table->max_pages, page_size, B, Hkv, W, (int*)plan);
+  return cudaGetLastError() == cudaSuccess ? B200KV_OK : B200KV_E_LAUNCH;
+}
+
+extern "C" int b200kv_decode_attn_planned(const void* q, int64_t q_sb, int64_t q_sh, const b200kv_cache* cache,
+                                          const b200kv_table* table, const int32_t* cached_lens,
+                                          const int32_t* num_decoding, float scale, void* out, int64_t o_sb, int64_t o_sh,
+                                          void* workspace, size_t workspace_bytes, const void* plan, size_t plan_bytes_given,
+                                          int32_t B, int32_t Hq, int32_t sm_count, int32_t variant, int32_t* status,
+                                          void* stream) {
+  if (B == 0) return B200KV_OK;
+  if (!plan) return B200KV_E_NULL;
+  const int rc = check_decode_args(q, q_sb, q_sh, cache, table, cached_lens, num_decoding, out, o_sb, o_sh, workspace,
+                                   workspace_bytes, B, Hq, sm_count, variant);
+  if (rc) return rc;
+  if (variant & 2) return B200KV_E_SHAPE;  // the two-kernel reduction reads a prefix array only the unplanned kernel writes
+  if (!aligned(plan, 16)) return B200KV_E_ALIGN;
+  if (plan_bytes_given < b200kv_decode_plan_bytes(sm_count)) return B200KV_E_WORKSPACE;
+  return launch_decode(q, q_sb, q_sh, cache, table, cached_lens, num_decoding, scale, out, o_sb, o_sh, workspace, 0, B, Hq,
+                       sm_count, variant, plan, status, stream);
+}
+
+#ifdef B200KV_STAMPS
+extern "C" int b200kv_stamps_read(unsigned long long* host, int clear) {
+  cudaError_t e = cudaMemcpyFromSymbol(host, b200kv::g_stamps, sizeof(unsigned long long) * kStampWarps * 8);
+  if (e == cudaSuccess && clear) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, b200kv::g_stamps);
+    if (e == cudaSuccess) e = cudaMemset(p, 0, sizeof(unsigned long long) * kStampWarps * 8);
+  }
+  return e == cudaSuccess ? kStampWarps : -1;
+}
+#endif
 
 // ------------------------------------------------------------------ entry point that allocates nothing
 // Some hosts of this library may not create device memory at all when they reach the attention
@@ -1052,10 +1271,12 @@ extern "C" int b200kv_decode_attn_static(const void* q, int64_t q_sb, int64_t q_
     g_static_scratch_ptr[dev] = static_cast<unsigned char*>(p);
   }
   unsigned char* scratch = g_static_scratch_ptr[dev];
+  if (B == 0) return B200KV_OK;
+  const int rc = check_decode_args(q, q_sb, q_sh, cache, table, cached_lens, num_decoding, out, o_sb, o_sh, scratch,
+                                   kStaticScratchBytes, B, Hq, sm_count, 0);
+  if (rc) return rc;  // nothing has been enqueued
   // The array keeps whatever the previous call (possibly of another batch size) left behind; the
-  // prefix + arrival-counter head of THIS call's layout must start at zero.
-  if (B > 0 && cudaMemsetAsync(scratch, 0, ws_head_bytes(B, cache->num_kv_heads), (cudaStream_t)stream) != cudaSuccess)
-    return B200KV_E_LAUNCH;
-  return b200kv_decode_attn(q, q_sb, q_sh, cache, table, cached_lens, num_decoding, scale, out, o_sb, o_sh, scratch,
-                            kStaticScratchBytes, B, Hq, sm_count, 0, status, stream);
+  // prefix + arrival-counter head of THIS call's layout is cleared on the stream ahead of the kernel.
+  return launch_decode(q, q_sb, q_sh, cache, table, cached_lens, num_decoding, scale, out, o_sb, o_sh, scratch,
+                       ws_head_bytes(B, cache->num_kv_heads), B, Hq, sm_count, 0, nullptr, status, stream);
 }

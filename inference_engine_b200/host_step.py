@@ -48,6 +48,8 @@ class HostDecodeStep:
         self.dev_out = torch.empty(L, B, Hq, D, dtype=torch.bfloat16, device=dev)
         self.q_w = [torch.ones(D, dtype=torch.bfloat16, device=dev) for _ in range(L)]
         self.k_w = [torch.ones(D, dtype=torch.bfloat16, device=dev) for _ in range(L)]
+        self.plan = torch.empty(K.plan_decode_bytes(dev), dtype=torch.uint8, device=dev)  # this step's work split
+        self.use_plan = True
         self.graph = None
         self.group_graphs: list[tuple[int, int, torch.cuda.CUDAGraph]] = []  # (first layer, end layer, graph)
         self.h2d_stream = torch.cuda.Stream(device=dev)
@@ -69,6 +71,9 @@ class HostDecodeStep:
         """The device part: per layer in [first, end), quantize-on-write of the new tokens then attention."""
         Hq, Hkv, D = self.Hq, self.Hkv, self.D
         end = len(self.caches) if end is None else end
+        if first == 0 and self.use_plan:
+            # once per step: the split depends on the step's metadata only, every layer reuses it
+            K.plan_decode_step(self.dev_cached, self.dev_table, self.dev_nd, self.caches[0], out=self.plan)
         for l in range(first, end):
             cache = self.caches[l]
             q, k, v = self.dev_qkv[l].split([Hq * D, Hkv * D, Hkv * D], dim=-1)
@@ -77,7 +82,8 @@ class HostDecodeStep:
             v = v.view(self.B, Hkv, D)
             qr = K.fused_rope_kv_decode(q, k, v, self.q_w[l], self.k_w[l], self.dev_cos, self.dev_sin, self.dev_table,
                                         cache, self.dev_cached, self.dev_nd, self.eps)
-            K.decode_attention(qr, cache, self.dev_cached, self.dev_table, self.dev_nd, D ** -0.5, out=self.dev_out[l])
+            K.decode_attention(qr, cache, self.dev_cached, self.dev_table, self.dev_nd, D ** -0.5, out=self.dev_out[l],
+                               plan=self.plan if self.use_plan else None)
 
     def capture(self, groups: int = 7):
         """Record device_step into a CUDA graph (two eager warm-up runs first, like engine.py:432-449), and

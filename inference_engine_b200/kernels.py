@@ -114,6 +114,32 @@ def decode_workspace(device: torch.device, B: int, Hq: int, Hkv: int, nbytes: in
     return ws
 
 
+_nvtx = False
+
+
+def set_nvtx(enabled: bool) -> None:
+    """Bracket every op of this module in an NVTX range named after it, as the reference's callers do around
+    theirs (architecture.py:84,100,115,200).  Off by default: a range costs two host calls per op."""
+    global _nvtx
+    _nvtx = bool(enabled)
+
+
+def _ranged(fn):
+    """The op inside an NVTX range of its own name while set_nvtx(True) is in force."""
+
+    @functools.wraps(fn)
+    def wrapper(*args, **kwargs):
+        if not _nvtx:
+            return fn(*args, **kwargs)
+        torch.cuda.nvtx.range_push(fn.__name__)
+        try:
+            return fn(*args, **kwargs)
+        finally:
+            torch.cuda.nvtx.range_pop()
+
+    return wrapper
+
+
 def _require_cuda(*tensors: torch.Tensor) -> None:
     for t in tensors:
         if not t.is_cuda:
@@ -157,6 +183,41 @@ def _row_stride(t: torch.Tensor) -> int:
 
 
 # ----------------------------------------------------------------------------- ops
+@_ranged
+def plan_decode_step(
+    cached_lens: torch.Tensor,  # [B]
+    slot_ids: torch.Tensor,  # [B] or [B, max_pages]
+    num_decoding: torch.Tensor,  # int32 [1]
+    kv_cache: LayerKVCache,  # any layer's cache of the step: only its head count and page size are used
+    out: torch.Tensor | None = None,
+) -> torch.Tensor:
+    """The work split of decode_attention for one decoder step, computed once (one small kernel) and
+    handed to every layer's call as `decode_attention(..., plan=plan)`.  It is a function of
+    cached_lens, num_decoding and the block table only, which the engine uploads once per step
+    (engine.py:347-356, 461-465) and no layer changes.  Not part of the reference's interface:
+    without a plan decode_attention derives the same split inside every launch.  The plan must be
+    remade whenever those three arrays change; under a CUDA graph, capture this call at the head of
+    the step.  `out`: a uint8 buffer of plan_decode_bytes(device) to reuse."""
+    _require_cuda(cached_lens, slot_ids, num_decoding, kv_cache.k)
+    lib = _lib.load()
+    dev = cached_lens.device
+    sms = num_sms(dev)
+    nbytes = lib.b200kv_decode_plan_bytes(sms)
+    if out is None:
+        out = torch.empty(nbytes, device=dev, dtype=torch.uint8)
+    assert out.dtype == torch.uint8 and out.numel() >= nbytes and out.is_contiguous()
+    ts = _table_struct(slot_ids)
+    rc = lib.b200kv_decode_plan(ctypes.byref(ts), _i32(cached_lens), _i32(num_decoding), cached_lens.shape[0],
+                                kv_cache.k.shape[1], kv_cache.k.shape[2], sms, out.data_ptr(), out.numel(), _stream())
+    _lib.check(rc, "plan_decode_step")
+    return out
+
+
+def plan_decode_bytes(device: torch.device) -> int:
+    return int(_lib.load().b200kv_decode_plan_bytes(num_sms(device)))
+
+
+@_ranged
 def decode_attention(
     q: torch.Tensor,  # [B, Hq, D], one new token per sequence
     kv_cache: LayerKVCache,
@@ -166,6 +227,7 @@ def decode_attention(
     scale,
     out: torch.Tensor | None = None,  # [>= B, Hq, D]
     variant: int = 0,
+    plan: torch.Tensor | None = None,  # from plan_decode_step for this step's metadata (not a reference argument)
 ):
     _require_cuda(q, kv_cache.k, cached_lens, slot_ids, num_decoding)
     lib = _lib.load()
@@ -181,14 +243,24 @@ def decode_attention(
         raise ValueError("decode_attention: unsupported geometry")
     workspace = decode_workspace(q.device, B, Hq, Hkv, nbytes)
     cs, ts = _cache_struct(kv_cache), _table_struct(slot_ids)
-    rc = lib.b200kv_decode_attn(
-        q.data_ptr(), q.stride(0), q.stride(1), ctypes.byref(cs), ctypes.byref(ts), _i32(cached_lens),
-        _i32(num_decoding), float(scale), out.data_ptr(), out.stride(0), out.stride(1), workspace.data_ptr(), workspace.numel(),
-        B, Hq, sms, variant | (4 if _early_start else 0), status_word(q.device).data_ptr(), _stream())
+    variant = variant | (4 if _early_start else 0)
+    if plan is None:
+        rc = lib.b200kv_decode_attn(
+            q.data_ptr(), q.stride(0), q.stride(1), ctypes.byref(cs), ctypes.byref(ts), _i32(cached_lens),
+            _i32(num_decoding), float(scale), out.data_ptr(), out.stride(0), out.stride(1), workspace.data_ptr(),
+            workspace.numel(), B, Hq, sms, variant, status_word(q.device).data_ptr(), _stream())
+    else:
+        assert plan.dtype == torch.uint8 and plan.is_cuda
+        rc = lib.b200kv_decode_attn_planned(
+            q.data_ptr(), q.stride(0), q.stride(1), ctypes.byref(cs), ctypes.byref(ts), _i32(cached_lens),
+            _i32(num_decoding), float(scale), out.data_ptr(), out.stride(0), out.stride(1), workspace.data_ptr(),
+            workspace.numel(), plan.data_ptr(), plan.numel(), B, Hq, sms, variant,
+            status_word(q.device).data_ptr(), _stream())
     _lib.check(rc, "decode_attention")
     return out
 
 
+@_ranged
 def decode_attention_static(q, kv_cache: LayerKVCache, cached_lens, slot_ids, num_decoding, scale, out: torch.Tensor):
     """decode_attention for callers that must not allocate device memory at this point (all of it
     already belongs to their own pool, or an allocator call is not allowed where they run): the
@@ -210,6 +282,7 @@ def decode_attention_static(q, kv_cache: LayerKVCache, cached_lens, slot_ids, nu
     return out
 
 
+@_ranged
 def fused_rope_kv_decode(
     q: torch.Tensor,  # (B, Hq, D), one new token per sequence
     k: torch.Tensor,  # (B, Hkv, D)
@@ -240,6 +313,7 @@ def fused_rope_kv_decode(
     return out
 
 
+@_ranged
 def fused_norm_rope_prefill(
     q: torch.Tensor,  # bf16 [N, Hq, D]
     k: torch.Tensor,  # bf16 [N, Hkv, D]
@@ -266,6 +340,7 @@ def fused_norm_rope_prefill(
     return q_out, k_out
 
 
+@_ranged
 def quantize_kv_prefill(
     k: torch.Tensor,  # bf16 [N, Hkv, D], all sequences packed along N
     v: torch.Tensor,
@@ -287,6 +362,7 @@ def quantize_kv_prefill(
     _lib.check(rc, "quantize_kv_prefill")
 
 
+@_ranged
 def dequantize_kv_prefix(
     cache: LayerKVCache,
     cu_cached: torch.Tensor,  # int32 [B + 1]
@@ -304,6 +380,7 @@ def dequantize_kv_prefix(
     _lib.check(rc, "dequantize_kv_prefix")
 
 
+@_ranged
 def prefill_attention(
     q: torch.Tensor,  # bf16 [N, Hq, D]
     k: torch.Tensor,  # bf16 [N, Hkv, D]
@@ -337,6 +414,7 @@ def prefill_attention(
 
 # ----------------------------------------------------------------------------- decoder-block ops
 # The two element-wise ops between the attention path and the GEMMs, as CUDA kernels behind the same C ABI.
+@_ranged
 def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
     """kernels.py:1204-1212: bf16 [N, 2D] -> bf16 [N, D] = silu(gate) * up."""
     _require_cuda(gate_up)
@@ -349,6 +427,7 @@ def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
     return out
 
 
+@_ranged
 def add_rms_norm(residual: torch.Tensor, delta: torch.Tensor, rms_norm: torch.Tensor, eps: float):
     """kernels.py:1261-1285: (residual + delta, rmsnorm(residual + delta) * weight), bf16 [N, D] each."""
     _require_cuda(residual, delta, rms_norm)
@@ -367,6 +446,7 @@ def add_rms_norm(residual: torch.Tensor, delta: torch.Tensor, rms_norm: torch.Te
 # ----------------------------------------------------------------------------- scaffold ops
 # The remaining names the reference's architecture.py / engine.py import from kernels.py.  They
 # are outside the attention path; plain PyTorch keeps a model built on this module runnable.
+@_ranged
 def sample(logits: torch.Tensor, tau: float, seed: torch.Tensor) -> torch.Tensor:
     """kernels.py:1341-1370: Gumbel-max sampling (tau = 0: greedy argmax), int64 [B, 1]; `seed` (int64 [1] on
     the device) advances by one."""

@@ -137,13 +137,15 @@ def upload_step(plan: dict[str, list[int]], table: torch.Tensor, ids: list[int],
 
 
 def attention_ops(q, k, v, qw, kw, cos, sin, cache, inp: StepInputs | None, cached_lens, slot_ids, num_decoding,
-                  prefix: PrefixScratch | None):
+                  prefix: PrefixScratch | None, plan: torch.Tensor | None = None):
     """The attention path of one layer, in the reference's call order (architecture.py:99-198).
-    `inp is None` = pure decode.  Returns the attention output [N, Hq, D]."""
+    `inp is None` = pure decode.  `plan` = this step's kernels.plan_decode_step result, shared by all
+    layers (None: every decode_attention call derives its work split itself).  Returns the attention
+    output [N, Hq, D]."""
     scale = D ** -0.5
     if inp is None:
         q_d = K.fused_rope_kv_decode(q, k, v, qw, kw, cos, sin, slot_ids, cache, cached_lens, num_decoding, EPS)
-        return K.decode_attention(q_d, cache, cached_lens, slot_ids, num_decoding, scale)
+        return K.decode_attention(q_d, cache, cached_lens, slot_ids, num_decoding, scale, plan=plan)
     q_p, k_p = K.fused_norm_rope_prefill(q, k, qw, kw, cos, sin, EPS)
     K.quantize_kv_prefill(k_p, v, inp.cu_seqlens, slot_ids, cached_lens, num_decoding, cache)
     K.dequantize_kv_prefix(cache, prefix.cu_cached, slot_ids, prefix.k, prefix.v)
@@ -152,7 +154,7 @@ def attention_ops(q, k, v, qw, kw, cos, sin, cache, inp: StepInputs | None, cach
     B = slot_ids.shape[0]
     q_d = K.fused_rope_kv_decode(q[:B], k[:B], v[:B], qw, kw, cos[:B], sin[:B], slot_ids, cache,
                                  cached_lens, num_decoding, EPS)
-    K.decode_attention(q_d, cache, cached_lens, slot_ids, num_decoding, scale, out=out)
+    K.decode_attention(q_d, cache, cached_lens, slot_ids, num_decoding, scale, out=out, plan=plan)
     return out
 
 
@@ -179,6 +181,7 @@ class DecoderScaffold:
             for _ in range(layers)
         ]
         self.norm = torch.ones(hidden, device=device, dtype=torch.bfloat16)
+        self.plan_steps = True  # one kernels.plan_decode_step per forward, shared by the layers
         self.tau = 0.0  # sampling temperature (0 = greedy) and the sampler's seed, advanced by every step
         self.seed = torch.zeros(1, dtype=torch.int64, device=device)
         self.inv_freq = ROPE_BASE ** (-torch.arange(0, D, 2, dtype=torch.float32, device=device) / D)
@@ -192,6 +195,8 @@ class DecoderScaffold:
                 prefix: PrefixScratch | None = None):
         """One step: token ids [N] -> sampled next token per entry [entries] (int64; greedy while tau = 0).
         `inp is None` = pure decode (ids has one token per entry, position = cached length)."""
+        # the decode-attention work split of this step, once for all layers (it depends on the step's metadata only)
+        plan = K.plan_decode_step(cached_lens, slot_ids, num_decoding, caches[0]) if self.plan_steps else None
         x = self.embed[ids.long()]
         cos, sin = self.rope(cached_lens if inp is None else inp.positions)
         N = x.shape[0]
@@ -204,7 +209,7 @@ class DecoderScaffold:
                 residual, normed = K.add_rms_norm(residual, x, L["ln1"], EPS)
             q, k, v = K.linear(normed, L["qkv"]).split([HQ * D, HKV * D, HKV * D], dim=-1)
             out = attention_ops(q.view(N, HQ, D), k.view(N, HKV, D), v.view(N, HKV, D), L["qn"], L["kn"], cos, sin,
-                                cache, inp, cached_lens, slot_ids, num_decoding, prefix)
+                                cache, inp, cached_lens, slot_ids, num_decoding, prefix, plan)
             attn = K.linear(out.view(N, HQ * D), L["o"])
             residual, normed = K.add_rms_norm(residual, attn, L["ln2"], EPS)
             x = K.linear(K.silu_mul(K.linear(normed, L["gate_up"])), L["down"])

@@ -32,7 +32,7 @@ def test_library_exports_every_declared_symbol():
     for name in declared_functions():
         assert hasattr(lib, name), f"{name} is declared in include/b200kv.h but not exported"
         assert name in _lib.SIGNATURES, f"{name} has no ctypes signature"
-    assert lib.b200kv_version() == 1
+    assert lib.b200kv_version() == 2
     lib.b200kv_error_string.restype = ctypes.c_char_p
     assert b"workspace" in lib.b200kv_error_string(-4)
 
