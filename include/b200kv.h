@@ -131,6 +131,24 @@ int b200kv_quantize_prefill(const void* k, int64_t k_stride_n, int64_t k_stride_
                             const int32_t* cached_lens, const int32_t* num_decoding,
                             int32_t N, int32_t* status, void* stream);
 
+/* fused_norm_rope_prefill and quantize_kv_prefill in one call (kernels.py:547-714 followed by :717-865), for callers
+ * that need not keep the two as separate steps: q_out / k_out receive the normed + roped rows of all N packed rows
+ * exactly as b200kv_norm_rope_prefill writes them, and the rows of prefilling entries are quantized from the
+ * bf16-rounded k_out (the reference stores k as bf16 between its two kernels, so the codes depend on that rounding)
+ * and from v, with the calibration rule of b200kv_quantize_prefill.  Same bits as the two calls made one after the
+ * other; two launches instead of three, none of which waits for a serial pass over the chunk. */
+int b200kv_write_prefill(const void* q, int64_t q_stride_n, int64_t q_stride_h,
+                         const void* k, int64_t k_stride_n, int64_t k_stride_h,
+                         const void* v, int64_t v_stride_n, int64_t v_stride_h,
+                         const void* q_norm_w, const void* k_norm_w,
+                         const void* cos, int64_t cos_stride_n, const void* sin, int64_t sin_stride_n,
+                         const int32_t* cu_seqlens, int32_t num_entries,
+                         const b200kv_cache* cache, const b200kv_table* table,
+                         const int32_t* cached_lens, const int32_t* num_decoding,
+                         void* q_out, int64_t qo_stride_n, int64_t qo_stride_h,
+                         void* k_out, int64_t ko_stride_n, int64_t ko_stride_h,
+                         int32_t N, int32_t Hq, float eps, int32_t* status, void* stream);
+
 /* Replaces dequantize_kv_prefix (kernels.py:868-970): rows [cu_cached[b], cu_cached[b+1]) of
  * k_out/v_out bf16 [Hkv, capacity, D] receive bf16(code*k_scale*calibration) / bf16(code*v_scale)
  * of entry b's first cached tokens. */

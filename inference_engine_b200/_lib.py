@@ -45,6 +45,10 @@ SIGNATURES = {
                                            c_int64, c_int64, c_int32, c_int32, c_int32, c_int32, c_float, c_void_p]),
     "b200kv_quantize_prefill": (c_int32, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_void_p, c_int32,
                                           P_CACHE, P_TABLE, c_void_p, c_void_p, c_int32, c_void_p, c_void_p]),
+    "b200kv_write_prefill": (c_int32, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64,
+                                       c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int32,
+                                       P_CACHE, P_TABLE, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_int64,
+                                       c_int64, c_int32, c_int32, c_float, c_void_p, c_void_p]),
     "b200kv_dequant_prefix": (c_int32, [P_CACHE, P_TABLE, c_void_p, c_int32, c_void_p, c_void_p, c_int64, c_int64,
                                         c_int32, c_void_p, c_void_p]),
     "b200kv_prefill_attn": (c_int32, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64,

@@ -103,6 +103,14 @@ __device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// Arrival on a counter in global memory with release (my stores before it) and acquire (others' stores after it)
+// semantics at device scope, in one instruction.
+__device__ __forceinline__ int atom_add_acq_rel(int* addr, int v) {
+  int old;
+  asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], %2;" : "=r"(old) : "l"(addr), "r"(v) : "memory");
+  return old;
+}
+
 // ------------------------------------------------------------------ partition (all CTAs agree)
 constexpr int kSmemLens = 512;  // token counts of the first entries are kept in shared memory
 
@@ -649,7 +657,7 @@ struct Pieces {
 // round: lane k fetches (m, l) of piece k while every lane fetches its channels of all sixteen in
 // the same round of memory latency (the loads are unconditional and independent; a padded slot
 // repeats the last piece and gets weight zero), then an online-softmax update folds the round in.
-__device__ __forceinline__ void merge_partials(const float* __restrict__ ws_ml, const float* __restrict__ ws_o,
+__device__ __forceinline__ void merge_partials_by_column(const float* __restrict__ ws_ml, const float* __restrict__ ws_o,
                                                const Pieces& pc, int G, uint16_t* __restrict__ out_row, long long o_sh,
                                                int lane) {
   constexpr int kRound = 16;
@@ -689,6 +697,70 @@ __device__ __forceinline__ void merge_partials(const float* __restrict__ ws_ml, 
     r.y = float_to_bf16_bits(acc.z * inv) | (float_to_bf16_bits(acc.w * inv) << 16);
     *reinterpret_cast<uint2*>(out_row + col * o_sh + 4 * lane) = r;
   }
+}
+
+// The same for a GQA group of two heads (the geometry of the path), both heads in ONE round of loads per eight
+// pieces: lane 2k + col fetches (m, l) of (piece k, head col) while every lane fetches its channels of both heads of
+// all eight pieces (16 independent 16-byte loads), so up to eight pieces cost a single round of memory latency.
+__device__ __forceinline__ void merge_partials_pair(const float* __restrict__ ws_ml, const float* __restrict__ ws_o,
+                                                    const Pieces& pc, uint16_t* __restrict__ out_row, long long o_sh, int lane) {
+  constexpr int kRound = 8, G = 2;
+  float M[G] = {-INFINITY, -INFINITY}, L[G] = {0.f, 0.f};
+  float4 acc[G] = {make_float4(0.f, 0.f, 0.f, 0.f), make_float4(0.f, 0.f, 0.f, 0.f)};
+  for (int k0 = 0; k0 < pc.n; k0 += kRound) {
+    const int nb = min(kRound, pc.n - k0);
+    float2 ml = make_float2(-INFINITY, 0.f);
+    if (lane < 2 * nb) ml = __ldcg(reinterpret_cast<const float2*>(ws_ml + ((size_t)pc.slot_of(k0 + (lane >> 1)) * G + (lane & 1)) * 2));
+    float4 buf[kRound][G];
+#pragma unroll
+    for (int j = 0; j < kRound; ++j) {
+      const float* base = ws_o + (size_t)pc.slot_of(k0 + min(j, nb - 1)) * G * kD + 4 * lane;
+      buf[j][0] = __ldcg(reinterpret_cast<const float4*>(base));
+      buf[j][1] = __ldcg(reinterpret_cast<const float4*>(base + kD));
+    }
+    // maximum per head: lanes of equal parity among the first sixteen hold that head's pieces
+    float mb = lane < 2 * nb ? ml.x : -INFINITY;
+#pragma unroll
+    for (int o = 2; o < 32; o <<= 1) mb = fmaxf(mb, __shfl_xor_sync(0xffffffffu, mb, o));
+    const float mb0 = __shfl_sync(0xffffffffu, mb, 0), mb1 = __shfl_sync(0xffffffffu, mb, 1);
+    const float Mn[G] = {fmaxf(M[0], mb0), fmaxf(M[1], mb1)};
+    const float wgt = lane < 2 * nb ? fast_exp2(ml.x - Mn[lane & 1]) : 0.f;
+    float ls = ml.y * wgt;
+#pragma unroll
+    for (int o = 2; o < 32; o <<= 1) ls += __shfl_xor_sync(0xffffffffu, ls, o);
+    const float ls0 = __shfl_sync(0xffffffffu, ls, 0), ls1 = __shfl_sync(0xffffffffu, ls, 1);
+#pragma unroll
+    for (int c = 0; c < G; ++c) {
+      const float resc = M[c] == -INFINITY ? 0.f : fast_exp2(M[c] - Mn[c]);
+      L[c] = L[c] * resc + (c ? ls1 : ls0);
+      acc[c].x *= resc; acc[c].y *= resc; acc[c].z *= resc; acc[c].w *= resc;
+      M[c] = Mn[c];
+    }
+#pragma unroll
+    for (int j = 0; j < kRound; ++j) {
+#pragma unroll
+      for (int c = 0; c < G; ++c) {
+        const float wg = __shfl_sync(0xffffffffu, wgt, 2 * j + c);
+        acc[c].x = fmaf(buf[j][c].x, wg, acc[c].x); acc[c].y = fmaf(buf[j][c].y, wg, acc[c].y);
+        acc[c].z = fmaf(buf[j][c].z, wg, acc[c].z); acc[c].w = fmaf(buf[j][c].w, wg, acc[c].w);
+      }
+    }
+  }
+#pragma unroll
+  for (int c = 0; c < G; ++c) {
+    const float inv = 1.f / L[c];
+    uint2 r;
+    r.x = float_to_bf16_bits(acc[c].x * inv) | (float_to_bf16_bits(acc[c].y * inv) << 16);
+    r.y = float_to_bf16_bits(acc[c].z * inv) | (float_to_bf16_bits(acc[c].w * inv) << 16);
+    *reinterpret_cast<uint2*>(out_row + c * o_sh + 4 * lane) = r;
+  }
+}
+
+__device__ __forceinline__ void merge_partials(const float* __restrict__ ws_ml, const float* __restrict__ ws_o,
+                                               const Pieces& pc, int G, uint16_t* __restrict__ out_row, long long o_sh,
+                                               int lane) {
+  if (G == 2) merge_partials_pair(ws_ml, ws_o, pc, out_row, o_sh, lane);
+  else merge_partials_by_column(ws_ml, ws_o, pc, G, out_row, o_sh, lane);
 }
 
 __host__ __device__ inline size_t ws_ml_bytes(int W, int G) { return (((size_t)W * 2 * G * 2 * 4 + 255) / 256) * 256; }
@@ -748,16 +820,20 @@ decode_plan_kernel(const int32_t* __restrict__ cached_lens, const int32_t* __res
 }
 
 #ifdef B200KV_STAMPS
-// Instrumented build only: per warp of the persistent grid {kernel entry, smid, first copy issued, first tile
-// landed, last tile consumed, exit, tiles, pieces merged} with %globaltimer nanoseconds.
-constexpr int kStampWarps = 4096;
-__device__ unsigned long long g_stamps[kStampWarps * 8];
+// Instrumented build only: 16 words per warp of the persistent grid.  [0] kernel entry and [5] exit in %globaltimer
+// nanoseconds, [1] SM id, [6] tiles, [7] pieces merged; the rest are SM clock cycles since this warp's entry:
+// [8] metadata there (plan or scan done), [2] first copies issued, [9] q of the first segment loaded, [3] first tile
+// landed, [4] last tile consumed, [10] last piece stored, [11] arrival counter answered (last arriver only),
+// [12] merge done (last arriver only), [13] exit.
+constexpr int kStampWarps = 4096, kStampWords = 16;
+__device__ unsigned long long g_stamps[kStampWarps * kStampWords];
 __device__ __forceinline__ unsigned long long gtime() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
 }
-#define STAMP(i, v) do { if (lane == 0 && w < kStampWarps) g_stamps[8 * w + (i)] = (v); } while (0)
+#define STAMP(i, v) do { if (lane == 0 && w < kStampWarps) g_stamps[kStampWords * w + (i)] = (v); } while (0)
+#define dclk() ((unsigned long long)(clock64() - c_entry))
 #else
 #define STAMP(i, v) do { } while (0)
 #endif
@@ -776,6 +852,7 @@ decode_attn_kernel(const uint16_t* __restrict__ q, long long q_sb, long long q_s
   const int w = blockIdx.x * kWarps + warp;
 #ifdef B200KV_STAMPS
   const unsigned long long t_entry = gtime();
+  const long long c_entry = clock64();
 #endif
 
   // The first CTA waits for the predecessor at once, so that this grid can never complete before it.  The
@@ -845,6 +922,7 @@ decode_attn_kernel(const uint16_t* __restrict__ q, long long q_sb, long long q_s
     const Lens probe{cached_lens, lens_s, nd};
     pc.seek(chunk_prefix, nchunks, chunk, probe, c.Hkv, c.page_size, w * part.per);
   }
+  STAMP(8, dclk());
   const Lens lens{cached_lens, lens_s, nd};
   const int u0 = w * part.per;
   const int ntiles = min(part.per, part.U - u0);
@@ -879,7 +957,7 @@ decode_attn_kernel(const uint16_t* __restrict__ q, long long q_sb, long long q_s
     }
     cp_async_commit();
   }
-  STAMP(2, gtime());
+  STAMP(2, dclk());
   // planned: the table row of the next tile is requested now and is there when the main loop wants it
   if (plan != nullptr && p_left > 0) load_window(c, pc.b, pc.slot, win, lane);
   if (must_wait) asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -893,6 +971,9 @@ decode_attn_kernel(const uint16_t* __restrict__ q, long long q_sb, long long q_s
     const int seg = min(cc.T - cc.tile, ntiles - done);
     if constexpr (kScalar) scalar_begin(st, my_q, q, q_sb, q_sh, cc.b, cc.h, G, scale_log2, lane);
     else mma_begin(st, q, q_sb, q_sh, cc.b, cc.h, G, scale_log2, lane);
+#ifdef B200KV_STAMPS
+    if (done == 0) STAMP(9, dclk());
+#endif
     int remaining = cc.n - cc.tile * kTile;  // tokens from this tile to the end of the sequence
     for (int k = 0; k < seg; ++k) {
       if (p_left > 0) {
@@ -904,7 +985,7 @@ decode_attn_kernel(const uint16_t* __restrict__ q, long long q_sb, long long q_s
       cp_async_wait<kStages - 1>();
       __syncwarp();
 #ifdef B200KV_STAMPS
-      if (done == 0 && k == 0) STAMP(3, gtime());
+      if (done == 0 && k == 0) STAMP(3, dclk());
 #endif
       const uint8_t* stage = my_ring + stage_c * kTileBytes;
       if constexpr (kScalar) scalar_tile(st, my_q, my_q + kMaxG * kD, stage, min(remaining, kTile), G, lane);
@@ -915,7 +996,7 @@ decode_attn_kernel(const uint16_t* __restrict__ q, long long q_sb, long long q_s
       stage_p = (stage_p + 1) & (kStages - 1);
     }
 #ifdef B200KV_STAMPS
-    if (done + seg >= ntiles) STAMP(4, gtime());
+    if (done + seg >= ntiles) STAMP(4, dclk());
 #endif
     // whole iff the segment began at the sequence's first tile and reached its last one
     const bool whole = cc.tile == 0 && seg == cc.T;
@@ -980,21 +1061,25 @@ decode_attn_kernel(const uint16_t* __restrict__ q, long long q_sb, long long q_s
       if constexpr (kScalar) scalar_end(st, whole, out, o_sb, o_sh, cc.b, cc.h, G, po, pml, lane);
       else mma_end(st, whole, out, o_sb, o_sh, cc.b, cc.h, G, po, pml, lane);
     }
+#ifdef B200KV_STAMPS
+    if (done + seg >= ntiles) STAMP(10, dclk());
+#endif
     if (fused && deliver) {
       // Fused cross-split reduction: the warp that delivers the last piece of (entry, head) merges
-      // all of them.  Release: partial stores -> fence -> counter; acquire: counter -> fence -> loads.
+      // all of them.  Release: partial stores -> warp barrier -> counter; acquire: counter -> warp barrier -> loads.
       const Pieces pieces(part, s0, s0 + cc.T);
-      __threadfence();
-      __syncwarp();
+      __syncwarp();  // the lanes' partial stores are ordered before lane 0's release below
       int arrived = 0;
-      if (lane == 0) arrived = atomicAdd(ws_count + cc.b * c.Hkv + cc.h, 1) + 1;
+      if (lane == 0) arrived = atom_add_acq_rel(ws_count + cc.b * c.Hkv + cc.h, 1) + 1;
       arrived = __shfl_sync(0xffffffffu, arrived, 0);
-      if (arrived == pieces.n) {
-        __threadfence();
+      if (arrived == pieces.n) {  // the acquire half makes every earlier arriver's stores visible to this warp
+        __syncwarp();
+        STAMP(11, dclk());
         merge_partials(ws_ml, ws_o, pieces, G, out_row, o_sh, lane);
         if (lane == 0) ws_count[cc.b * c.Hkv + cc.h] = 0;  // leave the counter zero for the next call
 #ifdef B200KV_STAMPS
         STAMP(7, (unsigned long long)pieces.n);
+        STAMP(12, dclk());
 #endif
       }
     }
@@ -1007,6 +1092,7 @@ decode_attn_kernel(const uint16_t* __restrict__ q, long long q_sb, long long q_s
     unsigned sm;
     asm volatile("mov.u32 %0, %%smid;" : "=r"(sm));
     STAMP(0, t_entry); STAMP(1, (unsigned long long)sm); STAMP(5, gtime()); STAMP(6, (unsigned long long)ntiles);
+    STAMP(13, dclk());
   }
 #endif
 }
@@ -1224,11 +1310,11 @@ extern "C" int b200kv_decode_attn_planned(const void* q, int64_t q_sb, int64_t q
 
 #ifdef B200KV_STAMPS
 extern "C" int b200kv_stamps_read(unsigned long long* host, int clear) {
-  cudaError_t e = cudaMemcpyFromSymbol(host, b200kv::g_stamps, sizeof(unsigned long long) * kStampWarps * 8);
+  cudaError_t e = cudaMemcpyFromSymbol(host, b200kv::g_stamps, sizeof(unsigned long long) * kStampWarps * kStampWords);
   if (e == cudaSuccess && clear) {
     void* p = nullptr;
     e = cudaGetSymbolAddress(&p, b200kv::g_stamps);
-    if (e == cudaSuccess) e = cudaMemset(p, 0, sizeof(unsigned long long) * kStampWarps * 8);
+    if (e == cudaSuccess) e = cudaMemset(p, 0, sizeof(unsigned long long) * kStampWarps * kStampWords);
   }
   return e == cudaSuccess ? kStampWarps : -1;
 }

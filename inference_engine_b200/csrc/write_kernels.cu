@@ -62,14 +62,39 @@ __device__ __forceinline__ float sum_squares_ordered(const float (&x)[4], float*
 }
 
 // RMSNorm + half-split rotation of one head row; result elements d = 4*lane + c.
-// kernels.py:414-436 / 583-633.
+// kernels.py:414-436 / 583-633.  The operands are already in registers, so that a caller can put all of its
+// loads (this row, the page table, the calibration) in flight before the first arithmetic instruction needs one.
+struct HeadRow {
+  uint2 x, w, c, s;  // 4 bf16 each: the row, the norm weight, cos and sin of this lane's rotary columns
+};
+__device__ __forceinline__ HeadRow load_head_row(const void* x_row, const void* w, const void* cos_row,
+                                                 const void* sin_row, int lane) {
+  HeadRow r;
+  r.x = *reinterpret_cast<const uint2*>(reinterpret_cast<const uint16_t*>(x_row) + 4 * lane);
+  r.w = *reinterpret_cast<const uint2*>(reinterpret_cast<const uint16_t*>(w) + 4 * lane);
+  r.c = *reinterpret_cast<const uint2*>(reinterpret_cast<const uint16_t*>(cos_row) + 4 * (lane & 15));
+  r.s = *reinterpret_cast<const uint2*>(reinterpret_cast<const uint16_t*>(sin_row) + 4 * (lane & 15));
+  return r;
+}
+__device__ __forceinline__ void unpack4(uint2 raw, float (&x)[4]) {
+  x[0] = bf16_bits_to_float(raw.x & 0xFFFFu);
+  x[1] = bf16_bits_to_float(raw.x >> 16);
+  x[2] = bf16_bits_to_float(raw.y & 0xFFFFu);
+  x[3] = bf16_bits_to_float(raw.y >> 16);
+}
+__device__ __forceinline__ void norm_rope_regs(const HeadRow& row, float eps, float* sq, int lane, float (&out)[4]);
+
 __device__ __forceinline__ void norm_rope_head(const void* x_row, const void* w, const void* cos_row,
                                                const void* sin_row, float eps, float* sq, int lane, float (&out)[4]) {
+  norm_rope_regs(load_head_row(x_row, w, cos_row, sin_row, lane), eps, sq, lane, out);
+}
+
+__device__ __forceinline__ void norm_rope_regs(const HeadRow& row, float eps, float* sq, int lane, float (&out)[4]) {
   float x[4], wv[4], c[4], s[4];
-  load4_bf16(x_row, lane, x);
-  load4_bf16(w, lane, wv);
-  load4_bf16(cos_row, lane & 15, c);
-  load4_bf16(sin_row, lane & 15, s);
+  unpack4(row.x, x);
+  unpack4(row.w, wv);
+  unpack4(row.c, c);
+  unpack4(row.s, s);
   float ss = sum_squares_ordered(x, sq, lane);
   float rstd = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)kD), eps)));
   const bool first_half = lane < 16;
@@ -123,46 +148,63 @@ write_decode_kernel(const uint16_t* __restrict__ q, long long q_sb, long long q_
   pdl_enter();
   const int b = blockIdx.x;
   if (b >= *num_decoding) return;
-  pdl_wait();  // q, k, v come from the kernel before this one
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int job = blockIdx.y * kWarpsPerBlock + warp;
   const int Hkv = c.Hkv;
   if (job >= Hq + 2 * Hkv) return;
   float* sq = sq_all[warp];
-
+  // Round one of loads (metadata, allowed before the wait): where the new token goes and the page that holds the
+  // sequence's calibration row.
+  const int32_t* trow = c.table + (long long)b * c.table_stride;
   const int pos = cached_lens[b];
-  if (job < Hq) {
-    float r[4], cal[4];
-    norm_rope_head(q + b * q_sb + job * q_sh, qw, cosp + b * cos_sb, sinp + b * sin_sb, eps, sq, lane, r);
-    int page0 = lookup_page(c, b, 0, status);
-    if (page0 < 0) return;
-    const int hk = job / (Hq / Hkv);
-    load4_f32(c.k_cal + page0 * c.cstride_page + hk * c.cstride_head, lane, cal);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) r[i] = __fmul_rn(r[i], cal[i]);
-    store4_bf16(q_out + b * o_sb + job * o_sh, lane, r);
+  int page0 = trow[0];
+  pdl_wait();  // q, k, v come from the kernel before this one
+  // ... and this warp's head row with its norm weight and rotary columns
+  const bool is_q = job < Hq, is_k = !is_q && job < Hq + Hkv;
+  const int j = is_q ? job : (is_k ? job - Hq : job - Hq - Hkv);
+  HeadRow row;
+  if (is_q) row = load_head_row(q + b * q_sb + j * q_sh, qw, cosp + b * cos_sb, sinp + b * sin_sb, lane);
+  else if (is_k) row = load_head_row(k + b * k_sb + j * k_sh, kw, cosp + b * cos_sb, sinp + b * sin_sb, lane);
+  else row.x = *reinterpret_cast<const uint2*>(v + b * v_sb + j * v_sh + 4 * lane);
+  // Round two, issued as soon as round one's metadata is there: the page of the new token and the calibration.
+  const int slot = pos / c.page_size;
+  const bool pos_ok = pos >= 0 && slot < c.max_pages;
+  int page = (!is_q && pos_ok) ? trow[slot] : 0;
+  const bool page0_ok = page0 >= 0 && page0 < c.num_pages;
+  float cal[4] = {1.f, 1.f, 1.f, 1.f};
+  if ((is_q || is_k) && page0_ok)
+    load4_f32(c.k_cal + page0 * c.cstride_page + (is_q ? j / (Hq / Hkv) : j) * c.cstride_head, lane, cal);
+  if ((is_q || is_k) && !page0_ok) {
+    if (lane == 0 && status) atomicOr(status, B200KV_S_BAD_PAGE);
     return;
   }
-  const int page = lookup_page(c, b, pos, status);
-  if (page < 0) return;
-  const int row = pos % c.page_size;
-  if (job < Hq + Hkv) {
-    const int j = job - Hq;
-    float r[4], cal[4];
-    norm_rope_head(k + b * k_sb + j * k_sh, kw, cosp + b * cos_sb, sinp + b * sin_sb, eps, sq, lane, r);
-    int page0 = lookup_page(c, b, 0, status);
-    if (page0 < 0) return;
-    load4_f32(c.k_cal + page0 * c.cstride_page + j * c.cstride_head, lane, cal);
+  if (!is_q) {
+    if (!pos_ok) {
+      if (lane == 0 && status) atomicOr(status, B200KV_S_BAD_POSITION);
+      return;
+    }
+    if (page < 0 || page >= c.num_pages) {
+      if (lane == 0 && status) atomicOr(status, B200KV_S_BAD_PAGE);
+      return;
+    }
+  }
+  const int prow = pos % c.page_size;
+  float r[4];
+  if (is_q) {
+    norm_rope_regs(row, eps, sq, lane, r);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) r[i] = __fmul_rn(r[i], cal[i]);
+    store4_bf16(q_out + b * o_sb + j * o_sh, lane, r);
+  } else if (is_k) {
+    norm_rope_regs(row, eps, sq, lane, r);
 #pragma unroll
     for (int i = 0; i < 4; ++i) r[i] = __fdiv_rn(r[i], cal[i]);
-    quantize_store(r, c.k + page * c.stride_page + j * c.stride_head + row * c.stride_tok,
-                   c.k_scale + page * c.sstride_page + j * c.sstride_head + row, lane);
+    quantize_store(r, c.k + page * c.stride_page + j * c.stride_head + prow * c.stride_tok,
+                   c.k_scale + page * c.sstride_page + j * c.sstride_head + prow, lane);
   } else {
-    const int j = job - Hq - Hkv;
-    float x[4];
-    load4_bf16(v + b * v_sb + j * v_sh, lane, x);
-    quantize_store(x, c.v + page * c.stride_page + j * c.stride_head + row * c.stride_tok,
-                   c.v_scale + page * c.sstride_page + j * c.sstride_head + row, lane);
+    unpack4(row.x, r);
+    quantize_store(r, c.v + page * c.stride_page + j * c.stride_head + prow * c.stride_tok,
+                   c.v_scale + page * c.sstride_page + j * c.sstride_head + prow, lane);
   }
 }
 
@@ -196,96 +238,251 @@ norm_rope_prefill_kernel(const uint16_t* __restrict__ q, long long q_sn, long lo
 }
 
 // ------------------------------------------------------------------ prefill quantize
-// Entry of packed row r, found by a whole warp: every lane tests one entry per round, so the answer costs one or
-// two rounds of memory latency instead of log2(entries) dependent ones.  The entry holding row r is the one
-// with cu[e] <= r < cu[e+1] (an empty entry never matches).  Returns -1 when r is past the last entry.
-__device__ __forceinline__ int entry_of_row_warp(const int32_t* cu, int num_entries, int r, int lane) {
-  for (int e0 = 0; e0 < num_entries; e0 += 32) {
-    const int e = e0 + lane;
-    const bool hit = e < num_entries && cu[e] <= r && r < cu[e + 1];
-    const unsigned m = __ballot_sync(0xffffffffu, hit);
-    if (m) return e0 + __ffs(m) - 1;
-  }
-  return -1;
-}
-
 __device__ __forceinline__ bool is_first_chunk(int b, int nd, const int32_t* cu, const int32_t* cached_lens) {
   return b >= nd && cu[b + 1] > cu[b] && cached_lens[b] == 0;
 }
 
-// Phase 1: calibration of first-chunk entries: cal[d] = max(1e-3, max_t |k[t,d]|) over the chunk's rows
-// (kernels.py:764-780).  max is exact and order-independent, so any split of the rows reproduces the serial
-// result.  grid (num_entries, Hkv), 1024 threads: 32 row groups x 32 lanes of 4 channels (8-byte loads, eight
-// rows in flight per thread), reduced through shared memory; entries that are not on their first chunk leave
-// at once.
-constexpr int kCalibGroups = 32;
-__global__ void __launch_bounds__(kCalibGroups * 32)
-calibrate_kernel(const uint16_t* __restrict__ k, long long k_sn, long long k_sh, CacheView c,
-                 const int32_t* __restrict__ cu, const int32_t* __restrict__ cached_lens,
-                 const int32_t* __restrict__ num_decoding, int N, int32_t* status) {
-  pdl_enter();
-  const int b = blockIdx.x, h = blockIdx.y;
-  if (!is_first_chunk(b, *num_decoding, cu, cached_lens)) return;
-  pdl_wait();  // k comes from the kernel before this one
-  const int lane = threadIdx.x & 31, g = threadIdx.x >> 5;
-  const int s0 = cu[b], s1 = min(cu[b + 1], N);
-  float m[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll 8
-  for (int t = s0 + g; t < s1; t += kCalibGroups) {
-    float x[4];
-    load4_bf16(k + t * k_sn + h * k_sh, lane, x);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) m[i] = fmaxf(m[i], fabsf(x[i]));
+// ------------------------------------------------------------------ prefill write
+// Two kernels that do not depend on one another replace the reference's serial loop over a chunk (8 programs per
+// chunk, kernels.py:717-823):
+//   rows kernel        one warp per (packed row, head): V of every prefilling row, and K of the rows whose entry
+//                      already has a calibration (not its first chunk): k / calibration -> codes + scale;
+//   first-chunk kernel K of entries on their first chunk, which need the column maxima of the WHOLE chunk before
+//                      any row can be quantized (kernels.py:764-780): a cluster of kFirstCtas CTAs per kv head
+//                      shares the rows, exchanges its 128 column maxima through distributed shared memory between
+//                      two cluster barriers (no global round trip, no spinning) and quantizes its rows from registers.
+// The fused entry point runs the rows kernel with the norm + rope of q and k folded in (one launch does what
+// fused_norm_rope_prefill and the row part of quantize_kv_prefill do), then the first-chunk kernel.
+
+// Which entry owns packed row r, with that entry's first row, cached length and first page, found by the whole
+// warp in one round of loads (lane e tests entry e0 + e).  b = -1: the row lies behind the last entry.
+struct RowEntry {
+  int b, start, cached, page0;
+};
+__device__ __forceinline__ RowEntry find_row_entry(const int32_t* __restrict__ cu, int num_entries,
+                                                   const int32_t* __restrict__ cached_lens, const CacheView& c, int r, int lane) {
+  RowEntry re{-1, 0, 0, -1};
+  for (int e0 = 0; e0 < num_entries; e0 += 32) {
+    const int e = e0 + lane;
+    const bool in = e < num_entries;
+    const int lo = in ? cu[e] : 0, hi = in ? cu[e + 1] : 0;
+    const int cl = in ? cached_lens[e] : 0;
+    const int p0 = in ? c.table[(long long)e * c.table_stride] : -1;
+    const unsigned m = __ballot_sync(0xffffffffu, in && lo <= r && r < hi);
+    if (m) {
+      const int src = __ffs(m) - 1;
+      re.b = e0 + src;
+      re.start = __shfl_sync(0xffffffffu, lo, src);
+      re.cached = __shfl_sync(0xffffffffu, cl, src);
+      re.page0 = __shfl_sync(0xffffffffu, p0, src);
+      break;
+    }
   }
-  __shared__ float part[kCalibGroups][kD];
+  return re;
+}
+
+// The cache row of token position `pos` of entry b: page id from the table (bounds-checked, status bit on failure).
+__device__ __forceinline__ int page_of(const CacheView& c, int b, int pos, int32_t* status, int lane) {
+  const int slot = pos / c.page_size;
+  if (pos < 0 || slot >= c.max_pages) {
+    if (lane == 0 && status) atomicOr(status, B200KV_S_BAD_POSITION);
+    return -1;
+  }
+  const int page = c.table[(long long)b * c.table_stride + slot];
+  if (page < 0 || page >= c.num_pages) {
+    if (lane == 0 && status) atomicOr(status, B200KV_S_BAD_PAGE);
+    return -1;
+  }
+  return page;
+}
+
+// kFusedNorm = true: q, k are the raw projections; the kernel norms and ropes every row of them into q_out / k_out
+// (what fused_norm_rope_prefill does, kernels.py:547-670) and quantizes from the bf16-rounded k it just produced.
+// kFusedNorm = false: k is already normed + roped bf16 (the argument of quantize_kv_prefill), q is not touched.
+// grid (N, ceil(jobs / 8)); warp job: [0, Hq) q heads (fused only), then Hkv k heads, then Hkv v heads.
+template <bool kFusedNorm>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+prefill_rows_kernel(const uint16_t* __restrict__ q, long long q_sn, long long q_sh,
+                    const uint16_t* __restrict__ k, long long k_sn, long long k_sh,
+                    const uint16_t* __restrict__ v, long long v_sn, long long v_sh,
+                    const uint16_t* __restrict__ qw, const uint16_t* __restrict__ kw,
+                    const uint16_t* __restrict__ cosp, long long cos_sn, const uint16_t* __restrict__ sinp, long long sin_sn,
+                    uint16_t* __restrict__ q_out, long long qo_sn, long long qo_sh,
+                    uint16_t* __restrict__ k_out, long long ko_sn, long long ko_sh,
+                    CacheView c, const int32_t* __restrict__ cu, int num_entries, const int32_t* __restrict__ cached_lens,
+                    const int32_t* __restrict__ num_decoding, int Hq, float eps, int32_t* status) {
+  __shared__ __align__(16) float sq_all[kFusedNorm ? kWarpsPerBlock : 1][kD];
+  pdl_enter();
+  const int r = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int job = blockIdx.y * kWarpsPerBlock + warp;
+  const int Hkv = c.Hkv, nq = kFusedNorm ? Hq : 0;
+  if (job >= nq + 2 * Hkv) return;
+  const bool is_q = job < nq, is_k = !is_q && job < nq + Hkv;
+  const int j = is_q ? job : (is_k ? job - nq : job - nq - Hkv);
+  // round one (metadata, readable before the wait): the row's entry
+  const int nd = *num_decoding;
+  const RowEntry re = find_row_entry(cu, num_entries, cached_lens, c, r, lane);
+  const bool prefilling = re.b >= 0 && re.b >= nd;
+  const bool first_chunk = prefilling && re.cached == 0;
+  if (!kFusedNorm && (!prefilling || (is_k && first_chunk))) return;  // nothing to quantize here
+  if (kFusedNorm && !is_q && !is_k && !prefilling) return;
+  pdl_wait();  // q, k, v come from the kernel before this one
+  HeadRow row;
+  if (kFusedNorm && is_q) row = load_head_row(q + r * q_sn + j * q_sh, qw, cosp + r * cos_sn, sinp + r * sin_sn, lane);
+  else if (kFusedNorm && is_k) row = load_head_row(k + r * k_sn + j * k_sh, kw, cosp + r * cos_sn, sinp + r * sin_sn, lane);
+  else row.x = *reinterpret_cast<const uint2*>((is_k ? k + r * k_sn + j * k_sh : v + r * v_sn + j * v_sh) + 4 * lane);
+  // round two: the page of this row's token and the entry's calibration
+  const bool quantizes = prefilling && !is_q && !(is_k && first_chunk);
+  const int pos = re.cached + (r - re.start);
+  int page = -1;
+  float cal[4] = {1.f, 1.f, 1.f, 1.f};
+  if (quantizes) {
+    page = page_of(c, re.b, pos, status, lane);
+    if (is_k) {
+      if (re.page0 < 0 || re.page0 >= c.num_pages) {
+        if (lane == 0 && status) atomicOr(status, B200KV_S_BAD_PAGE);
+        page = -1;
+      } else {
+        load4_f32(c.k_cal + re.page0 * c.cstride_page + j * c.cstride_head, lane, cal);
+      }
+    }
+  }
+  float x[4];
+  if (kFusedNorm && (is_q || is_k)) {
+    norm_rope_regs(row, eps, sq_all[kFusedNorm ? warp : 0], lane, x);
+    if (is_q) {
+      store4_bf16(q_out + r * qo_sn + j * qo_sh, lane, x);
+      return;
+    }
+    store4_bf16(k_out + r * ko_sn + j * ko_sh, lane, x);
 #pragma unroll
-  for (int i = 0; i < 4; ++i) part[g][4 * lane + i] = m[i];
-  __syncthreads();
-  if (threadIdx.x < kD) {
-    float r = 1e-3f;
+    for (int i = 0; i < 4; ++i) x[i] = bf16_bits_to_float(float_to_bf16_bits(x[i]));  // the quantizer reads the stored bf16
+  } else {
+    unpack4(row.x, x);
+  }
+  if (!quantizes || page < 0) return;
+  const int prow = pos % c.page_size;
+  if (is_k) {
 #pragma unroll
-    for (int i = 0; i < kCalibGroups; ++i) r = fmaxf(r, part[i][threadIdx.x]);
-    const int page0 = lookup_page(c, b, 0, status);
-    if (page0 >= 0) c.k_cal[page0 * c.cstride_page + h * c.cstride_head + threadIdx.x] = r;
+    for (int i = 0; i < 4; ++i) x[i] = __fdiv_rn(x[i], cal[i]);
+    quantize_store(x, c.k + page * c.stride_page + j * c.stride_head + prow * c.stride_tok,
+                   c.k_scale + page * c.sstride_page + j * c.sstride_head + prow, lane);
+  } else {
+    quantize_store(x, c.v + page * c.stride_page + j * c.stride_head + prow * c.stride_tok,
+                   c.v_scale + page * c.sstride_page + j * c.sstride_head + prow, lane);
   }
 }
 
-// Phase 2: quantize every prefill row (kernels.py:786-823).  grid (N, ceil(2*Hkv/8)); warp job
-// j: [0,Hkv) k heads, [Hkv,2Hkv) v heads.
-__global__ void __launch_bounds__(kWarpsPerBlock * 32)
-quantize_prefill_kernel(const uint16_t* __restrict__ k, long long k_sn, long long k_sh,
-                        const uint16_t* __restrict__ v, long long v_sn, long long v_sh, CacheView c,
-                        const int32_t* __restrict__ cu, int num_entries, const int32_t* __restrict__ cached_lens,
-                        const int32_t* __restrict__ num_decoding, int32_t* status) {
+// K of first-chunk entries.  grid (Hkv, kFirstLanes, kFirstCtas), cluster (1, 1, kFirstCtas), kFirstWarps warps.
+// Cluster (h, y) walks the entries b = y, y + kFirstLanes, ... that are on their first chunk; its CTAs share the
+// chunk's rows round-robin by warp.  Per entry: every warp takes the column maxima of its rows (the first
+// kKeepRows stay in registers), the CTA folds its warps' maxima in shared memory, the cluster's CTAs read one
+// another's 128 maxima through distributed shared memory between two cluster barriers, calibration =
+// max(1e-3, column max) (exact and order-independent, kernels.py:764-780) is stored by CTA 0, and every warp
+// quantizes its rows as k / calibration (kernels.py:786-811).
+constexpr int kFirstCtas = 8, kFirstWarps = 16, kFirstLanes = 4, kKeepRows = 8;
+__global__ void __launch_bounds__(kFirstWarps * 32)
+first_chunk_k_kernel(const uint16_t* __restrict__ k, long long k_sn, long long k_sh, CacheView c,
+                     const int32_t* __restrict__ cu, int num_entries, const int32_t* __restrict__ cached_lens,
+                     const int32_t* __restrict__ num_decoding, int N, int32_t* status) {
+  __shared__ __align__(16) float part[kFirstWarps][kD];
+  __shared__ float cta_max[kD];
+  __shared__ __align__(16) float cal_s[kD];
   pdl_enter();
-  const int r = blockIdx.x;
-  if (r >= cu[num_entries]) return;
+  const int h = blockIdx.x, y = blockIdx.y;
+  unsigned crank;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(crank));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int job = blockIdx.y * kWarpsPerBlock + warp;
-  if (job >= 2 * c.Hkv) return;
-  const int b = entry_of_row_warp(cu, num_entries, r, lane);
-  if (b < 0 || b < *num_decoding) return;
-  pdl_wait();  // k, v and the calibration come from the kernels before this one
-  float x[4];
-  if (job < c.Hkv) load4_bf16(k + r * k_sn + job * k_sh, lane, x);  // in flight during the page lookups
-  else load4_bf16(v + r * v_sn + (job - c.Hkv) * v_sh, lane, x);
-  const int pos = cached_lens[b] + (r - cu[b]);
-  const int page = lookup_page(c, b, pos, status);
-  if (page < 0) return;
-  const int row = pos % c.page_size;
-  if (job < c.Hkv) {
-    const int page0 = lookup_page(c, b, 0, status);
-    if (page0 < 0) return;
-    float cal[4];
-    load4_f32(c.k_cal + page0 * c.cstride_page + job * c.cstride_head, lane, cal);
+  const int nd = *num_decoding;
+  const int wid = (int)crank * kFirstWarps + warp, nw = kFirstCtas * kFirstWarps;  // this warp among the cluster's
+  bool waited = false;
+  for (int e0 = 0; e0 < num_entries; e0 += 32) {
+    // the entries of this cluster's lane that are on their first chunk, 32 candidates per round of loads; every
+    // thread of the cluster sees the same mask, so the barriers below are reached by all or by none
+    const int e = e0 + lane;
+    unsigned mask = __ballot_sync(0xffffffffu, e < num_entries && (e % kFirstLanes) == y && is_first_chunk(e, nd, cu, cached_lens));
+    while (mask) {
+      const int b = e0 + __ffs(mask) - 1;
+      mask &= mask - 1;
+      if (!waited) {
+        pdl_wait();  // k comes from the kernel before this one
+        waited = true;
+      }
+      const int s0 = cu[b], s1 = min(cu[b + 1], N);
+      const uint16_t* kcol = k + h * k_sh + 4 * lane;
+      uint2 keep[kKeepRows];
+      float m[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-    for (int i = 0; i < 4; ++i) x[i] = __fdiv_rn(x[i], cal[i]);
-    quantize_store(x, c.k + page * c.stride_page + job * c.stride_head + row * c.stride_tok,
-                   c.k_scale + page * c.sstride_page + job * c.sstride_head + row, lane);
-  } else {
-    const int j = job - c.Hkv;
-    quantize_store(x, c.v + page * c.stride_page + j * c.stride_head + row * c.stride_tok,
-                   c.v_scale + page * c.sstride_page + j * c.sstride_head + row, lane);
+      for (int i = 0; i < kKeepRows; ++i) {  // independent loads: all in flight together
+        const int t = s0 + wid + i * nw;
+        keep[i] = t < s1 ? *reinterpret_cast<const uint2*>(kcol + t * k_sn) : make_uint2(0u, 0u);
+      }
+#pragma unroll
+      for (int i = 0; i < kKeepRows; ++i) {
+        float x[4];
+        unpack4(keep[i], x);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) m[j] = fmaxf(m[j], fabsf(x[j]));
+      }
+      for (int t = s0 + wid + kKeepRows * nw; t < s1; t += nw) {  // chunks beyond kKeepRows * 128 rows
+        float x[4];
+        unpack4(*reinterpret_cast<const uint2*>(kcol + t * k_sn), x);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) m[j] = fmaxf(m[j], fabsf(x[j]));
+      }
+      *reinterpret_cast<float4*>(&part[warp][4 * lane]) = make_float4(m[0], m[1], m[2], m[3]);
+      __syncthreads();
+      if (threadIdx.x < kD) {
+        float v = 0.f;
+#pragma unroll
+        for (int w = 0; w < kFirstWarps; ++w) v = fmaxf(v, part[w][threadIdx.x]);
+        cta_max[threadIdx.x] = v;
+      }
+      asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+      if (threadIdx.x < kD) {
+        float v = 1e-3f;
+        const uint32_t mine = (uint32_t)__cvta_generic_to_shared(&cta_max[threadIdx.x]);
+#pragma unroll
+        for (int p = 0; p < kFirstCtas; ++p) {
+          uint32_t remote;
+          float pv;
+          asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(mine), "r"(p));
+          asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(pv) : "r"(remote) : "memory");
+          v = fmaxf(v, pv);
+        }
+        cal_s[threadIdx.x] = v;
+      }
+      // nobody may overwrite cta_max (next entry) or leave while a peer still reads it
+      asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+      __syncthreads();
+      const int page0 = c.table[(long long)b * c.table_stride];
+      const bool page0_ok = page0 >= 0 && page0 < c.num_pages;
+      if (!page0_ok && crank == 0 && threadIdx.x == 0 && status) atomicOr(status, B200KV_S_BAD_PAGE);
+      if (crank == 0 && threadIdx.x < kD && page0_ok)
+        c.k_cal[page0 * c.cstride_page + h * c.cstride_head + threadIdx.x] = cal_s[threadIdx.x];
+      float cal[4];
+      load4_f32(cal_s, lane, cal);
+      auto quantize_row = [&](int t, uint2 raw) {
+        float x[4];
+        unpack4(raw, x);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) x[j] = __fdiv_rn(x[j], cal[j]);
+        const int pos = t - s0;  // first chunk: the entry's cached length is zero
+        const int page = page_of(c, b, pos, status, lane);
+        if (page < 0) return;
+        const int prow = pos % c.page_size;
+        quantize_store(x, c.k + page * c.stride_page + h * c.stride_head + prow * c.stride_tok,
+                       c.k_scale + page * c.sstride_page + h * c.sstride_head + prow, lane);
+      };
+#pragma unroll
+      for (int i = 0; i < kKeepRows; ++i) {
+        const int t = s0 + wid + i * nw;
+        if (t < s1) quantize_row(t, keep[i]);
+      }
+      for (int t = s0 + wid + kKeepRows * nw; t < s1; t += nw) quantize_row(t, *reinterpret_cast<const uint2*>(kcol + t * k_sn));
+      __syncthreads();  // part / cal_s are reused by the next entry
+    }
   }
 }
 
@@ -413,6 +610,28 @@ extern "C" int b200kv_norm_rope_prefill(const void* q, int64_t q_sn, int64_t q_s
   return launch_status();
 }
 
+// The first-chunk kernel: a cluster of kFirstCtas CTAs per (kv head, entry lane), chained like the others.
+static cudaError_t launch_first_chunk(const uint16_t* k, long long k_sn, long long k_sh, const CacheView& view,
+                                      const int32_t* cu, int num_entries, const int32_t* cached_lens,
+                                      const int32_t* num_decoding, int N, int32_t* status, cudaStream_t s) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(view.Hkv, kFirstLanes, kFirstCtas);
+  cfg.blockDim = dim3(kFirstWarps * 32);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = kFirstCtas;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = chained_launch_enabled() ? 2 : 1;
+  return cudaLaunchKernelEx(&cfg, first_chunk_k_kernel, k, k_sn, k_sh, view, cu, num_entries, cached_lens, num_decoding, N,
+                            status);
+}
+
 extern "C" int b200kv_quantize_prefill(const void* k, int64_t k_sn, int64_t k_sh, const void* v, int64_t v_sn,
                                        int64_t v_sh, const int32_t* cu_seqlens, int32_t num_entries,
                                        const b200kv_cache* cache, const b200kv_table* table, const int32_t* cached_lens,
@@ -425,15 +644,54 @@ extern "C" int b200kv_quantize_prefill(const void* k, int64_t k_sn, int64_t k_sh
   if (N < 0 || num_entries < 0) return B200KV_E_SHAPE;
   if (!aligned(k, 8) || !aligned(v, 8) || !stride_ok4(k_sn) || !stride_ok4(k_sh) || !stride_ok4(v_sn) || !stride_ok4(v_sh))
     return B200KV_E_ALIGN;
-  if (N == 0 || num_entries == 0) return B200KV_OK;
   const int Hkv = cache->num_kv_heads;
   CacheView view = make_view(cache, table);
   cudaStream_t s = (cudaStream_t)stream;
-  launch_chained(calibrate_kernel, dim3(num_entries, Hkv), dim3(kCalibGroups * 32), 0, s, (const uint16_t*)k, k_sn, k_sh, view,
-                 cu_seqlens, cached_lens, num_decoding, N, status);
-  launch_chained(quantize_prefill_kernel, dim3(N, (2 * Hkv + kWarpsPerBlock - 1) / kWarpsPerBlock), dim3(kWarpsPerBlock * 32), 0, s,
-      (const uint16_t*)k, k_sn, k_sh, (const uint16_t*)v, v_sn, v_sh, view, cu_seqlens, num_entries, cached_lens,
-      num_decoding, status);
+  launch_chained(prefill_rows_kernel<false>, dim3(N, (2 * Hkv + kWarpsPerBlock - 1) / kWarpsPerBlock), dim3(kWarpsPerBlock * 32), 0, s,
+                 (const uint16_t*)nullptr, 0LL, 0LL, (const uint16_t*)k, (long long)k_sn, (long long)k_sh, (const uint16_t*)v,
+                 (long long)v_sn, (long long)v_sh, (const uint16_t*)nullptr, (const uint16_t*)nullptr, (const uint16_t*)nullptr,
+                 0LL, (const uint16_t*)nullptr, 0LL, (uint16_t*)nullptr, 0LL, 0LL, (uint16_t*)nullptr, 0LL, 0LL, view,
+                 cu_seqlens, (int)num_entries, cached_lens, num_decoding, 0, 0.f, status);
+  if (cudaGetLastError() != cudaSuccess) return B200KV_E_LAUNCH;
+  if (launch_first_chunk((const uint16_t*)k, k_sn, k_sh, view, cu_seqlens, num_entries, cached_lens, num_decoding, N, status,
+                         s) != cudaSuccess)
+    return B200KV_E_LAUNCH;
+  return launch_status();
+}
+
+extern "C" int b200kv_write_prefill(const void* q, int64_t q_sn, int64_t q_sh, const void* k, int64_t k_sn, int64_t k_sh,
+                                    const void* v, int64_t v_sn, int64_t v_sh, const void* qw, const void* kw,
+                                    const void* cosp, int64_t cos_sn, const void* sinp, int64_t sin_sn,
+                                    const int32_t* cu_seqlens, int32_t num_entries, const b200kv_cache* cache,
+                                    const b200kv_table* table, const int32_t* cached_lens, const int32_t* num_decoding,
+                                    void* q_out, int64_t qo_sn, int64_t qo_sh, void* k_out, int64_t ko_sn, int64_t ko_sh,
+                                    int32_t N, int32_t Hq, float eps, int32_t* status, void* stream) {
+  if (N == 0) return B200KV_OK;
+  if (!q || !k || !v || !qw || !kw || !cosp || !sinp || !cu_seqlens || !cached_lens || !num_decoding || !q_out || !k_out)
+    return B200KV_E_NULL;
+  int rc = check_cache(cache, table);
+  if (rc) return rc;
+  const int Hkv = cache->num_kv_heads;
+  if (N < 0 || num_entries < 1 || Hq < 1 || Hq % Hkv) return B200KV_E_SHAPE;
+  if (!aligned(q, 8) || !aligned(k, 8) || !aligned(v, 8) || !aligned(qw, 8) || !aligned(kw, 8) || !aligned(cosp, 8) ||
+      !aligned(sinp, 8) || !aligned(q_out, 8) || !aligned(k_out, 8))
+    return B200KV_E_ALIGN;
+  if (!stride_ok4(q_sn) || !stride_ok4(q_sh) || !stride_ok4(k_sn) || !stride_ok4(k_sh) || !stride_ok4(v_sn) ||
+      !stride_ok4(v_sh) || !stride_ok4(cos_sn) || !stride_ok4(sin_sn) || !stride_ok4(qo_sn) || !stride_ok4(qo_sh) ||
+      !stride_ok4(ko_sn) || !stride_ok4(ko_sh))
+    return B200KV_E_ALIGN;
+  CacheView view = make_view(cache, table);
+  cudaStream_t s = (cudaStream_t)stream;
+  launch_chained(prefill_rows_kernel<true>, dim3(N, (Hq + 2 * Hkv + kWarpsPerBlock - 1) / kWarpsPerBlock),
+                 dim3(kWarpsPerBlock * 32), 0, s, (const uint16_t*)q, (long long)q_sn, (long long)q_sh, (const uint16_t*)k,
+                 (long long)k_sn, (long long)k_sh, (const uint16_t*)v, (long long)v_sn, (long long)v_sh, (const uint16_t*)qw,
+                 (const uint16_t*)kw, (const uint16_t*)cosp, (long long)cos_sn, (const uint16_t*)sinp, (long long)sin_sn,
+                 (uint16_t*)q_out, (long long)qo_sn, (long long)qo_sh, (uint16_t*)k_out, (long long)ko_sn, (long long)ko_sh, view,
+                 cu_seqlens, (int)num_entries, cached_lens, num_decoding, (int)Hq, eps, status);
+  if (cudaGetLastError() != cudaSuccess) return B200KV_E_LAUNCH;
+  if (launch_first_chunk((const uint16_t*)k_out, ko_sn, ko_sh, view, cu_seqlens, num_entries, cached_lens, num_decoding, N,
+                         status, s) != cudaSuccess)
+    return B200KV_E_LAUNCH;
   return launch_status();
 }
 

@@ -363,6 +363,44 @@ def quantize_kv_prefill(
 
 
 @_ranged
+def write_prefill(
+    q: torch.Tensor,  # bf16 [N, Hq, D], raw projections, all sequences packed along N
+    k: torch.Tensor,  # bf16 [N, Hkv, D]
+    v: torch.Tensor,
+    q_norm_weight: torch.Tensor,
+    k_norm_weight: torch.Tensor,
+    cos: torch.Tensor,  # [N, 1, D // 2]
+    sin: torch.Tensor,
+    cu_seqlens: torch.Tensor,  # int32 [B + 1]
+    slot_ids: torch.Tensor,
+    cached_lens: torch.Tensor,
+    num_decoding: torch.Tensor,
+    cache: LayerKVCache,
+    eps: float,
+) -> tuple[torch.Tensor, torch.Tensor]:
+    """fused_norm_rope_prefill followed by quantize_kv_prefill as one call (not a reference function; the
+    reference's caller makes the two calls, architecture.py:133-150): returns the same (q_p, k_p) and leaves the
+    same bytes in the cache."""
+    _require_cuda(q, k, v, cache.k)
+    lib = _lib.load()
+    N, Hq, D = q.shape
+    Hkv = k.shape[1]
+    assert q.stride(-1) == 1 and k.stride(-1) == 1 and v.stride(-1) == 1
+    assert cos.stride(-1) == 1 and sin.stride(-1) == 1
+    q_out = torch.empty(N, Hq, D, device=q.device, dtype=q.dtype)
+    k_out = torch.empty(N, Hkv, D, device=k.device, dtype=k.dtype)
+    cs, ts = _cache_struct(cache), _table_struct(slot_ids)
+    rc = lib.b200kv_write_prefill(
+        q.data_ptr(), q.stride(0), q.stride(1), k.data_ptr(), k.stride(0), k.stride(1), v.data_ptr(), v.stride(0),
+        v.stride(1), q_norm_weight.data_ptr(), k_norm_weight.data_ptr(), cos.data_ptr(), _row_stride(cos), sin.data_ptr(),
+        _row_stride(sin), _i32(cu_seqlens), cu_seqlens.shape[0] - 1, ctypes.byref(cs), ctypes.byref(ts), _i32(cached_lens),
+        _i32(num_decoding), q_out.data_ptr(), q_out.stride(0), q_out.stride(1), k_out.data_ptr(), k_out.stride(0),
+        k_out.stride(1), N, Hq, float(eps), status_word(q.device).data_ptr(), _stream())
+    _lib.check(rc, "write_prefill")
+    return q_out, k_out
+
+
+@_ranged
 def dequantize_kv_prefix(
     cache: LayerKVCache,
     cu_cached: torch.Tensor,  # int32 [B + 1]

@@ -33,6 +33,7 @@ HIDDEN, FFN, VOCAB, LAYERS = 2048, 6144, 151936, 28
 HQ, HKV, D = 16, 8, 128
 EPS = 1e-6
 ROPE_BASE = 1e6
+FUSED_PREFILL_WRITE = True  # attention_ops: kernels.write_prefill instead of fused_norm_rope_prefill + quantize_kv_prefill
 
 
 @dataclass
@@ -146,8 +147,11 @@ def attention_ops(q, k, v, qw, kw, cos, sin, cache, inp: StepInputs | None, cach
     if inp is None:
         q_d = K.fused_rope_kv_decode(q, k, v, qw, kw, cos, sin, slot_ids, cache, cached_lens, num_decoding, EPS)
         return K.decode_attention(q_d, cache, cached_lens, slot_ids, num_decoding, scale, plan=plan)
-    q_p, k_p = K.fused_norm_rope_prefill(q, k, qw, kw, cos, sin, EPS)
-    K.quantize_kv_prefill(k_p, v, inp.cu_seqlens, slot_ids, cached_lens, num_decoding, cache)
+    if FUSED_PREFILL_WRITE:  # norm + rope + quantize-on-write of the chunk rows in one call
+        q_p, k_p = K.write_prefill(q, k, v, qw, kw, cos, sin, inp.cu_seqlens, slot_ids, cached_lens, num_decoding, cache, EPS)
+    else:  # the two calls the reference's caller makes
+        q_p, k_p = K.fused_norm_rope_prefill(q, k, qw, kw, cos, sin, EPS)
+        K.quantize_kv_prefill(k_p, v, inp.cu_seqlens, slot_ids, cached_lens, num_decoding, cache)
     K.dequantize_kv_prefix(cache, prefix.cu_cached, slot_ids, prefix.k, prefix.v)
     out = K.prefill_attention(q_p, k_p, v, inp.seq_ids, inp.cu_seqlens, inp.tile_start,
                               prefix.k, prefix.v, prefix.cu_cached, inp.block_m)

@@ -107,11 +107,14 @@ def test_write_decode_paged_random(K, T, calibrated):
     assert K.check_status() == 0
 
 
-@pytest.mark.parametrize("T", [64, 1024])
+@pytest.mark.parametrize("fused", [False, True])
+@pytest.mark.parametrize("T", [64, 1024, 1500])
 @pytest.mark.parametrize("first_chunk", [True, False])
-def test_prefill_write_paged_random(K, T, first_chunk):
+def test_prefill_write_paged_random(K, T, first_chunk, fused):
     """One T-token prefill chunk behind two decoding entries, paged cache: bf16 q/k outputs,
-    calibration, codes and scales equal the oracle; then the dequantized prefix does too."""
+    calibration, codes and scales equal the oracle; then the dequantized prefix does too.  fused = the single
+    write_prefill call instead of fused_norm_rope_prefill + quantize_kv_prefill.  T = 1500: more rows than the
+    first-chunk kernel keeps in registers."""
     rng = np.random.default_rng(2000 + T + int(first_chunk))
     P = 16
     prior = 0 if first_chunk else 48
@@ -136,11 +139,17 @@ def test_prefill_write_paged_random(K, T, first_chunk):
     O.quantize_prefill(want_kp, v, cu, table, cached, 2, cache)
 
     tq, tk, tv = split_views(H.bf16_tensor(qkv))
-    got_qp, got_kp = K.fused_norm_rope_prefill(tq, tk, H.bf16_tensor(qw), H.bf16_tensor(kw), H.bf16_tensor(cos)[:, None, :],
-                                               H.bf16_tensor(sin)[:, None, :], 1e-6)
+    if fused:
+        got_qp, got_kp = K.write_prefill(tq, tk, tv, H.bf16_tensor(qw), H.bf16_tensor(kw), H.bf16_tensor(cos)[:, None, :],
+                                         H.bf16_tensor(sin)[:, None, :], H.i32(cu), H.i32(table), H.i32(cached), H.i32([2]),
+                                         dev_cache, 1e-6)
+    else:
+        got_qp, got_kp = K.fused_norm_rope_prefill(tq, tk, H.bf16_tensor(qw), H.bf16_tensor(kw), H.bf16_tensor(cos)[:, None, :],
+                                                   H.bf16_tensor(sin)[:, None, :], 1e-6)
     assert np.array_equal(H.to_bits(got_qp), O.bf16_bits(want_qp))
     assert np.array_equal(H.to_bits(got_kp), O.bf16_bits(want_kp))
-    K.quantize_kv_prefill(got_kp, tv, H.i32(cu), H.i32(table), H.i32(cached), H.i32([2]), dev_cache)
+    if not fused:
+        K.quantize_kv_prefill(got_kp, tv, H.i32(cu), H.i32(table), H.i32(cached), H.i32([2]), dev_cache)
     H.assert_cache_equal(H.cache_to_numpy(dev_cache), cache, f"T={T} first={first_chunk} ")
 
     # dequantize what is now cached for the prefilling entry (prior + T tokens)
