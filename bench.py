@@ -1209,6 +1209,63 @@ def run_vs_triton(args):
         print(json.dumps(line), flush=True)
 
 
+def run_linear(args):
+    """--linear: the weight-streaming matmul of the decode step (kernels.skinny_matmul, tcgen05) beside cuBLAS
+    (F.linear) at the five weight shapes of the Qwen3-1.7B-shaped decoder and M = 1, 8, 64 rows.  Each case is a
+    CUDA graph of R calls on R distinct weight copies (R chosen so that the graph streams more than 400 MB, above the
+    126 MB L2), median of `steps` replays.  GB/s = weight bytes / time; fractions are of the measured copy peak."""
+    import torch
+    import torch.nn.functional as F
+
+    from inference_engine_b200 import kernels as K
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    peak, peak_kind = peaks()
+    gen = torch.Generator(device=dev).manual_seed(6)
+    shapes = {"qkv": (4096, 2048), "o": (2048, 2048), "gate_up": (12288, 2048), "down": (2048, 6144), "lm_head": (151936, 2048)}
+    for name, (N, Kd) in shapes.items():
+        wbytes = N * Kd * 2
+        R = int(min(64, max(2, -(-400_000_000 // wbytes))))
+        ws = [(torch.randn(N, Kd, generator=gen, device=dev) * 0.02).to(torch.bfloat16) for _ in range(R)]
+        for M in (1, 8, 64):
+            x = torch.randn(M, Kd, generator=gen, device=dev).to(torch.bfloat16)
+
+            def graph_us(fn):
+                fn()
+                torch.cuda.synchronize()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    fn()
+                for _ in range(3):
+                    g.replay()
+                torch.cuda.synchronize()
+                ts = []
+                for _ in range(args.steps):
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record()
+                    g.replay()
+                    e1.record()
+                    torch.cuda.synchronize()
+                    ts.append(e0.elapsed_time(e1) * 1e3 / R)
+                return statistics.median(ts)
+
+            line = {"case": "linear", "weight": name, "N": N, "K": Kd, "M": M, "weights_in_graph": R,
+                    "cublas_us": round(graph_us(lambda: [F.linear(x, w) for w in ws]), 2)}
+            best = None
+            for s in K.skinny_supported(M, N, Kd):
+                us = graph_us(lambda: [K.skinny_matmul(x, w, s) for w in ws])
+                line[f"skinny_s{s}_us"] = round(us, 2)
+                if best is None or us < best[0]:
+                    best = (us, s)
+            line.update({"best_splits": best[1], "best_us": round(best[0], 2), "gbs": round(wbytes / best[0] / 1e3, 1),
+                         "frac_of_measured": round(wbytes / best[0] / 1e3 / peak, 4),
+                         "speedup_vs_cublas": round(line["cublas_us"] / best[0], 3), "status": K.check_status(dev)})
+            print(json.dumps(line), flush=True)
+        del ws
+        torch.cuda.empty_cache()
+
+
 def run_phases(args):
     """--phases: where the time of one decode_attention launch goes, from the instrumented build of the library
     (libb200kv_stamps.so: the same sources with -DB200KV_STAMPS; every warp records %globaltimer at kernel entry and
@@ -1313,7 +1370,7 @@ def run_phases(args):
                                            "pieces": mm[2]}
             print(json.dumps(line), flush=True)
             if args.dump and B == 64:
-                np.save(f"{args.dump}_B{B}_ctx{n}_{'planned' if planned else 'plain'}.npy", np.stack([r[:1776] for r in raw if len(r) >= 1776]))
+                np.save(f"{args.dump}_B{B}_ctx{n}_{'planned' if planned else 'plain'}.npy", np.stack([r[: min(len(x) for x in raw)] for r in raw]))
         del caches, tables
         torch.cuda.empty_cache()
 
@@ -1399,6 +1456,28 @@ def run_write(args):
             print(json.dumps({"case": "fused_norm_rope_prefill + quantize_kv_prefill (first chunk)", "T": T,
                               "us_per_call": round(us, 2), "gbs": round(T * WRITE_BYTES_PER_TOKEN / us / 1e3, 1),
                               "kernels_per_call": 3}), flush=True)
+
+            def fused_flavour():
+                for c in pcaches:
+                    K.write_prefill(q, k, v, qw, kw, cos, sin, cu, tab1, zero, zero, c, 1e-6)
+
+            us = timed(fused_flavour)
+            print(json.dumps({"case": "write_prefill (the two calls as one, first chunk)", "T": T,
+                              "us_per_call": round(us, 2), "gbs": round(T * WRITE_BYTES_PER_TOKEN / us / 1e3, 1),
+                              "kernels_per_call": 2}), flush=True)
+            # a later chunk of the same prompt: the calibration exists, only the row kernel has work
+            later = torch.tensor([T], dtype=torch.int32, device=dev)
+            tab2 = torch.arange(1, 1 + (2 * T + PAGE - 1) // PAGE, dtype=torch.int32, device=dev)[None, :].contiguous()
+            lcaches = [K.make_layer_cache(2 + (2 * T + PAGE - 1) // PAGE, HKV, PAGE, D, device=dev) for _ in range(reps)]
+
+            def fused_later():
+                for c in lcaches:
+                    K.write_prefill(q, k, v, qw, kw, cos, sin, cu, tab2, later, zero, c, 1e-6)
+
+            us = timed(fused_later)
+            print(json.dumps({"case": "write_prefill (a later chunk: calibration loaded)", "T": T,
+                              "us_per_call": round(us, 2), "gbs": round(T * WRITE_BYTES_PER_TOKEN / us / 1e3, 1),
+                              "kernels_per_call": 2}), flush=True)
 
 
 def run_sweep(args):
@@ -1500,10 +1579,13 @@ def main():
     ap.add_argument("--reference", default=None, help="--vs-triton: checkout of the reference (or its qwen3-1.7b directory)")
     ap.add_argument("--all-cells", action="store_true", help="--vs-triton: also the five cells the sweep configuration drops")
     ap.add_argument("--dump", default=None, help="--phases: prefix of .npy files for the raw per-warp words")
+    ap.add_argument("--linear", action="store_true", help="weight-streaming matmul for few rows beside cuBLAS")
     ap.add_argument("--phases", action="store_true", help="per-phase and per-SM times of the decode kernel (instrumented build)")
     args = ap.parse_args()
     if args.phases:
         run_phases(args)
+    elif args.linear:
+        run_linear(args)
     elif args.vs_triton:
         run_vs_triton(args)
     elif args.sweep:

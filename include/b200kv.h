@@ -215,6 +215,18 @@ int b200kv_sample(const void* logits, int64_t stride, int32_t elem_bytes, int64_
                   void* workspace, size_t workspace_bytes, int64_t* out, int64_t out_stride,
                   int32_t B, int32_t V, void* stream);
 
+/* Replaces skinny_matmul (kernels.py:1373-1455), the matmul `linear` uses for the few rows of a decode step, where
+ * reading the weight once from HBM is the whole cost: y[M, N] = x[M, K] . w[N, K]^T, bf16 in, fp32 accumulate, bf16
+ * out; w in the layout of nn.Linear.weight.  M <= 64 (the reference's bound), N a multiple of 128, K a multiple of
+ * 64; x and w 16-byte aligned with row strides (ldx, ldw, elements) that are multiples of 8.  `splits` in
+ * {1, 2, 4, 8}: the CTAs of a cluster of that size share a block of 128 weight rows and split K (at most
+ * max(16, M rounded up to a power of two) / 2 and at most K / 64); the caller picks it so that (N / 128) * splits
+ * fills the SMs (b200kv_skinny_linear is what tune_linear times against cuBLAS per shape, as the reference does).
+ * The fp32 summation order differs from the reference's (as its own does between autotuned block sizes), so results
+ * agree to the last bf16 bit, not bit for bit. */
+int b200kv_skinny_linear(const void* x, int64_t ldx, const void* w, int64_t ldw, void* y, int64_t ldy,
+                         int32_t M, int32_t N, int32_t K, int32_t splits, int32_t* status, void* stream);
+
 /* Chained launches (off by default).  While enabled, every kernel of this library except decode attention
  * (which is chained per call, through bit 2 of its `variant`) and b200kv_decode_plan (never chained) is launched
  * with programmatic stream serialization: it may be brought up while the kernel launched just before it on

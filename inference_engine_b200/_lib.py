@@ -65,6 +65,8 @@ SIGNATURES = {
     "b200kv_sample_workspace_bytes": (c_size_t, [c_int32, c_int32]),
     "b200kv_sample": (c_int32, [c_void_p, c_int64, c_int32, c_void_p, c_float, c_void_p, c_size_t, c_void_p, c_int64,
                                 c_int32, c_int32, c_void_p]),
+    "b200kv_skinny_linear": (c_int32, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int32, c_int32, c_int32,
+                                       c_int32, c_void_p, c_void_p]),
     "b200kv_set_chained_launch": (None, [c_int32]),
     "b200kv_get_chained_launch": (c_int32, []),
     "b200kv_decode_attn_workspace_bytes": (c_size_t, [c_int32, c_int32, c_int32, c_int32, c_int32]),

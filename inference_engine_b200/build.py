@@ -30,6 +30,7 @@ UNITS = {
     "prefill_attn_tc5.cu": [],
     "block_ops.cu": [],
     "sampler.cu": ["-fmad=false"],
+    "skinny_linear_tc5.cu": [],
 }
 # The same library with per-warp timestamps compiled into the decode-attention kernel (bench.py --phases);
 # never loaded by the product path.

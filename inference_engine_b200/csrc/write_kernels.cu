@@ -412,11 +412,14 @@ first_chunk_k_kernel(const uint16_t* __restrict__ k, long long k_sn, long long k
       const int s0 = cu[b], s1 = min(cu[b + 1], N);
       const uint16_t* kcol = k + h * k_sh + 4 * lane;
       uint2 keep[kKeepRows];
+      int keep_page[kKeepRows];  // table entries of the kept rows, fetched in the same round as the rows
       float m[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int i = 0; i < kKeepRows; ++i) {  // independent loads: all in flight together
         const int t = s0 + wid + i * nw;
         keep[i] = t < s1 ? *reinterpret_cast<const uint2*>(kcol + t * k_sn) : make_uint2(0u, 0u);
+        const int slot = (t - s0) / c.page_size;
+        keep_page[i] = (t < s1 && slot < c.max_pages) ? c.table[(long long)b * c.table_stride + slot] : -2;
       }
 #pragma unroll
       for (int i = 0; i < kKeepRows; ++i) {
@@ -463,14 +466,16 @@ first_chunk_k_kernel(const uint16_t* __restrict__ k, long long k_sn, long long k
         c.k_cal[page0 * c.cstride_page + h * c.cstride_head + threadIdx.x] = cal_s[threadIdx.x];
       float cal[4];
       load4_f32(cal_s, lane, cal);
-      auto quantize_row = [&](int t, uint2 raw) {
+      auto quantize_row = [&](int t, uint2 raw, int page) {
         float x[4];
         unpack4(raw, x);
 #pragma unroll
         for (int j = 0; j < 4; ++j) x[j] = __fdiv_rn(x[j], cal[j]);
         const int pos = t - s0;  // first chunk: the entry's cached length is zero
-        const int page = page_of(c, b, pos, status, lane);
-        if (page < 0) return;
+        if (page < 0 || page >= c.num_pages) {
+          if (lane == 0 && status) atomicOr(status, page == -2 ? B200KV_S_BAD_POSITION : B200KV_S_BAD_PAGE);
+          return;
+        }
         const int prow = pos % c.page_size;
         quantize_store(x, c.k + page * c.stride_page + h * c.stride_head + prow * c.stride_tok,
                        c.k_scale + page * c.sstride_page + h * c.sstride_head + prow, lane);
@@ -478,9 +483,13 @@ first_chunk_k_kernel(const uint16_t* __restrict__ k, long long k_sn, long long k
 #pragma unroll
       for (int i = 0; i < kKeepRows; ++i) {
         const int t = s0 + wid + i * nw;
-        if (t < s1) quantize_row(t, keep[i]);
+        if (t < s1) quantize_row(t, keep[i], keep_page[i]);
       }
-      for (int t = s0 + wid + kKeepRows * nw; t < s1; t += nw) quantize_row(t, *reinterpret_cast<const uint2*>(kcol + t * k_sn));
+      for (int t = s0 + wid + kKeepRows * nw; t < s1; t += nw) {
+        const int slot = (t - s0) / c.page_size;
+        quantize_row(t, *reinterpret_cast<const uint2*>(kcol + t * k_sn),
+                     slot < c.max_pages ? c.table[(long long)b * c.table_stride + slot] : -2);
+      }
       __syncthreads();  // part / cal_s are reused by the next entry
     }
   }

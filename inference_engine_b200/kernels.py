@@ -502,9 +502,82 @@ def sample(logits: torch.Tensor, tau: float, seed: torch.Tensor) -> torch.Tensor
     return out
 
 
+def skinny_matmul(x: torch.Tensor, weight: torch.Tensor, splits: int = 1) -> torch.Tensor:
+    """kernels.py:1430-1455: [M, K] bf16 @ [N, K] bf16 .T -> [M, N] bf16 for M <= 64, the weight read once from HBM
+    (tcgen05 kernel behind b200kv_skinny_linear).  `splits` = CTAs sharing a block of 128 weight rows (1, 2, 4, 8)."""
+    _require_cuda(x, weight)
+    M, K = x.shape
+    N = weight.shape[0]
+    assert x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
+    assert x.stride(-1) == 1 and weight.stride(-1) == 1
+    assert M <= 64, "many rows are compute bound: cuBLAS is the tool there"
+    y = torch.empty(M, N, device=x.device, dtype=torch.bfloat16)
+    rc = _lib.load().b200kv_skinny_linear(x.data_ptr(), x.stride(0), weight.data_ptr(), weight.stride(0), y.data_ptr(),
+                                          y.stride(0), M, N, K, int(splits), status_word(x.device).data_ptr(), _stream())
+    _lib.check(rc, "skinny_matmul")
+    return y
+
+
+# (N, K, M) -> cluster size with which skinny_matmul beat cuBLAS for that weight shape and row count (0: cuBLAS won).
+# Filled by tune_linear before graph capture; anything it never measured uses cuBLAS (kernels.py:1458-1470).
+use_skinny: dict[tuple[int, int, int], int] = {}
+
+
+def skinny_supported(M: int, N: int, K: int) -> list[int]:
+    """The cluster sizes b200kv_skinny_linear accepts for this shape ([] = not at all)."""
+    if M < 1 or M > 64 or N % 128 or K % 64 or K < 64:
+        return []
+    T = 16 if M <= 16 else (32 if M <= 32 else 64)
+    return [s for s in (1, 2, 4, 8) if s <= T // 2 and s <= K // 64]
+
+
 def linear(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:  # kernels.py:1465
+    """[M, K] @ [N, K].T -> [M, N] with whichever of skinny_matmul and cuBLAS (F.linear) tune_linear measured faster
+    for this (weight shape, row count); unmeasured shapes go to cuBLAS."""
+    if x.dim() == 2 and x.stride(-1) == 1 and weight.stride(-1) == 1:
+        s = use_skinny.get((weight.shape[0], weight.shape[1], x.shape[0]), 0)
+        if s:
+            return skinny_matmul(x, weight, s)
     return F.linear(x, weight)
 
 
-def tune_linear(weights, row_counts) -> None:  # kernels.py:1473: nothing to tune for F.linear
-    return None
+def tune_linear(weights, rows, min_gain: float = 0.02) -> None:
+    """kernels.py:1473-1485: time skinny_matmul (every cluster size the shape allows) against cuBLAS for each weight
+    shape at each row count <= 64 and keep the faster; skinny_matmul has to win by `min_gain` to be picked.  L2 is
+    flushed before every timed call, as in the model, where each layer's weights come from HBM."""
+    if not weights:
+        return
+    dev = weights[0].device
+    flush = torch.empty(192 << 20, dtype=torch.uint8, device=dev)
+
+    def time_us(fn, reps: int = 5) -> float:
+        fn()
+        ts = []
+        for _ in range(reps):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            e1.synchronize()
+            ts.append(e0.elapsed_time(e1) * 1e3)
+        return sorted(ts)[len(ts) // 2]
+
+    for weight in weights:
+        N, K = weight.shape
+        for M in rows:
+            if M > 64 or (N, K, M) in use_skinny or weight.dtype != torch.bfloat16 or weight.stride(-1) != 1:
+                continue
+            options = skinny_supported(M, N, K)
+            if not options:
+                use_skinny[(N, K, M)] = 0
+                continue
+            x = torch.randn(M, K, device=dev, dtype=weight.dtype)
+            cublas = time_us(lambda: F.linear(x, weight))
+            best, best_s = cublas * (1.0 - min_gain), 0
+            for s in options:
+                t = time_us(lambda: skinny_matmul(x, weight, s))
+                if t < best:
+                    best, best_s = t, s
+            use_skinny[(N, K, M)] = best_s
+    check_status(dev)

@@ -361,6 +361,16 @@ def rope_tables(positions, D: int = 128, base: float = 1e6):
     return cos, sin
 
 
+# --------------------------------------------------------------------------- weight-streaming matmul
+def linear(x, weight) -> np.ndarray:
+    """skinny_matmul / linear, kernels.py:1386-1470: y = x @ weight.T for bf16 x [M, K] and weight [N, K] (the layout
+    of nn.Linear.weight), products and sums in fp32, result rounded to bf16.  The order of the fp32 sums is not part
+    of the contract (the reference's depends on its autotuned BLOCK_K), so parity is "within one bf16 step"."""
+    x = np.asarray(x, np.float32)
+    w = np.asarray(weight, np.float32)
+    return bf16_round((x.astype(np.float64) @ w.astype(np.float64).T).astype(np.float32))
+
+
 # --------------------------------------------------------------------------- decoder-block element-wise ops
 def silu_mul(gate_up) -> np.ndarray:
     """silu_mul, kernels.py:1178-1212: [N, 2D] bf16 -> [N, D]: bf16((gate * sigmoid(gate)) * up), all in fp32,
