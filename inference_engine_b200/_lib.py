@@ -74,6 +74,7 @@ SIGNATURES = {
                                      c_int64, c_int64, c_void_p, c_size_t, c_int32, c_int32, c_int32, c_int32, c_void_p,
                                      c_void_p]),
     "b200kv_decode_plan_bytes": (c_size_t, [c_int32]),
+    "b200kv_decode_attn_planned_workspace_bytes": (c_size_t, [c_int32, c_int32, c_int32, c_int32, c_int32]),
     "b200kv_decode_plan": (c_int32, [P_TABLE, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32, c_void_p, c_size_t,
                                      c_void_p]),
     "b200kv_decode_attn_planned": (c_int32, [c_void_p, c_int64, c_int64, P_CACHE, P_TABLE, c_void_p, c_void_p, c_float,

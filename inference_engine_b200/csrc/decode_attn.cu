@@ -48,9 +48,21 @@ static_assert((kStages & (kStages - 1)) == 0, "ring indices are masked");
 
 struct Partition {
   int U;        // total tiles over all (entry, head)
-  int per;      // tiles per worker
+  int per;      // tiles of a warp's static range
   int W;        // workers (warps in the grid)
+  // The pool (planned calls on large batches only; Us == U and n1 == n2 == 0 otherwise): the static ranges cover
+  // tiles [0, Us) = W * per exactly; tiles [Us, U) are cut into n1 pieces of P1 tiles followed by n2 pieces of P2
+  // tiles (the very last piece may be shorter), which the warps claim one at a time when their own range is done.
+  int Us, n1, P1, n2, P2;
+  __host__ __device__ __forceinline__ int pool_pieces() const { return n1 + n2; }
+  __host__ __device__ __forceinline__ int piece_start(int j) const { return j < n1 ? Us + j * P1 : Us + n1 * P1 + (j - n1) * P2; }
+  __host__ __device__ __forceinline__ int piece_of(int u) const {
+    const int r = u - Us;
+    return r < n1 * P1 ? r / P1 : n1 + (r - n1 * P1) / P2;
+  }
 };
+constexpr int kMaxPool = 8192;    // pieces a plan may hold
+constexpr int kPoolMinShare = 24; // a pool is only made when the even share of a warp is at least this many tiles
 
 // ------------------------------------------------------------------ small PTX wrappers
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -184,6 +196,31 @@ __host__ __device__ __forceinline__ Partition make_partition(int total_tiles_one
   const int min_tiles = (num_entries > 0 && total_tiles_one_head <= 32 * num_entries) ? 8 : 4;
   int per = (p.U + W - 1) / W;
   p.per = per > min_tiles ? per : min_tiles;
+  p.Us = p.U; p.n1 = 0; p.P1 = 1; p.n2 = 0; p.P2 = 1;
+  return p;
+}
+
+// The same with a pool: about a fifth of the tiles is held back from the static ranges.  Warps on fast SMs finish
+// their (equal) ranges early - the per-SM streaming rate differs by +-10 % with the SM's place on the chip, stably
+// from launch to launch - and then take pool pieces, larger ones first, small ones at the end so that the last
+// pieces finish close together.  Piece boundaries are a function of the batch alone, so the result does not depend
+// on which warp took which piece.
+__host__ __device__ __forceinline__ Partition make_pooled_partition(int total_tiles_one_head, int Hkv, int W, int num_entries) {
+  Partition p = make_partition(total_tiles_one_head, Hkv, W, num_entries);
+  if (p.U / W < kPoolMinShare) return p;
+  p.per = (int)(((long long)p.U * 4 / 5) / W);
+  p.Us = p.per * W;
+  const int pool = p.U - p.Us;
+  int P1 = 8, P2 = 4;
+  for (;;) {
+    const int t2 = ((pool * 2 / 5) / P2) * P2;  // the last two fifths of the pool in small pieces
+    p.n1 = (pool - t2) / P1;
+    const int rest = pool - p.n1 * P1;           // >= t2; everything behind the large pieces
+    p.n2 = (rest + P2 - 1) / P2;
+    if (p.n1 + p.n2 <= kMaxPool) break;
+    P1 *= 2; P2 *= 2;
+  }
+  p.P1 = P1; p.P2 = P2;
   return p;
 }
 
@@ -617,10 +654,12 @@ __device__ __forceinline__ void scalar_end(ScalarState& st, bool whole, uint16_t
 // ------------------------------------------------------------------ main kernel
 // Workspace: int32 prefix[B+1] (padded to 256 B; read by the separate reduction kernel) |
 // int32 arrivals[B*Hkv] (padded; zero on entry, left zero: counts the partials of each (entry, head)
-// when the reduction is fused into this kernel) | float ml[W][2][G][2] | float acc[W][2][G][128]
+// when the reduction is fused into this kernel) | pool claim counter (256 B) | float ml[R][2][G][2] |
+// float acc[R][2][G][128], R = ranges the call can have: the W warps, plus kMaxPool pool pieces for a planned call
 __host__ __device__ inline size_t ws_prefix_bytes(int B) { return (((size_t)(B + 1) * 4 + 255) / 256) * 256; }
 __host__ __device__ inline size_t ws_count_bytes(int B, int Hkv) { return (((size_t)B * Hkv * 4 + 255) / 256) * 256; }
-__host__ __device__ inline size_t ws_head_bytes(int B, int Hkv) { return ws_prefix_bytes(B) + ws_count_bytes(B, Hkv); }
+// ... followed by 256 bytes whose first word is the pool's claim counter (zero on entry, left zero)
+__host__ __device__ inline size_t ws_head_bytes(int B, int Hkv) { return ws_prefix_bytes(B) + ws_count_bytes(B, Hkv) + 256; }
 
 // The pieces of one (entry, head) that reached the workspace, in tile order.  Its flat tile range
 // [s0, e) is covered by warps w_first..w_last; CTAs c_lo..c_hi-1 lie entirely inside it, each of
@@ -630,23 +669,41 @@ __host__ __device__ inline size_t ws_head_bytes(int B, int Hkv) { return ws_pref
 // (entry, head) starts inside that warp's range.
 struct Pieces {
   int w_first, n_a, w_b, n_b, w_c, n, slot_first;
-  __device__ __forceinline__ Pieces(const Partition& part, int s0, int e) {
-    w_first = s0 / part.per;
-    const int w_last = (e - 1) / part.per;
-    const int span = kWarps * part.per;
-    const int c_lo = (s0 + span - 1) / span, c_hi = min(e, part.U) / span;
-    slot_first = s0 > w_first * part.per ? 1 : 0;
-    if (c_hi > c_lo) {
-      w_b = kWarps * c_lo; w_c = kWarps * c_hi;
-      n_a = w_b - w_first; n_b = c_hi - c_lo;
-      n = n_a + n_b + (w_last - w_c + 1);
-    } else {
-      w_b = w_c = w_first; n_a = 0; n_b = 0;
-      n = w_last - w_first + 1;
+  int n_static, j_first, pool_slot_first, W;  // pool pieces follow the static ones, in tile order
+  __device__ __forceinline__ Pieces(const Partition& part, int s0, int e_all) {
+    W = part.W;
+    n_static = 0; j_first = 0; pool_slot_first = 0;
+    w_first = 0; n_a = 0; w_b = 0; n_b = 0; w_c = 0; slot_first = 0;
+    const int e = min(e_all, part.Us);  // the part of the range the static ranges cover
+    if (s0 < e) {
+      w_first = s0 / part.per;
+      const int w_last = (e - 1) / part.per;
+      const int span = kWarps * part.per;
+      const int c_lo = (s0 + span - 1) / span, c_hi = e / span;
+      slot_first = s0 > w_first * part.per ? 1 : 0;
+      if (c_hi > c_lo) {
+        w_b = kWarps * c_lo; w_c = kWarps * c_hi;
+        n_a = w_b - w_first; n_b = c_hi - c_lo;
+        n_static = n_a + n_b + (w_last - w_c + 1);
+      } else {
+        w_b = w_c = w_first; n_a = 0; n_b = 0;
+        n_static = w_last - w_first + 1;
+      }
+    }
+    n = n_static;
+    if (e_all > part.Us && part.pool_pieces() > 0) {
+      const int p0 = max(s0, part.Us);
+      j_first = part.piece_of(p0);
+      pool_slot_first = p0 > part.piece_start(j_first) ? 1 : 0;
+      n += part.piece_of(e_all - 1) - j_first + 1;
     }
   }
-  // workspace slot index (2 * warp + slot) of piece k
+  // workspace slot index (2 * range + slot) of piece k; range = warp for a static range, W + j for pool piece j
   __device__ __forceinline__ int slot_of(int k) const {
+    if (k >= n_static) {
+      const int j = j_first + (k - n_static);
+      return 2 * (W + j) + (j == j_first ? pool_slot_first : 0);
+    }
     const int w = k < n_a ? w_first + k : (k < n_a + n_b ? w_b + kWarps * (k - n_a) : w_c + (k - n_a - n_b));
     return 2 * w + (w == w_first ? slot_first : 0);
   }
@@ -773,10 +830,11 @@ __host__ __device__ inline size_t ws_ml_bytes(int W, int G) { return (((size_t)W
 // before its first copies are in flight, instead of the length scan, a binary search and a dependent
 // page-table read in each of its CTAs in each layer.
 constexpr int kPlanMagic = 0x6b765031;  // "kvP1"
-constexpr int kPlanHeaderInts = 8;      // magic, B, Hkv, W, U, per, num_decoding, page_size
-constexpr int kPlanEntryInts = 16;      // b, h, tile, T, n, base, page[0..2], reserved
-constexpr int kPlanThreads = 1024;
-__host__ __device__ inline size_t plan_bytes(int W) { return ((size_t)kPlanHeaderInts + (size_t)W * kPlanEntryInts) * 4; }
+constexpr int kPlanHeaderInts = 16;     // magic, B, Hkv, W, U, per, num_decoding, page_size, Us, n1, P1, n2, P2, reserved
+constexpr int kPlanEntryInts = 16;      // b, h, tile, T, n, base, page[0..2], tiles of the range, reserved
+constexpr int kPlanThreads = 1024, kPlanCtas = 6;
+// header, one entry per warp of the grid, one entry per pool piece
+__host__ __device__ inline size_t plan_bytes(int W) { return ((size_t)kPlanHeaderInts + (size_t)(W + kMaxPool) * kPlanEntryInts) * 4; }
 
 __global__ void __launch_bounds__(kPlanThreads)
 decode_plan_kernel(const int32_t* __restrict__ cached_lens, const int32_t* __restrict__ num_decoding,
@@ -791,22 +849,35 @@ decode_plan_kernel(const int32_t* __restrict__ cached_lens, const int32_t* __res
   int nd;
   scan_tiles(cached_lens, B, num_decoding, chunk, chunk_prefix, lens_s, nullptr, nd);
   const Lens lens{cached_lens, lens_s, nd};
-  const Partition part = make_partition(chunk_prefix[kPlanThreads], Hkv, W, nd);
-  if (threadIdx.x == 0) {
+  const Partition part = make_pooled_partition(chunk_prefix[kPlanThreads], Hkv, W, nd);
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
     plan[0] = kPlanMagic; plan[1] = B; plan[2] = Hkv; plan[3] = W;
     plan[4] = part.U; plan[5] = part.per; plan[6] = nd; plan[7] = page_size;
+    plan[8] = part.Us; plan[9] = part.n1; plan[10] = part.P1; plan[11] = part.n2; plan[12] = part.P2;
+    plan[13] = plan[14] = plan[15] = 0;
   }
-  for (int w = threadIdx.x; w < W; w += kPlanThreads) {
-    int* e = plan + kPlanHeaderInts + (size_t)w * kPlanEntryInts;
-    const long long u_begin = (long long)w * part.per;
-    if (u_begin >= part.U) {
+  const int npool = part.pool_pieces();
+  // range r: warp r's static range, or pool piece r - W
+  for (int r = blockIdx.x * kPlanThreads + threadIdx.x; r < W + npool; r += gridDim.x * kPlanThreads) {
+    int* e = plan + kPlanHeaderInts + (size_t)r * kPlanEntryInts;
+    long long u_begin;
+    int left;
+    if (r < W) {
+      u_begin = (long long)r * part.per;
+      left = u_begin < part.Us ? min(part.per, part.Us - (int)u_begin) : 0;
+    } else {
+      u_begin = part.piece_start(r - W);
+      left = min(part.piece_start(r - W + 1), part.U) - (int)u_begin;
+    }
+    if (left <= 0) {
       e[0] = -1;
+      e[9] = 0;
       continue;
     }
     Cursor cur;
     cur.seek(chunk_prefix, kPlanThreads, chunk, lens, Hkv, page_size, (int)u_begin);
     e[0] = cur.b; e[1] = cur.h; e[2] = cur.tile; e[3] = cur.T; e[4] = cur.n; e[5] = cur.base;
-    int left = min(part.per, part.U - (int)u_begin);
+    e[9] = left;
     for (int i = 0; i < kStages - 1; ++i) {
       int page = -1;
       if (left > 0) {
@@ -847,7 +918,9 @@ decode_attn_kernel(const uint16_t* __restrict__ q, long long q_sb, long long q_s
   extern __shared__ __align__(128) uint8_t smem[];
   uint8_t* ring = smem;                                                       // kWarps * kStages * kTileBytes
   float* q_s = reinterpret_cast<float*>(ring + kWarps * kStages * kTileBytes);  // scalar variant: kWarps * (G*128 + G*16)
-  int* chunk_prefix = reinterpret_cast<int*>(q_s + (kScalar ? kWarps * (kMaxG * kD + kMaxG * kTile) : 0));
+  // where the four warps of a CTA park their pieces of one (entry, head) for the CTA-level sum: [kWarps][G*128 + G*2]
+  float* park = q_s + (kScalar ? kWarps * (kMaxG * kD + kMaxG * kTile) : 0);
+  int* chunk_prefix = reinterpret_cast<int*>(park + kWarps * (G * kD + G * 2));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int w = blockIdx.x * kWarps + warp;
 #ifdef B200KV_STAMPS
@@ -867,12 +940,12 @@ decode_attn_kernel(const uint16_t* __restrict__ q, long long q_sb, long long q_s
   Partition part;
   Cursor pc;  // producer position (runs kStages-1 tiles ahead of the consumer)
   int first_page = -1;  // planned: lane i < kStages-1 holds the page id of the warp's i-th tile
+  int rid = w;          // the range being processed: a warp's static range (its index) or pool piece j (W + j)
+  int ntiles = 0;       // tiles of that range
   if (plan != nullptr) {
-    // One round of independent loads: the warp's plan entry (lanes 0-15), the header (lanes 16-23),
+    // One round of independent loads: the warp's plan entry (lanes 0-15), the header (lanes 16-31),
     // num_decoding and this thread's share of the lengths.
-    int pe = 0;
-    if (lane < kPlanEntryInts) pe = __ldcg(plan + kPlanHeaderInts + (size_t)w * kPlanEntryInts + lane);
-    else if (lane < kPlanEntryInts + kPlanHeaderInts) pe = __ldcg(plan + (lane - kPlanEntryInts));
+    int pe = __ldcg(plan + (lane < kPlanEntryInts ? kPlanHeaderInts + (size_t)w * kPlanEntryInts + lane : lane - kPlanEntryInts));
     const int nd_raw = __ldcg(num_decoding);
     int cl[kSmemLens / (kWarps * 32)];
 #pragma unroll
@@ -887,12 +960,16 @@ decode_attn_kernel(const uint16_t* __restrict__ q, long long q_sb, long long q_s
       if (b < B) lens_s[b] = b < nd ? cl[i] + 1 : 0;
     }
     __syncthreads();
-    const bool hdr_ok = __shfl_sync(0xffffffffu, pe, 16) == kPlanMagic && __shfl_sync(0xffffffffu, pe, 17) == B &&
-                        __shfl_sync(0xffffffffu, pe, 18) == c.Hkv && __shfl_sync(0xffffffffu, pe, 19) == W &&
-                        __shfl_sync(0xffffffffu, pe, 22) == nd && __shfl_sync(0xffffffffu, pe, 23) == c.page_size;
-    part.U = __shfl_sync(0xffffffffu, pe, 20);
-    part.per = __shfl_sync(0xffffffffu, pe, 21);
-    part.W = W;
+    auto hdr = [&](int i) { return __shfl_sync(0xffffffffu, pe, kPlanEntryInts + i); };
+    const bool hdr_ok = hdr(0) == kPlanMagic && hdr(1) == B && hdr(2) == c.Hkv && hdr(3) == W && hdr(6) == nd &&
+                        hdr(7) == c.page_size;
+    part.U = hdr(4); part.per = hdr(5); part.W = W;
+    part.Us = hdr(8); part.n1 = hdr(9); part.P1 = hdr(10); part.n2 = hdr(11); part.P2 = hdr(12);
+    if (!hdr_ok || part.per < 1 || part.P1 < 1 || part.P2 < 1 || part.pool_pieces() > kMaxPool || part.Us > part.U) {
+      // not a plan of this batch on this grid: nothing is read or written through it
+      if (lane == 0 && status) atomicOr(status, B200KV_S_BAD_PLAN);
+      return;
+    }
     pc.b = __shfl_sync(0xffffffffu, pe, 0);
     pc.h = __shfl_sync(0xffffffffu, pe, 1);
     pc.tile = __shfl_sync(0xffffffffu, pe, 2);
@@ -900,14 +977,11 @@ decode_attn_kernel(const uint16_t* __restrict__ q, long long q_sb, long long q_s
     pc.n = __shfl_sync(0xffffffffu, pe, 4);
     pc.base = __shfl_sync(0xffffffffu, pe, 5);
     first_page = __shfl_sync(0xffffffffu, pe, 6 + (lane < kStages - 1 ? lane : 0));
-    if (!hdr_ok) {  // not a plan of this batch on this grid: nothing is read or written through it
-      if (lane == 0 && status) atomicOr(status, B200KV_S_BAD_PLAN);
-      return;
-    }
-    if (pc.b < 0) return;  // no work for this warp
+    ntiles = __shfl_sync(0xffffffffu, pe, 9);
+    if (pc.b < 0) return;  // no work for this warp (only in plans without a pool)
     const Lens probe{cached_lens, lens_s, nd};
     if (pc.b >= B || pc.h < 0 || pc.h >= c.Hkv || pc.n != probe.n(pc.b) || pc.T != probe.tiles(pc.b) || pc.tile < 0 ||
-        pc.tile >= pc.T || (long long)w * part.per >= part.U) {  // the plan was made from other lengths
+        pc.tile >= pc.T || ntiles < 1 || ntiles > part.per) {  // the plan was made from other lengths
       if (lane == 0 && status) atomicOr(status, B200KV_S_BAD_PLAN);
       return;
     }
@@ -921,177 +995,222 @@ decode_attn_kernel(const uint16_t* __restrict__ q, long long q_sb, long long q_s
     if ((long long)w * part.per >= part.U) return;
     const Lens probe{cached_lens, lens_s, nd};
     pc.seek(chunk_prefix, nchunks, chunk, probe, c.Hkv, c.page_size, w * part.per);
+    ntiles = min(part.per, part.U - w * part.per);
   }
   STAMP(8, dclk());
   const Lens lens{cached_lens, lens_s, nd};
-  const int u0 = w * part.per;
-  const int ntiles = min(part.per, part.U - u0);
+  const int R = plan != nullptr ? W + kMaxPool : W;  // ranges the workspace is laid out for
 
   int* ws_count = reinterpret_cast<int*>(workspace + ws_prefix_bytes(B));
+  int* pool_ctr = reinterpret_cast<int*>(workspace + ws_prefix_bytes(B) + ws_count_bytes(B, c.Hkv));
   float* ws_ml = reinterpret_cast<float*>(workspace + ws_head_bytes(B, c.Hkv));
-  float* ws_o = reinterpret_cast<float*>(workspace + ws_head_bytes(B, c.Hkv) + ws_ml_bytes(W, G));
+  float* ws_o = reinterpret_cast<float*>(workspace + ws_head_bytes(B, c.Hkv) + ws_ml_bytes(R, G));
   uint8_t* my_ring = ring + warp * kStages * kTileBytes;
   const uint32_t my_ring_s = smem_u32(my_ring);
   float* my_q = q_s + warp * (kMaxG * kD + kMaxG * kTile);
+  const int park_stride = G * kD + G * 2;
 
-  Cursor cc = pc;  // consumer position, advanced segment by segment
   PageWindow win{-1, 0, -1};
   const LaneCopy lc = make_lane_copy(c, lane);
-
+  typename std::conditional<kScalar, ScalarState, MmaState>::type st;
+  if constexpr (!kScalar) mma_init_lane(st, lane);
   // Early start: everything above read only the batch metadata.  q, the workspace and the newest
   // token of every sequence (the last tile) may still be in flight from the kernel launched just
   // before this one (the quantize-on-write of this layer), so those wait for it; older tiles are
   // not touched by it and are fetched right away, hiding the first burst behind that kernel.
   bool must_wait = early != 0;
-  int p_left = ntiles;  // tiles not yet issued
-#pragma unroll
-  for (int i = 0; i < kStages - 1; ++i) {
-    if (p_left > 0) {
-      if (must_wait && pc.tile == pc.T - 1) {
-        asm volatile("griddepcontrol.wait;" ::: "memory");
-        must_wait = false;
-      }
-      const int page = plan != nullptr ? __shfl_sync(0xffffffffu, first_page, i) : window_page(c, pc, win, lane);
-      issue_tile(c, pc, page, lc, my_ring_s + i * kTileBytes, lane, status);
-      if (--p_left > 0) pc.next(lens, c.Hkv, c.page_size);
-    }
-    cp_async_commit();
-  }
-  STAMP(2, dclk());
-  // planned: the table row of the next tile is requested now and is there when the main loop wants it
-  if (plan != nullptr && p_left > 0) load_window(c, pc.b, pc.slot, win, lane);
-  if (must_wait) asm volatile("griddepcontrol.wait;" ::: "memory");
+  bool first_range = true;
 
-  typename std::conditional<kScalar, ScalarState, MmaState>::type st;
-  if constexpr (!kScalar) mma_init_lane(st, lane);
-  int stage_c = 0, stage_p = kStages - 1;  // ring slots of the tile consumed / issued next
-  int done = 0;
-  while (done < ntiles) {
-    // one segment: the tiles [cc.tile, cc.tile + seg) of (entry cc.b, head cc.h)
-    const int seg = min(cc.T - cc.tile, ntiles - done);
-    if constexpr (kScalar) scalar_begin(st, my_q, q, q_sb, q_sh, cc.b, cc.h, G, scale_log2, lane);
-    else mma_begin(st, q, q_sb, q_sh, cc.b, cc.h, G, scale_log2, lane);
-#ifdef B200KV_STAMPS
-    if (done == 0) STAMP(9, dclk());
-#endif
-    int remaining = cc.n - cc.tile * kTile;  // tokens from this tile to the end of the sequence
-    for (int k = 0; k < seg; ++k) {
+  for (;;) {  // the warp's static range, then pool pieces until the pool is empty
+    Cursor cc = pc;  // consumer position, advanced segment by segment; pc runs kStages-1 tiles ahead
+    int p_left = ntiles;  // tiles not yet issued
+#pragma unroll
+    for (int i = 0; i < kStages - 1; ++i) {
       if (p_left > 0) {
-        issue_tile(c, pc, window_page(c, pc, win, lane), lc, my_ring_s + stage_p * kTileBytes, lane, status);
+        if (must_wait && pc.tile == pc.T - 1) {
+          asm volatile("griddepcontrol.wait;" ::: "memory");
+          must_wait = false;
+        }
+        const int page = plan != nullptr ? __shfl_sync(0xffffffffu, first_page, i) : window_page(c, pc, win, lane);
+        issue_tile(c, pc, page, lc, my_ring_s + i * kTileBytes, lane, status);
         if (--p_left > 0) pc.next(lens, c.Hkv, c.page_size);
-        else pdl_trigger();  // this warp has nothing left to fetch
       }
       cp_async_commit();
-      cp_async_wait<kStages - 1>();
-      __syncwarp();
-#ifdef B200KV_STAMPS
-      if (done == 0 && k == 0) STAMP(3, dclk());
-#endif
-      const uint8_t* stage = my_ring + stage_c * kTileBytes;
-      if constexpr (kScalar) scalar_tile(st, my_q, my_q + kMaxG * kD, stage, min(remaining, kTile), G, lane);
-      else mma_tile(st, stage, remaining, lane);
-      __syncwarp();
-      remaining -= kTile;
-      stage_c = (stage_c + 1) & (kStages - 1);
-      stage_p = (stage_p + 1) & (kStages - 1);
     }
 #ifdef B200KV_STAMPS
-    if (done + seg >= ntiles) STAMP(4, dclk());
+    if (first_range) STAMP(2, dclk());
 #endif
-    // whole iff the segment began at the sequence's first tile and reached its last one
-    const bool whole = cc.tile == 0 && seg == cc.T;
-    const int slot = done == 0 ? 0 : 1;
-    const int s0 = cc.base + cc.h * cc.T;  // flat tile range of this (entry, head): [s0, s0 + T)
-    uint16_t* out_row = out + cc.b * o_sb + (long long)(cc.h * G) * o_sh;
-    // Do all four warps of this CTA hold pieces of this same (entry, head)?  Then the pieces meet
-    // in shared memory and one warp forwards their sum (no global round trip for three of them).
-    const int cta_u0 = blockIdx.x * kWarps * part.per, cta_u1 = cta_u0 + kWarps * part.per;
-    const bool cta_inside = !whole && s0 <= cta_u0 && cta_u1 <= s0 + cc.T && cta_u1 <= part.U;
-    bool deliver = !whole;                       // a piece of mine (or my CTA's sum) goes to the workspace
-    float* po = ws_o + ((size_t)w * 2 + slot) * G * kD;
-    float* pml = ws_ml + ((size_t)w * 2 + slot) * G * 2;
-    if (cta_inside) {
-      cp_async_wait<0>();
-      __syncwarp();
-      float* so = reinterpret_cast<float*>(my_ring);  // [G][128] then [G][2]; the ring is idle now
-      if constexpr (kScalar) scalar_end(st, false, out, o_sb, o_sh, cc.b, cc.h, G, so, so + kMaxG * kD, lane);
-      else mma_end(st, false, out, o_sb, o_sh, cc.b, cc.h, G, so, so + kMaxG * kD, lane);
-      __threadfence_block();
-      __syncwarp();
-      int t = 0;
-      if (lane == 0) t = atomicAdd(cta_arrive, 1);
-      t = __shfl_sync(0xffffffffu, t, 0);
-      deliver = t == kWarps - 1;
-      if (deliver) {  // last of the four: sum them; lane l owns channels 4l..4l+3
-        __threadfence_block();
-        const bool exact = s0 == cta_u0 && s0 + cc.T == cta_u1;  // the CTA saw the whole sequence
-        po = ws_o + ((size_t)(blockIdx.x * kWarps) * 2) * G * kD;  // slot 0 of the CTA's first warp
-        pml = ws_ml + ((size_t)(blockIdx.x * kWarps) * 2) * G * 2;
-        for (int col = 0; col < G; ++col) {
-          float m4[kWarps], M = -INFINITY;
-#pragma unroll
-          for (int i = 0; i < kWarps; ++i) {
-            m4[i] = reinterpret_cast<const float*>(ring + i * kStages * kTileBytes)[kMaxG * kD + col * 2];
-            M = fmaxf(M, m4[i]);
-          }
-          float L = 0.f;
-          float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-          for (int i = 0; i < kWarps; ++i) {
-            const float* sp = reinterpret_cast<const float*>(ring + i * kStages * kTileBytes);
-            const float wg = fast_exp2(m4[i] - M);
-            L = fmaf(sp[kMaxG * kD + col * 2 + 1], wg, L);
-            const float4 o = *reinterpret_cast<const float4*>(sp + col * kD + 4 * lane);
-            a.x = fmaf(o.x, wg, a.x); a.y = fmaf(o.y, wg, a.y); a.z = fmaf(o.z, wg, a.z); a.w = fmaf(o.w, wg, a.w);
-          }
-          if (exact) {
-            const float inv = 1.f / L;
-            uint2 r;
-            r.x = float_to_bf16_bits(a.x * inv) | (float_to_bf16_bits(a.y * inv) << 16);
-            r.y = float_to_bf16_bits(a.z * inv) | (float_to_bf16_bits(a.w * inv) << 16);
-            *reinterpret_cast<uint2*>(out_row + col * o_sh + 4 * lane) = r;
-          } else {
-            *reinterpret_cast<float4*>(po + col * kD + 4 * lane) = a;
-            if (lane == 0) { pml[col * 2] = M; pml[col * 2 + 1] = L; }
-          }
+    // planned: the table row of the next tile is requested now and is there when the main loop wants it
+    if (plan != nullptr && p_left > 0) load_window(c, pc.b, pc.slot, win, lane);
+    if (must_wait) {
+      asm volatile("griddepcontrol.wait;" ::: "memory");
+      must_wait = false;
+    }
+
+    int stage_c = 0, stage_p = kStages - 1;  // ring slots of the tile consumed / issued next
+    int done = 0;
+    while (done < ntiles) {
+      // one segment: the tiles [cc.tile, cc.tile + seg) of (entry cc.b, head cc.h)
+      const int seg = min(cc.T - cc.tile, ntiles - done);
+      if constexpr (kScalar) scalar_begin(st, my_q, q, q_sb, q_sh, cc.b, cc.h, G, scale_log2, lane);
+      else mma_begin(st, q, q_sb, q_sh, cc.b, cc.h, G, scale_log2, lane);
+#ifdef B200KV_STAMPS
+      if (first_range && done == 0) STAMP(9, dclk());
+#endif
+      int remaining = cc.n - cc.tile * kTile;  // tokens from this tile to the end of the sequence
+      for (int k = 0; k < seg; ++k) {
+        if (p_left > 0) {
+          issue_tile(c, pc, window_page(c, pc, win, lane), lc, my_ring_s + stage_p * kTileBytes, lane, status);
+          if (--p_left > 0) pc.next(lens, c.Hkv, c.page_size);
+          else if (part.pool_pieces() == 0) pdl_trigger();  // this warp has nothing left to fetch
         }
-        if (exact) deliver = false;
-      }
-    } else {
-      if constexpr (kScalar) scalar_end(st, whole, out, o_sb, o_sh, cc.b, cc.h, G, po, pml, lane);
-      else mma_end(st, whole, out, o_sb, o_sh, cc.b, cc.h, G, po, pml, lane);
-    }
-#ifdef B200KV_STAMPS
-    if (done + seg >= ntiles) STAMP(10, dclk());
-#endif
-    if (fused && deliver) {
-      // Fused cross-split reduction: the warp that delivers the last piece of (entry, head) merges
-      // all of them.  Release: partial stores -> warp barrier -> counter; acquire: counter -> warp barrier -> loads.
-      const Pieces pieces(part, s0, s0 + cc.T);
-      __syncwarp();  // the lanes' partial stores are ordered before lane 0's release below
-      int arrived = 0;
-      if (lane == 0) arrived = atom_add_acq_rel(ws_count + cc.b * c.Hkv + cc.h, 1) + 1;
-      arrived = __shfl_sync(0xffffffffu, arrived, 0);
-      if (arrived == pieces.n) {  // the acquire half makes every earlier arriver's stores visible to this warp
+        cp_async_commit();
+        cp_async_wait<kStages - 1>();
         __syncwarp();
-        STAMP(11, dclk());
-        merge_partials(ws_ml, ws_o, pieces, G, out_row, o_sh, lane);
-        if (lane == 0) ws_count[cc.b * c.Hkv + cc.h] = 0;  // leave the counter zero for the next call
 #ifdef B200KV_STAMPS
-        STAMP(7, (unsigned long long)pieces.n);
-        STAMP(12, dclk());
+        if (first_range && done == 0 && k == 0) STAMP(3, dclk());
 #endif
+        const uint8_t* stage = my_ring + stage_c * kTileBytes;
+        if constexpr (kScalar) scalar_tile(st, my_q, my_q + kMaxG * kD, stage, min(remaining, kTile), G, lane);
+        else mma_tile(st, stage, remaining, lane);
+        __syncwarp();
+        remaining -= kTile;
+        stage_c = (stage_c + 1) & (kStages - 1);
+        stage_p = (stage_p + 1) & (kStages - 1);
       }
+#ifdef B200KV_STAMPS
+      if (first_range && done + seg >= ntiles) STAMP(4, dclk());
+#endif
+      // whole iff the segment began at the sequence's first tile and reached its last one
+      const bool whole = cc.tile == 0 && seg == cc.T;
+      const int slot = done == 0 ? 0 : 1;
+      const int s0 = cc.base + cc.h * cc.T;  // flat tile range of this (entry, head): [s0, s0 + T)
+      uint16_t* out_row = out + cc.b * o_sb + (long long)(cc.h * G) * o_sh;
+      // Do all four warps of this CTA hold pieces of this same (entry, head) in their static ranges?  Then the
+      // pieces meet in shared memory and one warp forwards their sum (no global round trip for three of them).
+      const int cta_u0 = blockIdx.x * kWarps * part.per, cta_u1 = cta_u0 + kWarps * part.per;
+      const bool cta_inside = first_range && !whole && s0 <= cta_u0 && cta_u1 <= s0 + cc.T && cta_u1 <= part.Us;
+      bool deliver = !whole;                       // a piece of mine (or my CTA's sum) goes to the workspace
+      float* po = ws_o + ((size_t)rid * 2 + slot) * G * kD;
+      float* pml = ws_ml + ((size_t)rid * 2 + slot) * G * 2;
+      if (cta_inside) {
+        float* so = park + warp * park_stride;  // [G][128] then [G][2]
+        if constexpr (kScalar) scalar_end(st, false, out, o_sb, o_sh, cc.b, cc.h, G, so, so + G * kD, lane);
+        else mma_end(st, false, out, o_sb, o_sh, cc.b, cc.h, G, so, so + G * kD, lane);
+        __threadfence_block();
+        __syncwarp();
+        int t = 0;
+        if (lane == 0) t = atomicAdd(cta_arrive, 1);
+        t = __shfl_sync(0xffffffffu, t, 0);
+        deliver = t == kWarps - 1;
+        if (deliver) {  // last of the four: sum them; lane l owns channels 4l..4l+3
+          __threadfence_block();
+          const bool exact = s0 == cta_u0 && s0 + cc.T == cta_u1;  // the CTA saw the whole sequence
+          po = ws_o + ((size_t)(blockIdx.x * kWarps) * 2) * G * kD;  // slot 0 of the CTA's first warp
+          pml = ws_ml + ((size_t)(blockIdx.x * kWarps) * 2) * G * 2;
+          for (int col = 0; col < G; ++col) {
+            float m4[kWarps], M = -INFINITY;
+#pragma unroll
+            for (int i = 0; i < kWarps; ++i) {
+              m4[i] = park[i * park_stride + G * kD + col * 2];
+              M = fmaxf(M, m4[i]);
+            }
+            float L = 0.f;
+            float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int i = 0; i < kWarps; ++i) {
+              const float* sp = park + i * park_stride;
+              const float wg = fast_exp2(m4[i] - M);
+              L = fmaf(sp[G * kD + col * 2 + 1], wg, L);
+              const float4 o = *reinterpret_cast<const float4*>(sp + col * kD + 4 * lane);
+              a.x = fmaf(o.x, wg, a.x); a.y = fmaf(o.y, wg, a.y); a.z = fmaf(o.z, wg, a.z); a.w = fmaf(o.w, wg, a.w);
+            }
+            if (exact) {
+              const float inv = 1.f / L;
+              uint2 r;
+              r.x = float_to_bf16_bits(a.x * inv) | (float_to_bf16_bits(a.y * inv) << 16);
+              r.y = float_to_bf16_bits(a.z * inv) | (float_to_bf16_bits(a.w * inv) << 16);
+              *reinterpret_cast<uint2*>(out_row + col * o_sh + 4 * lane) = r;
+            } else {
+              *reinterpret_cast<float4*>(po + col * kD + 4 * lane) = a;
+              if (lane == 0) { pml[col * 2] = M; pml[col * 2 + 1] = L; }
+            }
+          }
+          if (exact) deliver = false;
+        }
+      } else {
+        if constexpr (kScalar) scalar_end(st, whole, out, o_sb, o_sh, cc.b, cc.h, G, po, pml, lane);
+        else mma_end(st, whole, out, o_sb, o_sh, cc.b, cc.h, G, po, pml, lane);
+      }
+#ifdef B200KV_STAMPS
+      if (first_range && done + seg >= ntiles) STAMP(10, dclk());
+#endif
+      if (fused && deliver) {
+        // Fused cross-split reduction: the warp that delivers the last piece of (entry, head) merges
+        // all of them.  Release: partial stores -> warp barrier -> counter; acquire: counter -> warp barrier -> loads.
+        const Pieces pieces(part, s0, s0 + cc.T);
+        __syncwarp();  // the lanes' partial stores are ordered before lane 0's release below
+        int arrived = 0;
+        if (lane == 0) arrived = atom_add_acq_rel(ws_count + cc.b * c.Hkv + cc.h, 1) + 1;
+        arrived = __shfl_sync(0xffffffffu, arrived, 0);
+        if (arrived == pieces.n) {  // the acquire half makes every earlier arriver's stores visible to this warp
+          __syncwarp();
+          STAMP(11, dclk());
+          merge_partials(ws_ml, ws_o, pieces, G, out_row, o_sh, lane);
+          if (lane == 0) ws_count[cc.b * c.Hkv + cc.h] = 0;  // leave the counter zero for the next call
+#ifdef B200KV_STAMPS
+          STAMP(7, (unsigned long long)pieces.n);
+          STAMP(12, dclk());
+#endif
+        }
+      }
+      done += seg;
+      if (done < ntiles) cc.next_segment(lens, c.Hkv);
     }
-    done += seg;
-    if (done < ntiles) cc.next_segment(lens, c.Hkv);
+#ifdef B200KV_STAMPS
+    if (first_range) STAMP(6, (unsigned long long)ntiles);
+#endif
+    first_range = false;
+    const int npool = part.pool_pieces();
+    if (npool == 0) break;
+    // ---- claim the next pool piece.  Every warp of the grid claims until it is told the pool is empty, i.e. makes
+    // exactly one claim beyond the pieces; the warp that draws the very last ticket knows that every other warp has
+    // drawn its final one, hence finished all of its pieces, and puts the counter back to zero for the next call.
+    int ticket = 0;
+    if (lane == 0) ticket = atomicAdd(pool_ctr, 1);
+    ticket = __shfl_sync(0xffffffffu, ticket, 0);
+    if (ticket >= npool) {
+      if (ticket == npool + W - 1 && lane == 0) *pool_ctr = 0;
+      break;
+    }
+    const int pe = __ldcg(plan + kPlanHeaderInts + (size_t)(W + ticket) * kPlanEntryInts + (lane & (kPlanEntryInts - 1)));
+    pc.b = __shfl_sync(0xffffffffu, pe, 0);
+    pc.h = __shfl_sync(0xffffffffu, pe, 1);
+    pc.tile = __shfl_sync(0xffffffffu, pe, 2);
+    pc.T = __shfl_sync(0xffffffffu, pe, 3);
+    pc.n = __shfl_sync(0xffffffffu, pe, 4);
+    pc.base = __shfl_sync(0xffffffffu, pe, 5);
+    first_page = __shfl_sync(0xffffffffu, pe, 6 + (lane < kStages - 1 ? lane : 0));
+    ntiles = __shfl_sync(0xffffffffu, pe, 9);
+    if (pc.b < 0 || pc.b >= B || pc.h < 0 || pc.h >= c.Hkv || pc.T != lens.tiles(pc.b) || pc.tile < 0 || pc.tile >= pc.T ||
+        ntiles < 1) {  // cannot happen with a plan that passed the checks above; never walk off the batch
+      if (lane == 0 && status) atomicOr(status, B200KV_S_BAD_PLAN);
+      break;
+    }
+    pc.slot = (pc.tile * kTile) / c.page_size;
+    pc.row0 = pc.tile * kTile - pc.slot * c.page_size;
+    rid = W + ticket;
+    win.b = -1;  // the page window belongs to the range that just ended
+    cp_async_wait<0>();
+    __syncwarp();
   }
+  pdl_trigger();
   cp_async_wait<0>();
 #ifdef B200KV_STAMPS
   {
     unsigned sm;
     asm volatile("mov.u32 %0, %%smid;" : "=r"(sm));
-    STAMP(0, t_entry); STAMP(1, (unsigned long long)sm); STAMP(5, gtime()); STAMP(6, (unsigned long long)ntiles);
+    STAMP(0, t_entry); STAMP(1, (unsigned long long)sm); STAMP(5, gtime());
     STAMP(13, dclk());
   }
 #endif
@@ -1173,12 +1292,16 @@ decode_combine_kernel(const uint8_t* __restrict__ workspace, const int32_t* __re
   }
 }
 
-static size_t main_smem_bytes(int B, bool scalar) {
+static size_t main_smem_bytes(int G, bool scalar) {
   size_t s = (size_t)kWarps * kStages * kTileBytes;
   if (scalar) s += (size_t)kWarps * (kMaxG * kD + kMaxG * kTile) * 4;
+  s += (size_t)kWarps * (G * kD + G * 2) * 4;  // where a CTA's warps park their pieces for the CTA-level sum
   s += (size_t)(kWarps * 32 + 1 + kSmemLens + 1) * 4;
-  (void)B;
   return s;
+}
+
+static size_t workspace_bytes_for(int B, int Hkv, int G, int ranges) {
+  return ws_head_bytes(B, Hkv) + ws_ml_bytes(ranges, G) + (size_t)ranges * 2 * G * kD * 4;
 }
 
 }  // namespace b200kv
@@ -1187,9 +1310,12 @@ using namespace b200kv;
 
 extern "C" size_t b200kv_decode_attn_workspace_bytes(int32_t B, int32_t Hq, int32_t Hkv, int32_t D, int32_t sm_count) {
   if (B < 0 || Hq < 1 || Hkv < 1 || Hq % Hkv || D != kD || sm_count < 1) return 0;
-  const int G = Hq / Hkv;
-  const int W = sm_count * kCtasPerSm * kWarps;
-  return ws_head_bytes(B, Hkv) + ws_ml_bytes(W, G) + (size_t)W * 2 * G * kD * 4;
+  return workspace_bytes_for(B, Hkv, Hq / Hkv, sm_count * kCtasPerSm * kWarps);
+}
+
+extern "C" size_t b200kv_decode_attn_planned_workspace_bytes(int32_t B, int32_t Hq, int32_t Hkv, int32_t D, int32_t sm_count) {
+  if (B < 0 || Hq < 1 || Hkv < 1 || Hq % Hkv || D != kD || sm_count < 1) return 0;
+  return workspace_bytes_for(B, Hkv, Hq / Hkv, sm_count * kCtasPerSm * kWarps + kMaxPool);
 }
 
 // Argument checks shared by the three decode-attention entry points; nothing is enqueued before they pass.
@@ -1228,7 +1354,7 @@ static int launch_decode(const void* q, int64_t q_sb, int64_t q_sh, const b200kv
   const bool scalar = (variant & 1) != 0;
   const int fused = (variant & 2) ? 0 : 1;
   const int early = ((variant & 4) && fused) ? 1 : 0;  // the separate reduction kernel's prefix array is written before the wait
-  const size_t smem = main_smem_bytes(B, scalar);
+  const size_t smem = main_smem_bytes(G, scalar);
   // the opt-in to more than 48 KB of dynamic shared memory is per function AND per device: set on every call
   cudaError_t e = scalar ? cudaFuncSetAttribute(decode_attn_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
                          : cudaFuncSetAttribute(decode_attn_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -1285,7 +1411,8 @@ extern "C" int b200kv_decode_plan(const b200kv_table* table, const int32_t* cach
   if (!aligned(plan, 16)) return B200KV_E_ALIGN;
   if (plan_bytes_given < b200kv_decode_plan_bytes(sm_count)) return B200KV_E_WORKSPACE;
   const int W = sm_count * kCtasPerSm * kWarps;
-  decode_plan_kernel<<<1, kPlanThreads, 0, (cudaStream_t)stream>>>(cached_lens, num_decoding, table->ids, table->stride,
+  // a few CTAs share the ranges (each repeats the cheap length scan); none of them releases a chained successor early
+  decode_plan_kernel<<<kPlanCtas, kPlanThreads, 0, (cudaStream_t)stream>>>(cached_lens, num_decoding, table->ids, table->stride,
                                                                    table->max_pages, page_size, B, Hkv, W, (int*)plan);
   return cudaGetLastError() == cudaSuccess ? B200KV_OK : B200KV_E_LAUNCH;
 }
@@ -1303,6 +1430,7 @@ extern "C" int b200kv_decode_attn_planned(const void* q, int64_t q_sb, int64_t q
   if (rc) return rc;
   if (variant & 2) return B200KV_E_SHAPE;  // the two-kernel reduction reads a prefix array only the unplanned kernel writes
   if (!aligned(plan, 16)) return B200KV_E_ALIGN;
+  if (workspace_bytes < b200kv_decode_attn_planned_workspace_bytes(B, Hq, cache->num_kv_heads, kD, sm_count)) return B200KV_E_WORKSPACE;
   if (plan_bytes_given < b200kv_decode_plan_bytes(sm_count)) return B200KV_E_WORKSPACE;
   return launch_decode(q, q_sb, q_sh, cache, table, cached_lens, num_decoding, scale, out, o_sb, o_sh, workspace, 0, B, Hq,
                        sm_count, variant, plan, status, stream);

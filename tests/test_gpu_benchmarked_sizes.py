@@ -70,7 +70,7 @@ def test_sweep_cells_at_ctx_4096(K, B):
     C.set_threads(os.cpu_count() or 1)
     want = C.decode_attention(H.to_f32(q), H.cache_to_numpy(cache), np.full(B, n - 1, np.int32), table, B, SCALE)
     outs = []
-    for variant, planned in ((0, False), (2, False), (0, True)):
+    for variant, planned in ((0, False), (2, False), (0, True), (0, True)):
         out = torch.full((B, HQ, D), 7.0, dtype=torch.bfloat16, device="cuda")
         plan = K.plan_decode_step(cached, tab, nd, cache) if planned else None
         for _ in range(2):
@@ -79,7 +79,11 @@ def test_sweep_cells_at_ctx_4096(K, B):
         assert K.check_status() == 0
         check(H.to_f32(out), want)
         outs.append(out)
-    assert torch.equal(outs[0], outs[2]), "planned and unplanned calls share one work split"
+    # At this size the plan holds back a pool of pieces that warps claim at run time: which warp takes which piece
+    # varies from call to call, the result must not.  (The unplanned call cuts the sequences elsewhere, so it agrees
+    # with the planned one to the last bf16 bit only.)
+    assert torch.equal(outs[2], outs[3]), "planned calls must be reproducible bit for bit"
+    assert torch.equal(outs[0], outs[1]), "fused and two-kernel reduction share one work split"
 
 
 def test_one_shard_of_the_sequence_sharded_decode(K):
@@ -123,7 +127,9 @@ def test_one_shard_of_the_sequence_sharded_decode(K):
     torch.cuda.synchronize()
     assert K.check_status() == 0
     check(H.to_f32(plain), want)
-    assert torch.equal(plain, planned)
+    check(H.to_f32(planned), want)
+    again = K.decode_attention(got_q, cache, cached, tab, nd, SCALE, plan=K.plan_decode_step(cached, tab, nd, cache))
+    assert torch.equal(planned, again), "planned calls must be reproducible bit for bit"
 
 
 @pytest.mark.parametrize("prior", [3072])
