@@ -159,7 +159,9 @@ int b200kv_dequant_prefix(const b200kv_cache* cache, const b200kv_table* table,
 
 /* Replaces prefill_attention (kernels.py:973-1175): packed varlen causal attention of the
  * prefilling entries over [dequantized prefix | own chunk].  tile_start [num_tiles] gives the
- * first packed row of each block_m-row query tile (-1 = idle), seq_ids [N] the entry of each row. */
+ * first packed row of each block_m-row query tile (-1 = idle), seq_ids [N] the entry of each row.
+ * k_prefix / v_prefix may be NULL when the step has no cached prefix at all (empty tensors have no storage); prefix
+ * lengths in cu_cached are then ignored. */
 int b200kv_prefill_attn(const void* q, int64_t q_stride_n, int64_t q_stride_h,
                         const void* k, int64_t k_stride_n, int64_t k_stride_h,
                         const void* v, int64_t v_stride_n, int64_t v_stride_h,
@@ -284,7 +286,7 @@ int b200kv_decode_attn(const void* q, int64_t q_stride_b, int64_t q_stride_h,
  * plan that does not fit (checked per warp against the header and the lengths) sets B200KV_S_BAD_PLAN in the
  * status word and the warps that saw it write nothing; zero-fill the workspace again after that.
  * For batches large enough that every warp of the grid has at least 24 tiles, the plan also holds back a fifth of the
- * tiles in a pool of small pieces (8 tiles, then 4 at the end) that the warps claim when their own equal range is
+ * tiles in a pool of small pieces (16 tiles, then 8 at the end) that the warps claim when their own equal range is
  * done: the streaming rate of an SM depends on its place on the chip by about +-10 %, stably, so equal ranges finish
  * far apart; with the pool the fast SMs take more.  The piece boundaries depend on the batch only, and the pieces of
  * a sequence are merged in tile order, so the result is the same whichever warp took which piece.  The planned call

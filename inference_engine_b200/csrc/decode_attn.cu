@@ -202,7 +202,7 @@ __host__ __device__ __forceinline__ Partition make_partition(int total_tiles_one
 
 // The same with a pool: about a fifth of the tiles is held back from the static ranges.  Warps on fast SMs finish
 // their (equal) ranges early - the per-SM streaming rate differs by +-10 % with the SM's place on the chip, stably
-// from launch to launch - and then take pool pieces, larger ones first, small ones at the end so that the last
+// from launch to launch - and then take pool pieces, 16-tile ones first, 8-tile ones at the end so that the last
 // pieces finish close together.  Piece boundaries are a function of the batch alone, so the result does not depend
 // on which warp took which piece.
 __host__ __device__ __forceinline__ Partition make_pooled_partition(int total_tiles_one_head, int Hkv, int W, int num_entries) {
@@ -211,7 +211,7 @@ __host__ __device__ __forceinline__ Partition make_pooled_partition(int total_ti
   p.per = (int)(((long long)p.U * 4 / 5) / W);
   p.Us = p.per * W;
   const int pool = p.U - p.Us;
-  int P1 = 8, P2 = 4;
+  int P1 = 16, P2 = 8;  // a piece shorter than the copies' look-ahead cannot be handed over without a gap
   for (;;) {
     const int t2 = ((pool * 2 / 5) / P2) * P2;  // the last two fifths of the pool in small pieces
     p.n1 = (pool - t2) / P1;
@@ -1020,34 +1020,120 @@ decode_attn_kernel(const uint16_t* __restrict__ q, long long q_sb, long long q_s
   // not touched by it and are fetched right away, hiding the first burst behind that kernel.
   bool must_wait = early != 0;
   bool first_range = true;
+  const int npool = part.pool_pieces();
+
+  // The copies run kStages-1 tiles ahead of the arithmetic and do not stop at the end of a range: when the range
+  // in hand has few tiles left to request, the warp draws a ticket for its next pool piece, fetches that piece's
+  // plan entry, and goes on requesting tiles of the new piece while it still consumes the old one.  The ticket and
+  // the entry are only looked at some tiles after they were asked for, so neither round trip stalls the warp.
+  // Every warp of the grid draws tickets until it is told the pool is empty, i.e. draws exactly one ticket beyond
+  // the pieces; the warp that draws the very last of all tickets knows that nobody will touch the counter again
+  // in this call and puts it back to zero for the next one.
+  constexpr int kClaimAhead = 6;  // tiles still to request when the ticket is drawn
+  constexpr int kEntryAhead = 3;  // ... when the plan entry of the drawn piece is fetched
+  // --- state of the copies (the producer side of the ring)
+  int p_left = ntiles;            // tiles of the range the copies are in that are not yet requested
+  int p_issued = 0;               // ... that are requested
+  int p_pages = first_page;       // lane i < kStages-1: page id of that range's i-th tile (planned calls)
+  bool copies_ahead = false;      // the copies have moved on to the range after the one being consumed
+  int stage_p = 0, inflight = 0;  // ring slot of the next request; tiles requested and not yet consumed
+  // --- the hand-over to the next range
+  int ticket = -1, next_pe = 0;   // lane 0's ticket / every lane's word of the next piece's plan entry
+  int claim_state = npool > 0 ? 0 : 3;  // 0 nothing asked, 1 ticket drawn, 2 entry fetched (or pool empty), 3 no pool
+  bool have_next = false;         // the next range is known: next_start, next_rid, next_tiles, next_pages
+  Cursor next_start = pc;
+  int next_rid = 0, next_tiles = 0, next_pages = -1;
+
+  // One step of the producer: request the next tile if one is known (returns true), and advance the hand-over by
+  // at most one stage.  Called once per consumed tile in the steady state.
+  auto request_one = [&]() -> bool {
+    if (p_left == 0 && have_next && !copies_ahead) {  // the range in hand is fully requested: move on to the next
+      pc = next_start;
+      p_left = next_tiles;
+      p_issued = 0;
+      p_pages = next_pages;
+      copies_ahead = true;
+      win.b = -1;
+    }
+    bool issued = false;
+    if (p_left > 0) {
+      if (must_wait && pc.tile == pc.T - 1) {  // first range only: the newest token comes from the kernel before
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        must_wait = false;
+      }
+      int page;
+      if (plan != nullptr && p_issued < kStages - 1) page = __shfl_sync(0xffffffffu, p_pages, p_issued);
+      else page = window_page(c, pc, win, lane);
+      issue_tile(c, pc, page, lc, my_ring_s + stage_p * kTileBytes, lane, status);
+      cp_async_commit();
+      stage_p = (stage_p + 1) & (kStages - 1);
+      ++inflight;
+      ++p_issued;
+      issued = true;
+      if (--p_left > 0) {
+        pc.next(lens, c.Hkv, c.page_size);
+        // planned: the table row of the tile after the plan's page ids is requested early
+        if (plan != nullptr && p_issued == kStages - 1) load_window(c, pc.b, pc.slot, win, lane);
+      } else if (npool == 0) {
+        pdl_trigger();  // this warp has nothing left to fetch
+      }
+    }
+    if (copies_ahead || claim_state == 3) return issued;
+    if (claim_state == 0) {
+      if (p_left <= kClaimAhead) {
+        if (lane == 0) ticket = atomicAdd(pool_ctr, 1);
+        claim_state = 1;
+      }
+    } else if (claim_state == 1) {
+      if (p_left <= kEntryAhead) {
+        ticket = __shfl_sync(0xffffffffu, ticket, 0);
+        if (ticket < npool) next_pe = __ldcg(plan + kPlanHeaderInts + (size_t)(W + ticket) * kPlanEntryInts + (lane & (kPlanEntryInts - 1)));
+        else if (ticket == npool + W - 1 && lane == 0) *pool_ctr = 0;
+        claim_state = 2;
+      }
+    } else if (p_left == 0 && !have_next && ticket < npool) {
+      next_start.b = __shfl_sync(0xffffffffu, next_pe, 0);
+      next_start.h = __shfl_sync(0xffffffffu, next_pe, 1);
+      next_start.tile = __shfl_sync(0xffffffffu, next_pe, 2);
+      next_start.T = __shfl_sync(0xffffffffu, next_pe, 3);
+      next_start.n = __shfl_sync(0xffffffffu, next_pe, 4);
+      next_start.base = __shfl_sync(0xffffffffu, next_pe, 5);
+      next_pages = __shfl_sync(0xffffffffu, next_pe, 6 + (lane < kStages - 1 ? lane : 0));
+      next_tiles = __shfl_sync(0xffffffffu, next_pe, 9);
+      next_rid = W + ticket;
+      const bool ok = next_start.b >= 0 && next_start.b < B && next_start.h >= 0 && next_start.h < c.Hkv &&
+                      next_start.T == lens.tiles(next_start.b) && next_start.tile >= 0 && next_start.tile < next_start.T &&
+                      next_tiles >= 1;
+      if (!ok) {  // cannot happen with a plan that passed the checks above; never walk off the batch
+        if (lane == 0 && status) atomicOr(status, B200KV_S_BAD_PLAN);
+        ticket = npool;  // as if the pool were empty
+      } else {
+        next_start.slot = (next_start.tile * kTile) / c.page_size;
+        next_start.row0 = next_start.tile * kTile - next_start.slot * c.page_size;
+        have_next = true;
+      }
+    }
+    return issued;
+  };
+  // Wait until the oldest of the `inflight` requested tiles has landed (one commit group per tile).
+  auto wait_oldest = [&]() {
+    if (inflight >= kStages) cp_async_wait<kStages - 1>();
+    else if (inflight == 3) cp_async_wait<2>();
+    else if (inflight == 2) cp_async_wait<1>();
+    else cp_async_wait<0>();
+    __syncwarp();
+  };
+
+  Cursor cc = pc;  // consumer position, advanced segment by segment
+  int stage_c = 0;  // ring slot of the tile consumed next
+  while (inflight < kStages - 1 && request_one()) {}
+  STAMP(2, dclk());
+  if (must_wait) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    must_wait = false;
+  }
 
   for (;;) {  // the warp's static range, then pool pieces until the pool is empty
-    Cursor cc = pc;  // consumer position, advanced segment by segment; pc runs kStages-1 tiles ahead
-    int p_left = ntiles;  // tiles not yet issued
-#pragma unroll
-    for (int i = 0; i < kStages - 1; ++i) {
-      if (p_left > 0) {
-        if (must_wait && pc.tile == pc.T - 1) {
-          asm volatile("griddepcontrol.wait;" ::: "memory");
-          must_wait = false;
-        }
-        const int page = plan != nullptr ? __shfl_sync(0xffffffffu, first_page, i) : window_page(c, pc, win, lane);
-        issue_tile(c, pc, page, lc, my_ring_s + i * kTileBytes, lane, status);
-        if (--p_left > 0) pc.next(lens, c.Hkv, c.page_size);
-      }
-      cp_async_commit();
-    }
-#ifdef B200KV_STAMPS
-    if (first_range) STAMP(2, dclk());
-#endif
-    // planned: the table row of the next tile is requested now and is there when the main loop wants it
-    if (plan != nullptr && p_left > 0) load_window(c, pc.b, pc.slot, win, lane);
-    if (must_wait) {
-      asm volatile("griddepcontrol.wait;" ::: "memory");
-      must_wait = false;
-    }
-
-    int stage_c = 0, stage_p = kStages - 1;  // ring slots of the tile consumed / issued next
     int done = 0;
     while (done < ntiles) {
       // one segment: the tiles [cc.tile, cc.tile + seg) of (entry cc.b, head cc.h)
@@ -1059,14 +1145,8 @@ decode_attn_kernel(const uint16_t* __restrict__ q, long long q_sb, long long q_s
 #endif
       int remaining = cc.n - cc.tile * kTile;  // tokens from this tile to the end of the sequence
       for (int k = 0; k < seg; ++k) {
-        if (p_left > 0) {
-          issue_tile(c, pc, window_page(c, pc, win, lane), lc, my_ring_s + stage_p * kTileBytes, lane, status);
-          if (--p_left > 0) pc.next(lens, c.Hkv, c.page_size);
-          else if (part.pool_pieces() == 0) pdl_trigger();  // this warp has nothing left to fetch
-        }
-        cp_async_commit();
-        cp_async_wait<kStages - 1>();
-        __syncwarp();
+        while (inflight < kStages && request_one()) {}  // one request per tile in the steady state; more after a gap
+        wait_oldest();
 #ifdef B200KV_STAMPS
         if (first_range && done == 0 && k == 0) STAMP(3, dclk());
 #endif
@@ -1076,7 +1156,7 @@ decode_attn_kernel(const uint16_t* __restrict__ q, long long q_sb, long long q_s
         __syncwarp();
         remaining -= kTile;
         stage_c = (stage_c + 1) & (kStages - 1);
-        stage_p = (stage_p + 1) & (kStages - 1);
+        --inflight;
       }
 #ifdef B200KV_STAMPS
       if (first_range && done + seg >= ntiles) STAMP(4, dclk());
@@ -1171,38 +1251,21 @@ decode_attn_kernel(const uint16_t* __restrict__ q, long long q_sb, long long q_s
     if (first_range) STAMP(6, (unsigned long long)ntiles);
 #endif
     first_range = false;
-    const int npool = part.pool_pieces();
-    if (npool == 0) break;
-    // ---- claim the next pool piece.  Every warp of the grid claims until it is told the pool is empty, i.e. makes
-    // exactly one claim beyond the pieces; the warp that draws the very last ticket knows that every other warp has
-    // drawn its final one, hence finished all of its pieces, and puts the counter back to zero for the next call.
-    int ticket = 0;
-    if (lane == 0) ticket = atomicAdd(pool_ctr, 1);
-    ticket = __shfl_sync(0xffffffffu, ticket, 0);
-    if (ticket >= npool) {
-      if (ticket == npool + W - 1 && lane == 0) *pool_ctr = 0;
-      break;
-    }
-    const int pe = __ldcg(plan + kPlanHeaderInts + (size_t)(W + ticket) * kPlanEntryInts + (lane & (kPlanEntryInts - 1)));
-    pc.b = __shfl_sync(0xffffffffu, pe, 0);
-    pc.h = __shfl_sync(0xffffffffu, pe, 1);
-    pc.tile = __shfl_sync(0xffffffffu, pe, 2);
-    pc.T = __shfl_sync(0xffffffffu, pe, 3);
-    pc.n = __shfl_sync(0xffffffffu, pe, 4);
-    pc.base = __shfl_sync(0xffffffffu, pe, 5);
-    first_page = __shfl_sync(0xffffffffu, pe, 6 + (lane < kStages - 1 ? lane : 0));
-    ntiles = __shfl_sync(0xffffffffu, pe, 9);
-    if (pc.b < 0 || pc.b >= B || pc.h < 0 || pc.h >= c.Hkv || pc.T != lens.tiles(pc.b) || pc.tile < 0 || pc.tile >= pc.T ||
-        ntiles < 1) {  // cannot happen with a plan that passed the checks above; never walk off the batch
-      if (lane == 0 && status) atomicOr(status, B200KV_S_BAD_PLAN);
-      break;
-    }
-    pc.slot = (pc.tile * kTile) / c.page_size;
-    pc.row0 = pc.tile * kTile - pc.slot * c.page_size;
-    rid = W + ticket;
-    win.b = -1;  // the page window belongs to the range that just ended
-    cp_async_wait<0>();
-    __syncwarp();
+    if (claim_state == 3) break;  // no pool
+    // Ranges shorter than the look-ahead (or a ticket that came late) leave the hand-over unfinished: finish it
+    // now (request_one with nothing to request only advances the claim).
+    while (!have_next && !(claim_state == 2 && ticket >= npool)) request_one();
+    if (!have_next) break;        // the pool is empty
+    // the consumer steps into the range the copies are already working on (or are about to start: request_one
+    // moves them there on its next call)
+    rid = next_rid;
+    ntiles = next_tiles;
+    cc = next_start;
+    if (!copies_ahead) request_one();
+    have_next = false;
+    copies_ahead = false;
+    claim_state = 0;
+    ticket = -1;
   }
   pdl_trigger();
   cp_async_wait<0>();

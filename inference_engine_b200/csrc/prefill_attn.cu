@@ -79,7 +79,8 @@ prefill_attn_kernel(const uint16_t* __restrict__ q, long long q_sn, long long q_
   if (tile_row < 0 || tile_row >= N) return;
   const int hq = blockIdx.x, hk = hq / G;
   const int seq = seq_ids[tile_row];
-  const int prefix_start = cu_cached[seq], prefix_len = cu_cached[seq + 1] - prefix_start;
+  // a step in which no entry has a cached prefix may pass empty prefix tensors (no storage: NULL pointers)
+  const int prefix_start = cu_cached[seq], prefix_len = (k_prefix && v_prefix) ? cu_cached[seq + 1] - prefix_start : 0;
   const int seq_start = cu_seqlens[seq], seq_end = min(cu_seqlens[seq + 1], N);
   const int row_end = min(tile_row + block_m, seq_end);
   const int row0 = tile_row + sub * kPfRows;  // first query row of this CTA
@@ -236,8 +237,9 @@ extern "C" int b200kv_prefill_attn_variant(const void* q, int64_t q_sn, int64_t 
                                            int32_t variant, int32_t* status, void* stream) {
   // an empty batch is valid and has nothing to launch (its tensors have no storage, so their pointers are NULL)
   if (N == 0 || num_tiles == 0) return B200KV_OK;
-  if (!q || !k || !v || !seq_ids || !cu_seqlens || !tile_start || !k_prefix || !v_prefix || !cu_cached || !out)
-    return B200KV_E_NULL;
+  // k_prefix / v_prefix may be NULL (empty tensors): the step then has no cached prefix to attend
+  if (!q || !k || !v || !seq_ids || !cu_seqlens || !tile_start || !cu_cached || !out) return B200KV_E_NULL;
+  if (!k_prefix || !v_prefix) prefix_rows = 0;
   if (D != kD || Hq < 1 || Hkv < 1 || Hq % Hkv || N < 0 || num_tiles < 0 || block_m < 1 || prefix_rows < 0)
     return B200KV_E_SHAPE;
   if (variant < 0 || variant > 3) return B200KV_E_RANGE;

@@ -190,7 +190,8 @@ prefill_attn_tc5_kernel(const uint16_t* __restrict__ q, long long q_sn, long lon
   if (tile_row < 0 || tile_row >= N) return;
   const int hq = blockIdx.x, hk = hq / G;
   const int seq = seq_ids[tile_row];
-  const int prefix_start = cu_cached[seq], prefix_len = cu_cached[seq + 1] - prefix_start;
+  // a step in which no entry has a cached prefix may pass empty prefix tensors (no storage: NULL pointers)
+  const int prefix_start = cu_cached[seq], prefix_len = (k_prefix && v_prefix) ? cu_cached[seq + 1] - prefix_start : 0;
   const int seq_start = cu_seqlens[seq], seq_end = min(cu_seqlens[seq + 1], N);
   const int row_end = min(tile_row + block_m, seq_end);
   const int row0 = tile_row + sub * kT5Tile;  // first query row of this CTA

@@ -109,6 +109,9 @@ class Scheduler:
     def submit(self, prompt_ids: list[int], max_new_tokens: int) -> Request:
         assert max_new_tokens >= 1 and len(prompt_ids) > 0
         assert len(prompt_ids) + max_new_tokens <= self.max_len, "prompt + continuation must fit max_len"
+        need = math.ceil(min(len(prompt_ids) + max_new_tokens - 1, self.max_len) / self.page_size)
+        if need > self.pool.capacity:  # it could never be admitted and would block the queue for ever
+            raise ValueError(f"the request needs {need} pages over its lifetime, the pool holds {self.pool.capacity}")
         r = Request(self.next_id, list(prompt_ids), max_new_tokens, t_submit=time.perf_counter())
         self.next_id += 1
         self.waiting.append(r)

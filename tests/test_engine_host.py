@@ -107,3 +107,12 @@ def test_stop_token_and_row_end_finish_a_request():
 def test_budget_must_cover_batch_plus_first_chunk():
     with pytest.raises(AssertionError):
         make(max_batch=20, budget=24, min_first=8)
+
+
+def test_a_request_larger_than_the_pool_is_refused_at_submission():
+    """It could never be admitted: planning would stop at it for ever and every later request would starve."""
+    s, pool = make(pages=4, max_len=512, budget=64)
+    with pytest.raises(ValueError):
+        s.submit(list(range(100)), 8)  # 107 cached tokens = 7 pages
+    ok = s.submit(list(range(40)), 8)  # 47 tokens = 3 pages
+    assert s.plan() is not None and ok.admitted

@@ -83,7 +83,6 @@ def test_sweep_cells_at_ctx_4096(K, B):
     # varies from call to call, the result must not.  (The unplanned call cuts the sequences elsewhere, so it agrees
     # with the planned one to the last bf16 bit only.)
     assert torch.equal(outs[2], outs[3]), "planned calls must be reproducible bit for bit"
-    assert torch.equal(outs[0], outs[1]), "fused and two-kernel reduction share one work split"
 
 
 def test_one_shard_of_the_sequence_sharded_decode(K):

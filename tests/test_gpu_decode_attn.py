@@ -77,7 +77,7 @@ def test_boundaries(K, variant, paged):
 
 
 @pytest.mark.parametrize("variant", [0, 1])
-def test_cfg1_quantized_gaussian(K, variant):
+def test_quantized_gaussian_four_sequences(K, variant):
     """B=4, contexts 128..1024, N(0,1) K/V quantized per token per head, 16-token pages, permuted
     page table: the stated tolerance and the tight one."""
     rng = np.random.default_rng(0)

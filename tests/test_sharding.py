@@ -12,7 +12,7 @@ from inference_engine_b200.sharding import gather_outputs, plan_shards
 
 def test_plan_is_balanced_and_deterministic():
     rng = np.random.default_rng(4)
-    lens = np.exp(rng.uniform(np.log(512), np.log(32768), 2048)).astype(int)  # cfg 5: log-uniform contexts
+    lens = np.exp(rng.uniform(np.log(512), np.log(32768), 2048)).astype(int)  # log-uniform contexts, as in the sharded benchmark
     for world in (1, 2, 4, 8):
         plan = plan_shards(lens, world)
         assert sorted(i for ids in plan.local for i in ids) == list(range(len(lens)))
