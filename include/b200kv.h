@@ -285,18 +285,10 @@ int b200kv_decode_attn(const void* q, int64_t q_stride_b, int64_t q_stride_h,
  * and the table must not change, and B, Hkv, page_size and sm_count must be the ones the plan was made with.  A
  * plan that does not fit (checked per warp against the header and the lengths) sets B200KV_S_BAD_PLAN in the
  * status word and the warps that saw it write nothing; zero-fill the workspace again after that.
- * For batches large enough that every warp of the grid has at least 24 tiles, the plan also holds back a fifth of the
- * tiles in a pool of small pieces (16 tiles, then 8 at the end) that the warps claim when their own equal range is
- * done: the streaming rate of an SM depends on its place on the chip by about +-10 %, stably, so equal ranges finish
- * far apart; with the pool the fast SMs take more.  The piece boundaries depend on the batch only, and the pieces of
- * a sequence are merged in tile order, so the result is the same whichever warp took which piece.  The planned call
- * needs room for the pool's partial results: b200kv_decode_attn_planned_workspace_bytes (same zero-fill contract;
- * a buffer of that size also serves b200kv_decode_attn).
  * `variant` as for b200kv_decode_attn, except bit 1 (the two-kernel reduction), which is refused.  With bit 2
  * (early start) the plan counts as metadata: it is read before the wait, which is safe because the plan kernel
  * never releases a chained successor before it has finished. */
 size_t b200kv_decode_plan_bytes(int32_t sm_count);
-size_t b200kv_decode_attn_planned_workspace_bytes(int32_t B, int32_t Hq, int32_t Hkv, int32_t D, int32_t sm_count);
 int b200kv_decode_plan(const b200kv_table* table, const int32_t* cached_lens, const int32_t* num_decoding,
                        int32_t B, int32_t num_kv_heads, int32_t page_size, int32_t sm_count,
                        void* plan, size_t plan_bytes, void* stream);

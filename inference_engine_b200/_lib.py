@@ -74,7 +74,6 @@ SIGNATURES = {
                                      c_int64, c_int64, c_void_p, c_size_t, c_int32, c_int32, c_int32, c_int32, c_void_p,
                                      c_void_p]),
     "b200kv_decode_plan_bytes": (c_size_t, [c_int32]),
-    "b200kv_decode_attn_planned_workspace_bytes": (c_size_t, [c_int32, c_int32, c_int32, c_int32, c_int32]),
     "b200kv_decode_plan": (c_int32, [P_TABLE, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32, c_void_p, c_size_t,
                                      c_void_p]),
     "b200kv_decode_attn_planned": (c_int32, [c_void_p, c_int64, c_int64, P_CACHE, P_TABLE, c_void_p, c_void_p, c_float,
@@ -114,6 +113,8 @@ def load(build_if_needed: bool = True) -> C.CDLL:
         path = _build.build()
     if _path_override is not None:
         path = _path_override
+    elif os.environ.get("B200KV_LIBRARY"):  # another build of the same sources (an experiment with other tile constants)
+        path = os.environ["B200KV_LIBRARY"]
     if not os.path.exists(path):
         raise B200KVError(f"{path} is missing: the CUDA extension is required, there is no fallback path")
     lib = C.CDLL(path)

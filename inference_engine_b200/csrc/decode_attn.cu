@@ -48,21 +48,9 @@ static_assert((kStages & (kStages - 1)) == 0, "ring indices are masked");
 
 struct Partition {
   int U;        // total tiles over all (entry, head)
-  int per;      // tiles of a warp's static range
+  int per;      // tiles per worker
   int W;        // workers (warps in the grid)
-  // The pool (planned calls on large batches only; Us == U and n1 == n2 == 0 otherwise): the static ranges cover
-  // tiles [0, Us) = W * per exactly; tiles [Us, U) are cut into n1 pieces of P1 tiles followed by n2 pieces of P2
-  // tiles (the very last piece may be shorter), which the warps claim one at a time when their own range is done.
-  int Us, n1, P1, n2, P2;
-  __host__ __device__ __forceinline__ int pool_pieces() const { return n1 + n2; }
-  __host__ __device__ __forceinline__ int piece_start(int j) const { return j < n1 ? Us + j * P1 : Us + n1 * P1 + (j - n1) * P2; }
-  __host__ __device__ __forceinline__ int piece_of(int u) const {
-    const int r = u - Us;
-    return r < n1 * P1 ? r / P1 : n1 + (r - n1 * P1) / P2;
-  }
 };
-constexpr int kMaxPool = 8192;    // pieces a plan may hold
-constexpr int kPoolMinShare = 24; // a pool is only made when the even share of a warp is at least this many tiles
 
 // ------------------------------------------------------------------ small PTX wrappers
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -101,7 +89,7 @@ __device__ __forceinline__ void cp_async16_imm(uint32_t dst, const void* src) { 
 }
 // D += A(16x32, row, s8) * B(32x8, col, s8), s32 accumulate.
 __device__ __forceinline__ void imma16832(int (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-  asm volatile(
+  asm(
       "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
       : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
@@ -109,7 +97,7 @@ __device__ __forceinline__ void imma16832(int (&d)[4], const uint32_t (&a)[4], u
 // D += A(16x16, row) * B(16x8, col), fp16 inputs, fp32 accumulate.
 __device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                          uint32_t b1) {
-  asm volatile(
+  asm(
       "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
       : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
@@ -196,31 +184,6 @@ __host__ __device__ __forceinline__ Partition make_partition(int total_tiles_one
   const int min_tiles = (num_entries > 0 && total_tiles_one_head <= 32 * num_entries) ? 8 : 4;
   int per = (p.U + W - 1) / W;
   p.per = per > min_tiles ? per : min_tiles;
-  p.Us = p.U; p.n1 = 0; p.P1 = 1; p.n2 = 0; p.P2 = 1;
-  return p;
-}
-
-// The same with a pool: about a fifth of the tiles is held back from the static ranges.  Warps on fast SMs finish
-// their (equal) ranges early - the per-SM streaming rate differs by +-10 % with the SM's place on the chip, stably
-// from launch to launch - and then take pool pieces, 16-tile ones first, 8-tile ones at the end so that the last
-// pieces finish close together.  Piece boundaries are a function of the batch alone, so the result does not depend
-// on which warp took which piece.
-__host__ __device__ __forceinline__ Partition make_pooled_partition(int total_tiles_one_head, int Hkv, int W, int num_entries) {
-  Partition p = make_partition(total_tiles_one_head, Hkv, W, num_entries);
-  if (p.U / W < kPoolMinShare) return p;
-  p.per = (int)(((long long)p.U * 4 / 5) / W);
-  p.Us = p.per * W;
-  const int pool = p.U - p.Us;
-  int P1 = 16, P2 = 8;  // a piece shorter than the copies' look-ahead cannot be handed over without a gap
-  for (;;) {
-    const int t2 = ((pool * 2 / 5) / P2) * P2;  // the last two fifths of the pool in small pieces
-    p.n1 = (pool - t2) / P1;
-    const int rest = pool - p.n1 * P1;           // >= t2; everything behind the large pieces
-    p.n2 = (rest + P2 - 1) / P2;
-    if (p.n1 + p.n2 <= kMaxPool) break;
-    P1 *= 2; P2 *= 2;
-  }
-  p.P1 = P1; p.P2 = P2;
   return p;
 }
 
@@ -436,13 +399,21 @@ __device__ __forceinline__ void mma_init_lane(MmaState& st, int lane) {
   st.v_off = kTile * kD + 2 * t * kD + ((g ^ (2 * t)) << 4);
 }
 
-__device__ __forceinline__ void mma_tile(MmaState& st, const uint8_t* stage, int nvalid, int lane) {
+// One tile is processed in three steps that the main loop overlaps across tiles: the scores of tile k+1 (int8
+// tensor cores, softmax bookkeeping) are independent of the P.V product of tile k (fp16 tensor cores), so the two
+// are issued side by side and hide each other's latencies; the rescaling of O by tile k+1's correction comes after
+// tile k's product, which is the order the plain online softmax has.
+struct Scored {
+  uint32_t pb0, pb1;  // P' = p * v_scale as the B fragment of the second contraction: k = 2t, 2t+1 | 2t+8, 2t+9, n = head g
+  float alpha;        // exp2(old max - new max): what O has to be multiplied by before this tile's product is added
+};
+
+// S = q . K^T on the int8 tensor cores, running max / sum update, P'.
+__device__ __forceinline__ Scored mma_score(MmaState& st, const uint8_t* stage, int nvalid, int lane) {
   const int t = lane & 3;
   const float* sS = reinterpret_cast<const float*>(stage + 2 * kTile * kD);
-  constexpr uint32_t kMagic = 0x64646464u, kFlip = 0x80808080u;
-
-  // ---- S = q . K^T on the int8 tensor cores.  B fragment of lane (g,t): token g (first MMA
-  // group) / g+8 (second), raw code words; one 16-byte read feeds two k-steps.
+  // B fragment of lane (g,t): token g (first MMA group) / g+8 (second), raw code words; one 16-byte read feeds
+  // two k-steps.
   int c1[4] = {0, 0, 0, 0}, c2[4] = {0, 0, 0, 0};
 #pragma unroll
   for (int c = 0; c < 2; ++c) {
@@ -471,16 +442,21 @@ __device__ __forceinline__ void mma_tile(MmaState& st, const uint8_t* stage, int
   mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
   mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
   const float m_new = fmaxf(st.m, mx);
-  const float alpha = fast_exp2(st.m - m_new);
+  Scored r;
+  r.alpha = fast_exp2(st.m - m_new);
   const float p0 = fast_exp2(a[0] - m_new), p1 = fast_exp2(a[1] - m_new);  // exp2(-inf) = 0 for masked rows
   const float p2 = fast_exp2(a[2] - m_new), p3 = fast_exp2(a[3] - m_new);
-  st.l = st.l * alpha + ((p0 + p1) + (p2 + p3));
+  st.l = st.l * r.alpha + ((p0 + p1) + (p2 + p3));
   st.m = m_new;
-  // P' = p * v_scale is already the B fragment of the second contraction: k = 2t, 2t+1 | 2t+8, 2t+9, n = head g
-  const uint32_t pb0 = pack_half2(p0 * vs_a.x, p1 * vs_a.y), pb1 = pack_half2(p2 * vs_b.x, p3 * vs_b.y);
+  r.pb0 = pack_half2(p0 * vs_a.x, p1 * vs_a.y);
+  r.pb1 = pack_half2(p2 * vs_b.x, p3 * vs_b.y);
+  return r;
+}
 
-  // ---- rescale O only when some running max moved (warp-uniform test); columns 2t, 2t+1 belong to
-  // heads whose state lives in lanes 8t.. and 8t+4..
+// Rescale O when some running max moved (warp-uniform test); columns 2t, 2t+1 belong to heads whose state lives
+// in lanes 8t.. and 8t+4..
+__device__ __forceinline__ void mma_rescale(MmaState& st, float alpha, int lane) {
+  const int t = lane & 3;
   if (__any_sync(0xffffffffu, alpha != 1.f)) {
     const float al0 = __shfl_sync(0xffffffffu, alpha, 8 * t), al1 = __shfl_sync(0xffffffffu, alpha, 8 * t + 4);
 #pragma unroll
@@ -489,7 +465,11 @@ __device__ __forceinline__ void mma_tile(MmaState& st, const uint8_t* stage, int
       st.o[j][2] *= al0; st.o[j][3] *= al1;
     }
   }
-  // ---- O^T += V^T . P' : lane reads channels 16g..16g+15 of tokens 2t, 2t+1, 2t+8, 2t+9
+}
+
+// O^T += V^T . P' : lane reads channels 16g..16g+15 of tokens 2t, 2t+1, 2t+8, 2t+9; codes widened exactly to fp16.
+__device__ __forceinline__ void mma_pv(MmaState& st, const uint8_t* stage, uint32_t pb0, uint32_t pb1) {
+  constexpr uint32_t kMagic = 0x64646464u, kFlip = 0x80808080u;
   uint32_t vw[4][4];
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
@@ -654,12 +634,10 @@ __device__ __forceinline__ void scalar_end(ScalarState& st, bool whole, uint16_t
 // ------------------------------------------------------------------ main kernel
 // Workspace: int32 prefix[B+1] (padded to 256 B; read by the separate reduction kernel) |
 // int32 arrivals[B*Hkv] (padded; zero on entry, left zero: counts the partials of each (entry, head)
-// when the reduction is fused into this kernel) | pool claim counter (256 B) | float ml[R][2][G][2] |
-// float acc[R][2][G][128], R = ranges the call can have: the W warps, plus kMaxPool pool pieces for a planned call
+// when the reduction is fused into this kernel) | float ml[W][2][G][2] | float acc[W][2][G][128]
 __host__ __device__ inline size_t ws_prefix_bytes(int B) { return (((size_t)(B + 1) * 4 + 255) / 256) * 256; }
 __host__ __device__ inline size_t ws_count_bytes(int B, int Hkv) { return (((size_t)B * Hkv * 4 + 255) / 256) * 256; }
-// ... followed by 256 bytes whose first word is the pool's claim counter (zero on entry, left zero)
-__host__ __device__ inline size_t ws_head_bytes(int B, int Hkv) { return ws_prefix_bytes(B) + ws_count_bytes(B, Hkv) + 256; }
+__host__ __device__ inline size_t ws_head_bytes(int B, int Hkv) { return ws_prefix_bytes(B) + ws_count_bytes(B, Hkv); }
 
 // The pieces of one (entry, head) that reached the workspace, in tile order.  Its flat tile range
 // [s0, e) is covered by warps w_first..w_last; CTAs c_lo..c_hi-1 lie entirely inside it, each of
@@ -669,41 +647,23 @@ __host__ __device__ inline size_t ws_head_bytes(int B, int Hkv) { return ws_pref
 // (entry, head) starts inside that warp's range.
 struct Pieces {
   int w_first, n_a, w_b, n_b, w_c, n, slot_first;
-  int n_static, j_first, pool_slot_first, W;  // pool pieces follow the static ones, in tile order
-  __device__ __forceinline__ Pieces(const Partition& part, int s0, int e_all) {
-    W = part.W;
-    n_static = 0; j_first = 0; pool_slot_first = 0;
-    w_first = 0; n_a = 0; w_b = 0; n_b = 0; w_c = 0; slot_first = 0;
-    const int e = min(e_all, part.Us);  // the part of the range the static ranges cover
-    if (s0 < e) {
-      w_first = s0 / part.per;
-      const int w_last = (e - 1) / part.per;
-      const int span = kWarps * part.per;
-      const int c_lo = (s0 + span - 1) / span, c_hi = e / span;
-      slot_first = s0 > w_first * part.per ? 1 : 0;
-      if (c_hi > c_lo) {
-        w_b = kWarps * c_lo; w_c = kWarps * c_hi;
-        n_a = w_b - w_first; n_b = c_hi - c_lo;
-        n_static = n_a + n_b + (w_last - w_c + 1);
-      } else {
-        w_b = w_c = w_first; n_a = 0; n_b = 0;
-        n_static = w_last - w_first + 1;
-      }
-    }
-    n = n_static;
-    if (e_all > part.Us && part.pool_pieces() > 0) {
-      const int p0 = max(s0, part.Us);
-      j_first = part.piece_of(p0);
-      pool_slot_first = p0 > part.piece_start(j_first) ? 1 : 0;
-      n += part.piece_of(e_all - 1) - j_first + 1;
+  __device__ __forceinline__ Pieces(const Partition& part, int s0, int e) {
+    w_first = s0 / part.per;
+    const int w_last = (e - 1) / part.per;
+    const int span = kWarps * part.per;
+    const int c_lo = (s0 + span - 1) / span, c_hi = min(e, part.U) / span;
+    slot_first = s0 > w_first * part.per ? 1 : 0;
+    if (c_hi > c_lo) {
+      w_b = kWarps * c_lo; w_c = kWarps * c_hi;
+      n_a = w_b - w_first; n_b = c_hi - c_lo;
+      n = n_a + n_b + (w_last - w_c + 1);
+    } else {
+      w_b = w_c = w_first; n_a = 0; n_b = 0;
+      n = w_last - w_first + 1;
     }
   }
-  // workspace slot index (2 * range + slot) of piece k; range = warp for a static range, W + j for pool piece j
+  // workspace slot index (2 * warp + slot) of piece k
   __device__ __forceinline__ int slot_of(int k) const {
-    if (k >= n_static) {
-      const int j = j_first + (k - n_static);
-      return 2 * (W + j) + (j == j_first ? pool_slot_first : 0);
-    }
     const int w = k < n_a ? w_first + k : (k < n_a + n_b ? w_b + kWarps * (k - n_a) : w_c + (k - n_a - n_b));
     return 2 * w + (w == w_first ? slot_first : 0);
   }
@@ -830,11 +790,10 @@ __host__ __device__ inline size_t ws_ml_bytes(int W, int G) { return (((size_t)W
 // before its first copies are in flight, instead of the length scan, a binary search and a dependent
 // page-table read in each of its CTAs in each layer.
 constexpr int kPlanMagic = 0x6b765031;  // "kvP1"
-constexpr int kPlanHeaderInts = 16;     // magic, B, Hkv, W, U, per, num_decoding, page_size, Us, n1, P1, n2, P2, reserved
-constexpr int kPlanEntryInts = 16;      // b, h, tile, T, n, base, page[0..2], tiles of the range, reserved
-constexpr int kPlanThreads = 1024, kPlanCtas = 6;
-// header, one entry per warp of the grid, one entry per pool piece
-__host__ __device__ inline size_t plan_bytes(int W) { return ((size_t)kPlanHeaderInts + (size_t)(W + kMaxPool) * kPlanEntryInts) * 4; }
+constexpr int kPlanHeaderInts = 8;      // magic, B, Hkv, W, U, per, num_decoding, page_size
+constexpr int kPlanEntryInts = 16;      // b, h, tile, T, n, base, page[0..2], reserved
+constexpr int kPlanThreads = 1024;
+__host__ __device__ inline size_t plan_bytes(int W) { return ((size_t)kPlanHeaderInts + (size_t)W * kPlanEntryInts) * 4; }
 
 __global__ void __launch_bounds__(kPlanThreads)
 decode_plan_kernel(const int32_t* __restrict__ cached_lens, const int32_t* __restrict__ num_decoding,
@@ -849,35 +808,22 @@ decode_plan_kernel(const int32_t* __restrict__ cached_lens, const int32_t* __res
   int nd;
   scan_tiles(cached_lens, B, num_decoding, chunk, chunk_prefix, lens_s, nullptr, nd);
   const Lens lens{cached_lens, lens_s, nd};
-  const Partition part = make_pooled_partition(chunk_prefix[kPlanThreads], Hkv, W, nd);
-  if (blockIdx.x == 0 && threadIdx.x == 0) {
+  const Partition part = make_partition(chunk_prefix[kPlanThreads], Hkv, W, nd);
+  if (threadIdx.x == 0) {
     plan[0] = kPlanMagic; plan[1] = B; plan[2] = Hkv; plan[3] = W;
     plan[4] = part.U; plan[5] = part.per; plan[6] = nd; plan[7] = page_size;
-    plan[8] = part.Us; plan[9] = part.n1; plan[10] = part.P1; plan[11] = part.n2; plan[12] = part.P2;
-    plan[13] = plan[14] = plan[15] = 0;
   }
-  const int npool = part.pool_pieces();
-  // range r: warp r's static range, or pool piece r - W
-  for (int r = blockIdx.x * kPlanThreads + threadIdx.x; r < W + npool; r += gridDim.x * kPlanThreads) {
-    int* e = plan + kPlanHeaderInts + (size_t)r * kPlanEntryInts;
-    long long u_begin;
-    int left;
-    if (r < W) {
-      u_begin = (long long)r * part.per;
-      left = u_begin < part.Us ? min(part.per, part.Us - (int)u_begin) : 0;
-    } else {
-      u_begin = part.piece_start(r - W);
-      left = min(part.piece_start(r - W + 1), part.U) - (int)u_begin;
-    }
-    if (left <= 0) {
+  for (int w = threadIdx.x; w < W; w += kPlanThreads) {
+    int* e = plan + kPlanHeaderInts + (size_t)w * kPlanEntryInts;
+    const long long u_begin = (long long)w * part.per;
+    if (u_begin >= part.U) {
       e[0] = -1;
-      e[9] = 0;
       continue;
     }
     Cursor cur;
     cur.seek(chunk_prefix, kPlanThreads, chunk, lens, Hkv, page_size, (int)u_begin);
     e[0] = cur.b; e[1] = cur.h; e[2] = cur.tile; e[3] = cur.T; e[4] = cur.n; e[5] = cur.base;
-    e[9] = left;
+    int left = min(part.per, part.U - (int)u_begin);
     for (int i = 0; i < kStages - 1; ++i) {
       int page = -1;
       if (left > 0) {
@@ -918,9 +864,7 @@ decode_attn_kernel(const uint16_t* __restrict__ q, long long q_sb, long long q_s
   extern __shared__ __align__(128) uint8_t smem[];
   uint8_t* ring = smem;                                                       // kWarps * kStages * kTileBytes
   float* q_s = reinterpret_cast<float*>(ring + kWarps * kStages * kTileBytes);  // scalar variant: kWarps * (G*128 + G*16)
-  // where the four warps of a CTA park their pieces of one (entry, head) for the CTA-level sum: [kWarps][G*128 + G*2]
-  float* park = q_s + (kScalar ? kWarps * (kMaxG * kD + kMaxG * kTile) : 0);
-  int* chunk_prefix = reinterpret_cast<int*>(park + kWarps * (G * kD + G * 2));
+  int* chunk_prefix = reinterpret_cast<int*>(q_s + (kScalar ? kWarps * (kMaxG * kD + kMaxG * kTile) : 0));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int w = blockIdx.x * kWarps + warp;
 #ifdef B200KV_STAMPS
@@ -940,12 +884,12 @@ decode_attn_kernel(const uint16_t* __restrict__ q, long long q_sb, long long q_s
   Partition part;
   Cursor pc;  // producer position (runs kStages-1 tiles ahead of the consumer)
   int first_page = -1;  // planned: lane i < kStages-1 holds the page id of the warp's i-th tile
-  int rid = w;          // the range being processed: a warp's static range (its index) or pool piece j (W + j)
-  int ntiles = 0;       // tiles of that range
   if (plan != nullptr) {
-    // One round of independent loads: the warp's plan entry (lanes 0-15), the header (lanes 16-31),
+    // One round of independent loads: the warp's plan entry (lanes 0-15), the header (lanes 16-23),
     // num_decoding and this thread's share of the lengths.
-    int pe = __ldcg(plan + (lane < kPlanEntryInts ? kPlanHeaderInts + (size_t)w * kPlanEntryInts + lane : lane - kPlanEntryInts));
+    int pe = 0;
+    if (lane < kPlanEntryInts) pe = __ldcg(plan + kPlanHeaderInts + (size_t)w * kPlanEntryInts + lane);
+    else if (lane < kPlanEntryInts + kPlanHeaderInts) pe = __ldcg(plan + (lane - kPlanEntryInts));
     const int nd_raw = __ldcg(num_decoding);
     int cl[kSmemLens / (kWarps * 32)];
 #pragma unroll
@@ -960,16 +904,12 @@ decode_attn_kernel(const uint16_t* __restrict__ q, long long q_sb, long long q_s
       if (b < B) lens_s[b] = b < nd ? cl[i] + 1 : 0;
     }
     __syncthreads();
-    auto hdr = [&](int i) { return __shfl_sync(0xffffffffu, pe, kPlanEntryInts + i); };
-    const bool hdr_ok = hdr(0) == kPlanMagic && hdr(1) == B && hdr(2) == c.Hkv && hdr(3) == W && hdr(6) == nd &&
-                        hdr(7) == c.page_size;
-    part.U = hdr(4); part.per = hdr(5); part.W = W;
-    part.Us = hdr(8); part.n1 = hdr(9); part.P1 = hdr(10); part.n2 = hdr(11); part.P2 = hdr(12);
-    if (!hdr_ok || part.per < 1 || part.P1 < 1 || part.P2 < 1 || part.pool_pieces() > kMaxPool || part.Us > part.U) {
-      // not a plan of this batch on this grid: nothing is read or written through it
-      if (lane == 0 && status) atomicOr(status, B200KV_S_BAD_PLAN);
-      return;
-    }
+    const bool hdr_ok = __shfl_sync(0xffffffffu, pe, 16) == kPlanMagic && __shfl_sync(0xffffffffu, pe, 17) == B &&
+                        __shfl_sync(0xffffffffu, pe, 18) == c.Hkv && __shfl_sync(0xffffffffu, pe, 19) == W &&
+                        __shfl_sync(0xffffffffu, pe, 22) == nd && __shfl_sync(0xffffffffu, pe, 23) == c.page_size;
+    part.U = __shfl_sync(0xffffffffu, pe, 20);
+    part.per = __shfl_sync(0xffffffffu, pe, 21);
+    part.W = W;
     pc.b = __shfl_sync(0xffffffffu, pe, 0);
     pc.h = __shfl_sync(0xffffffffu, pe, 1);
     pc.tile = __shfl_sync(0xffffffffu, pe, 2);
@@ -977,11 +917,14 @@ decode_attn_kernel(const uint16_t* __restrict__ q, long long q_sb, long long q_s
     pc.n = __shfl_sync(0xffffffffu, pe, 4);
     pc.base = __shfl_sync(0xffffffffu, pe, 5);
     first_page = __shfl_sync(0xffffffffu, pe, 6 + (lane < kStages - 1 ? lane : 0));
-    ntiles = __shfl_sync(0xffffffffu, pe, 9);
-    if (pc.b < 0) return;  // no work for this warp (only in plans without a pool)
+    if (!hdr_ok) {  // not a plan of this batch on this grid: nothing is read or written through it
+      if (lane == 0 && status) atomicOr(status, B200KV_S_BAD_PLAN);
+      return;
+    }
+    if (pc.b < 0) return;  // no work for this warp
     const Lens probe{cached_lens, lens_s, nd};
     if (pc.b >= B || pc.h < 0 || pc.h >= c.Hkv || pc.n != probe.n(pc.b) || pc.T != probe.tiles(pc.b) || pc.tile < 0 ||
-        pc.tile >= pc.T || ntiles < 1 || ntiles > part.per) {  // the plan was made from other lengths
+        pc.tile >= pc.T || (long long)w * part.per >= part.U) {  // the plan was made from other lengths
       if (lane == 0 && status) atomicOr(status, B200KV_S_BAD_PLAN);
       return;
     }
@@ -995,285 +938,193 @@ decode_attn_kernel(const uint16_t* __restrict__ q, long long q_sb, long long q_s
     if ((long long)w * part.per >= part.U) return;
     const Lens probe{cached_lens, lens_s, nd};
     pc.seek(chunk_prefix, nchunks, chunk, probe, c.Hkv, c.page_size, w * part.per);
-    ntiles = min(part.per, part.U - w * part.per);
   }
   STAMP(8, dclk());
   const Lens lens{cached_lens, lens_s, nd};
-  const int R = plan != nullptr ? W + kMaxPool : W;  // ranges the workspace is laid out for
+  const int u0 = w * part.per;
+  const int ntiles = min(part.per, part.U - u0);
 
   int* ws_count = reinterpret_cast<int*>(workspace + ws_prefix_bytes(B));
-  int* pool_ctr = reinterpret_cast<int*>(workspace + ws_prefix_bytes(B) + ws_count_bytes(B, c.Hkv));
   float* ws_ml = reinterpret_cast<float*>(workspace + ws_head_bytes(B, c.Hkv));
-  float* ws_o = reinterpret_cast<float*>(workspace + ws_head_bytes(B, c.Hkv) + ws_ml_bytes(R, G));
+  float* ws_o = reinterpret_cast<float*>(workspace + ws_head_bytes(B, c.Hkv) + ws_ml_bytes(W, G));
   uint8_t* my_ring = ring + warp * kStages * kTileBytes;
   const uint32_t my_ring_s = smem_u32(my_ring);
   float* my_q = q_s + warp * (kMaxG * kD + kMaxG * kTile);
-  const int park_stride = G * kD + G * 2;
 
+  Cursor cc = pc;  // consumer position, advanced segment by segment
   PageWindow win{-1, 0, -1};
   const LaneCopy lc = make_lane_copy(c, lane);
-  typename std::conditional<kScalar, ScalarState, MmaState>::type st;
-  if constexpr (!kScalar) mma_init_lane(st, lane);
+
   // Early start: everything above read only the batch metadata.  q, the workspace and the newest
   // token of every sequence (the last tile) may still be in flight from the kernel launched just
   // before this one (the quantize-on-write of this layer), so those wait for it; older tiles are
   // not touched by it and are fetched right away, hiding the first burst behind that kernel.
   bool must_wait = early != 0;
-  bool first_range = true;
-  const int npool = part.pool_pieces();
-
-  // The copies run kStages-1 tiles ahead of the arithmetic and do not stop at the end of a range: when the range
-  // in hand has few tiles left to request, the warp draws a ticket for its next pool piece, fetches that piece's
-  // plan entry, and goes on requesting tiles of the new piece while it still consumes the old one.  The ticket and
-  // the entry are only looked at some tiles after they were asked for, so neither round trip stalls the warp.
-  // Every warp of the grid draws tickets until it is told the pool is empty, i.e. draws exactly one ticket beyond
-  // the pieces; the warp that draws the very last of all tickets knows that nobody will touch the counter again
-  // in this call and puts it back to zero for the next one.
-  constexpr int kClaimAhead = 6;  // tiles still to request when the ticket is drawn
-  constexpr int kEntryAhead = 3;  // ... when the plan entry of the drawn piece is fetched
-  // --- state of the copies (the producer side of the ring)
-  int p_left = ntiles;            // tiles of the range the copies are in that are not yet requested
-  int p_issued = 0;               // ... that are requested
-  int p_pages = first_page;       // lane i < kStages-1: page id of that range's i-th tile (planned calls)
-  bool copies_ahead = false;      // the copies have moved on to the range after the one being consumed
-  int stage_p = 0, inflight = 0;  // ring slot of the next request; tiles requested and not yet consumed
-  // --- the hand-over to the next range
-  int ticket = -1, next_pe = 0;   // lane 0's ticket / every lane's word of the next piece's plan entry
-  int claim_state = npool > 0 ? 0 : 3;  // 0 nothing asked, 1 ticket drawn, 2 entry fetched (or pool empty), 3 no pool
-  bool have_next = false;         // the next range is known: next_start, next_rid, next_tiles, next_pages
-  Cursor next_start = pc;
-  int next_rid = 0, next_tiles = 0, next_pages = -1;
-
-  // One step of the producer: request the next tile if one is known (returns true), and advance the hand-over by
-  // at most one stage.  Called once per consumed tile in the steady state.
-  auto request_one = [&]() -> bool {
-    if (p_left == 0 && have_next && !copies_ahead) {  // the range in hand is fully requested: move on to the next
-      pc = next_start;
-      p_left = next_tiles;
-      p_issued = 0;
-      p_pages = next_pages;
-      copies_ahead = true;
-      win.b = -1;
-    }
-    bool issued = false;
+  int p_left = ntiles;  // tiles not yet issued
+#pragma unroll
+  for (int i = 0; i < kStages - 1; ++i) {
     if (p_left > 0) {
-      if (must_wait && pc.tile == pc.T - 1) {  // first range only: the newest token comes from the kernel before
+      if (must_wait && pc.tile == pc.T - 1) {
         asm volatile("griddepcontrol.wait;" ::: "memory");
         must_wait = false;
       }
-      int page;
-      if (plan != nullptr && p_issued < kStages - 1) page = __shfl_sync(0xffffffffu, p_pages, p_issued);
-      else page = window_page(c, pc, win, lane);
-      issue_tile(c, pc, page, lc, my_ring_s + stage_p * kTileBytes, lane, status);
-      cp_async_commit();
-      stage_p = (stage_p + 1) & (kStages - 1);
-      ++inflight;
-      ++p_issued;
-      issued = true;
-      if (--p_left > 0) {
-        pc.next(lens, c.Hkv, c.page_size);
-        // planned: the table row of the tile after the plan's page ids is requested early
-        if (plan != nullptr && p_issued == kStages - 1) load_window(c, pc.b, pc.slot, win, lane);
-      } else if (npool == 0) {
-        pdl_trigger();  // this warp has nothing left to fetch
-      }
+      const int page = plan != nullptr ? __shfl_sync(0xffffffffu, first_page, i) : window_page(c, pc, win, lane);
+      issue_tile(c, pc, page, lc, my_ring_s + i * kTileBytes, lane, status);
+      if (--p_left > 0) pc.next(lens, c.Hkv, c.page_size);
     }
-    if (copies_ahead || claim_state == 3) return issued;
-    if (claim_state == 0) {
-      if (p_left <= kClaimAhead) {
-        if (lane == 0) ticket = atomicAdd(pool_ctr, 1);
-        claim_state = 1;
-      }
-    } else if (claim_state == 1) {
-      if (p_left <= kEntryAhead) {
-        ticket = __shfl_sync(0xffffffffu, ticket, 0);
-        if (ticket < npool) next_pe = __ldcg(plan + kPlanHeaderInts + (size_t)(W + ticket) * kPlanEntryInts + (lane & (kPlanEntryInts - 1)));
-        else if (ticket == npool + W - 1 && lane == 0) *pool_ctr = 0;
-        claim_state = 2;
-      }
-    } else if (p_left == 0 && !have_next && ticket < npool) {
-      next_start.b = __shfl_sync(0xffffffffu, next_pe, 0);
-      next_start.h = __shfl_sync(0xffffffffu, next_pe, 1);
-      next_start.tile = __shfl_sync(0xffffffffu, next_pe, 2);
-      next_start.T = __shfl_sync(0xffffffffu, next_pe, 3);
-      next_start.n = __shfl_sync(0xffffffffu, next_pe, 4);
-      next_start.base = __shfl_sync(0xffffffffu, next_pe, 5);
-      next_pages = __shfl_sync(0xffffffffu, next_pe, 6 + (lane < kStages - 1 ? lane : 0));
-      next_tiles = __shfl_sync(0xffffffffu, next_pe, 9);
-      next_rid = W + ticket;
-      const bool ok = next_start.b >= 0 && next_start.b < B && next_start.h >= 0 && next_start.h < c.Hkv &&
-                      next_start.T == lens.tiles(next_start.b) && next_start.tile >= 0 && next_start.tile < next_start.T &&
-                      next_tiles >= 1;
-      if (!ok) {  // cannot happen with a plan that passed the checks above; never walk off the batch
-        if (lane == 0 && status) atomicOr(status, B200KV_S_BAD_PLAN);
-        ticket = npool;  // as if the pool were empty
-      } else {
-        next_start.slot = (next_start.tile * kTile) / c.page_size;
-        next_start.row0 = next_start.tile * kTile - next_start.slot * c.page_size;
-        have_next = true;
-      }
-    }
-    return issued;
-  };
-  // Wait until the oldest of the `inflight` requested tiles has landed (one commit group per tile).
-  auto wait_oldest = [&]() {
-    if (inflight >= kStages) cp_async_wait<kStages - 1>();
-    else if (inflight == 3) cp_async_wait<2>();
-    else if (inflight == 2) cp_async_wait<1>();
-    else cp_async_wait<0>();
-    __syncwarp();
-  };
-
-  Cursor cc = pc;  // consumer position, advanced segment by segment
-  int stage_c = 0;  // ring slot of the tile consumed next
-  while (inflight < kStages - 1 && request_one()) {}
+    cp_async_commit();
+  }
   STAMP(2, dclk());
-  if (must_wait) {
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-    must_wait = false;
-  }
+  // planned: the table row of the next tile is requested now and is there when the main loop wants it
+  if (plan != nullptr && p_left > 0) load_window(c, pc.b, pc.slot, win, lane);
+  if (must_wait) asm volatile("griddepcontrol.wait;" ::: "memory");
 
-  for (;;) {  // the warp's static range, then pool pieces until the pool is empty
-    int done = 0;
-    while (done < ntiles) {
-      // one segment: the tiles [cc.tile, cc.tile + seg) of (entry cc.b, head cc.h)
-      const int seg = min(cc.T - cc.tile, ntiles - done);
-      if constexpr (kScalar) scalar_begin(st, my_q, q, q_sb, q_sh, cc.b, cc.h, G, scale_log2, lane);
-      else mma_begin(st, q, q_sb, q_sh, cc.b, cc.h, G, scale_log2, lane);
+  typename std::conditional<kScalar, ScalarState, MmaState>::type st;
+  if constexpr (!kScalar) mma_init_lane(st, lane);
+  int stage_c = 0, stage_p = kStages - 1;  // ring slots of the tile consumed / issued next
+  int done = 0;
+  cp_async_wait<kStages - 2>();  // the first tile of the range has landed (the scores of a tile are taken one step ahead)
+  __syncwarp();
+  while (done < ntiles) {
+    // one segment: the tiles [cc.tile, cc.tile + seg) of (entry cc.b, head cc.h)
+    const int seg = min(cc.T - cc.tile, ntiles - done);
+    if constexpr (kScalar) scalar_begin(st, my_q, q, q_sb, q_sh, cc.b, cc.h, G, scale_log2, lane);
+    else mma_begin(st, q, q_sb, q_sh, cc.b, cc.h, G, scale_log2, lane);
 #ifdef B200KV_STAMPS
-      if (first_range && done == 0) STAMP(9, dclk());
+    if (done == 0) STAMP(9, dclk());
 #endif
-      int remaining = cc.n - cc.tile * kTile;  // tokens from this tile to the end of the sequence
-      for (int k = 0; k < seg; ++k) {
-        while (inflight < kStages && request_one()) {}  // one request per tile in the steady state; more after a gap
-        wait_oldest();
-#ifdef B200KV_STAMPS
-        if (first_range && done == 0 && k == 0) STAMP(3, dclk());
-#endif
-        const uint8_t* stage = my_ring + stage_c * kTileBytes;
-        if constexpr (kScalar) scalar_tile(st, my_q, my_q + kMaxG * kD, stage, min(remaining, kTile), G, lane);
-        else mma_tile(st, stage, remaining, lane);
-        __syncwarp();
-        remaining -= kTile;
-        stage_c = (stage_c + 1) & (kStages - 1);
-        --inflight;
+    int remaining = cc.n - cc.tile * kTile;  // tokens from this tile to the end of the sequence
+    // The ring invariant: when the consumer is at tile k of its range, tiles k and k+1 have landed and tiles k+2,
+    // k+3 are in flight (one commit group per loop iteration, at most kStages-2 of them pending after the wait).
+    [[maybe_unused]] Scored cur_s;
+    if constexpr (!kScalar) cur_s = mma_score(st, my_ring + stage_c * kTileBytes, remaining, lane);
+    for (int k = 0; k < seg; ++k) {
+      if (p_left > 0) {
+        issue_tile(c, pc, window_page(c, pc, win, lane), lc, my_ring_s + stage_p * kTileBytes, lane, status);
+        if (--p_left > 0) pc.next(lens, c.Hkv, c.page_size);
+        else pdl_trigger();  // this warp has nothing left to fetch
       }
+      cp_async_commit();
+      cp_async_wait<kStages - 2>();
+      __syncwarp();
 #ifdef B200KV_STAMPS
-      if (first_range && done + seg >= ntiles) STAMP(4, dclk());
+      if (done == 0 && k == 0) STAMP(3, dclk());
 #endif
-      // whole iff the segment began at the sequence's first tile and reached its last one
-      const bool whole = cc.tile == 0 && seg == cc.T;
-      const int slot = done == 0 ? 0 : 1;
-      const int s0 = cc.base + cc.h * cc.T;  // flat tile range of this (entry, head): [s0, s0 + T)
-      uint16_t* out_row = out + cc.b * o_sb + (long long)(cc.h * G) * o_sh;
-      // Do all four warps of this CTA hold pieces of this same (entry, head) in their static ranges?  Then the
-      // pieces meet in shared memory and one warp forwards their sum (no global round trip for three of them).
-      const int cta_u0 = blockIdx.x * kWarps * part.per, cta_u1 = cta_u0 + kWarps * part.per;
-      const bool cta_inside = first_range && !whole && s0 <= cta_u0 && cta_u1 <= s0 + cc.T && cta_u1 <= part.Us;
-      bool deliver = !whole;                       // a piece of mine (or my CTA's sum) goes to the workspace
-      float* po = ws_o + ((size_t)rid * 2 + slot) * G * kD;
-      float* pml = ws_ml + ((size_t)rid * 2 + slot) * G * 2;
-      if (cta_inside) {
-        float* so = park + warp * park_stride;  // [G][128] then [G][2]
-        if constexpr (kScalar) scalar_end(st, false, out, o_sb, o_sh, cc.b, cc.h, G, so, so + G * kD, lane);
-        else mma_end(st, false, out, o_sb, o_sh, cc.b, cc.h, G, so, so + G * kD, lane);
-        __threadfence_block();
-        __syncwarp();
-        int t = 0;
-        if (lane == 0) t = atomicAdd(cta_arrive, 1);
-        t = __shfl_sync(0xffffffffu, t, 0);
-        deliver = t == kWarps - 1;
-        if (deliver) {  // last of the four: sum them; lane l owns channels 4l..4l+3
-          __threadfence_block();
-          const bool exact = s0 == cta_u0 && s0 + cc.T == cta_u1;  // the CTA saw the whole sequence
-          po = ws_o + ((size_t)(blockIdx.x * kWarps) * 2) * G * kD;  // slot 0 of the CTA's first warp
-          pml = ws_ml + ((size_t)(blockIdx.x * kWarps) * 2) * G * 2;
-          for (int col = 0; col < G; ++col) {
-            float m4[kWarps], M = -INFINITY;
-#pragma unroll
-            for (int i = 0; i < kWarps; ++i) {
-              m4[i] = park[i * park_stride + G * kD + col * 2];
-              M = fmaxf(M, m4[i]);
-            }
-            float L = 0.f;
-            float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-            for (int i = 0; i < kWarps; ++i) {
-              const float* sp = park + i * park_stride;
-              const float wg = fast_exp2(m4[i] - M);
-              L = fmaf(sp[G * kD + col * 2 + 1], wg, L);
-              const float4 o = *reinterpret_cast<const float4*>(sp + col * kD + 4 * lane);
-              a.x = fmaf(o.x, wg, a.x); a.y = fmaf(o.y, wg, a.y); a.z = fmaf(o.z, wg, a.z); a.w = fmaf(o.w, wg, a.w);
-            }
-            if (exact) {
-              const float inv = 1.f / L;
-              uint2 r;
-              r.x = float_to_bf16_bits(a.x * inv) | (float_to_bf16_bits(a.y * inv) << 16);
-              r.y = float_to_bf16_bits(a.z * inv) | (float_to_bf16_bits(a.w * inv) << 16);
-              *reinterpret_cast<uint2*>(out_row + col * o_sh + 4 * lane) = r;
-            } else {
-              *reinterpret_cast<float4*>(po + col * kD + 4 * lane) = a;
-              if (lane == 0) { pml[col * 2] = M; pml[col * 2 + 1] = L; }
-            }
-          }
-          if (exact) deliver = false;
-        }
+      const uint8_t* stage = my_ring + stage_c * kTileBytes;
+      const int stage_n = (stage_c + 1) & (kStages - 1);
+      if constexpr (kScalar) {
+        scalar_tile(st, my_q, my_q + kMaxG * kD, stage, min(remaining, kTile), G, lane);
       } else {
-        if constexpr (kScalar) scalar_end(st, whole, out, o_sb, o_sh, cc.b, cc.h, G, po, pml, lane);
-        else mma_end(st, whole, out, o_sb, o_sh, cc.b, cc.h, G, po, pml, lane);
+        // scores of the next tile of this segment side by side with this tile's product
+        Scored next_s = cur_s;
+        const bool more = k + 1 < seg;
+        if (more) next_s = mma_score(st, my_ring + stage_n * kTileBytes, remaining - kTile, lane);
+        mma_pv(st, stage, cur_s.pb0, cur_s.pb1);
+        if (more) mma_rescale(st, next_s.alpha, lane);
+        cur_s = next_s;
       }
-#ifdef B200KV_STAMPS
-      if (first_range && done + seg >= ntiles) STAMP(10, dclk());
-#endif
-      if (fused && deliver) {
-        // Fused cross-split reduction: the warp that delivers the last piece of (entry, head) merges
-        // all of them.  Release: partial stores -> warp barrier -> counter; acquire: counter -> warp barrier -> loads.
-        const Pieces pieces(part, s0, s0 + cc.T);
-        __syncwarp();  // the lanes' partial stores are ordered before lane 0's release below
-        int arrived = 0;
-        if (lane == 0) arrived = atom_add_acq_rel(ws_count + cc.b * c.Hkv + cc.h, 1) + 1;
-        arrived = __shfl_sync(0xffffffffu, arrived, 0);
-        if (arrived == pieces.n) {  // the acquire half makes every earlier arriver's stores visible to this warp
-          __syncwarp();
-          STAMP(11, dclk());
-          merge_partials(ws_ml, ws_o, pieces, G, out_row, o_sh, lane);
-          if (lane == 0) ws_count[cc.b * c.Hkv + cc.h] = 0;  // leave the counter zero for the next call
-#ifdef B200KV_STAMPS
-          STAMP(7, (unsigned long long)pieces.n);
-          STAMP(12, dclk());
-#endif
-        }
-      }
-      done += seg;
-      if (done < ntiles) cc.next_segment(lens, c.Hkv);
+      __syncwarp();
+      remaining -= kTile;
+      stage_c = stage_n;
+      stage_p = (stage_p + 1) & (kStages - 1);
     }
 #ifdef B200KV_STAMPS
-    if (first_range) STAMP(6, (unsigned long long)ntiles);
+    if (done + seg >= ntiles) STAMP(4, dclk());
 #endif
-    first_range = false;
-    if (claim_state == 3) break;  // no pool
-    // Ranges shorter than the look-ahead (or a ticket that came late) leave the hand-over unfinished: finish it
-    // now (request_one with nothing to request only advances the claim).
-    while (!have_next && !(claim_state == 2 && ticket >= npool)) request_one();
-    if (!have_next) break;        // the pool is empty
-    // the consumer steps into the range the copies are already working on (or are about to start: request_one
-    // moves them there on its next call)
-    rid = next_rid;
-    ntiles = next_tiles;
-    cc = next_start;
-    if (!copies_ahead) request_one();
-    have_next = false;
-    copies_ahead = false;
-    claim_state = 0;
-    ticket = -1;
+    // whole iff the segment began at the sequence's first tile and reached its last one
+    const bool whole = cc.tile == 0 && seg == cc.T;
+    const int slot = done == 0 ? 0 : 1;
+    const int s0 = cc.base + cc.h * cc.T;  // flat tile range of this (entry, head): [s0, s0 + T)
+    uint16_t* out_row = out + cc.b * o_sb + (long long)(cc.h * G) * o_sh;
+    // Do all four warps of this CTA hold pieces of this same (entry, head)?  Then the pieces meet
+    // in shared memory and one warp forwards their sum (no global round trip for three of them).
+    const int cta_u0 = blockIdx.x * kWarps * part.per, cta_u1 = cta_u0 + kWarps * part.per;
+    const bool cta_inside = !whole && s0 <= cta_u0 && cta_u1 <= s0 + cc.T && cta_u1 <= part.U;
+    bool deliver = !whole;                       // a piece of mine (or my CTA's sum) goes to the workspace
+    float* po = ws_o + ((size_t)w * 2 + slot) * G * kD;
+    float* pml = ws_ml + ((size_t)w * 2 + slot) * G * 2;
+    if (cta_inside) {
+      cp_async_wait<0>();
+      __syncwarp();
+      float* so = reinterpret_cast<float*>(my_ring);  // [G][128] then [G][2]; the ring is idle now
+      if constexpr (kScalar) scalar_end(st, false, out, o_sb, o_sh, cc.b, cc.h, G, so, so + kMaxG * kD, lane);
+      else mma_end(st, false, out, o_sb, o_sh, cc.b, cc.h, G, so, so + kMaxG * kD, lane);
+      __threadfence_block();
+      __syncwarp();
+      int t = 0;
+      if (lane == 0) t = atomicAdd(cta_arrive, 1);
+      t = __shfl_sync(0xffffffffu, t, 0);
+      deliver = t == kWarps - 1;
+      if (deliver) {  // last of the four: sum them; lane l owns channels 4l..4l+3
+        __threadfence_block();
+        const bool exact = s0 == cta_u0 && s0 + cc.T == cta_u1;  // the CTA saw the whole sequence
+        po = ws_o + ((size_t)(blockIdx.x * kWarps) * 2) * G * kD;  // slot 0 of the CTA's first warp
+        pml = ws_ml + ((size_t)(blockIdx.x * kWarps) * 2) * G * 2;
+        for (int col = 0; col < G; ++col) {
+          float m4[kWarps], M = -INFINITY;
+#pragma unroll
+          for (int i = 0; i < kWarps; ++i) {
+            m4[i] = reinterpret_cast<const float*>(ring + i * kStages * kTileBytes)[kMaxG * kD + col * 2];
+            M = fmaxf(M, m4[i]);
+          }
+          float L = 0.f;
+          float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+          for (int i = 0; i < kWarps; ++i) {
+            const float* sp = reinterpret_cast<const float*>(ring + i * kStages * kTileBytes);
+            const float wg = fast_exp2(m4[i] - M);
+            L = fmaf(sp[kMaxG * kD + col * 2 + 1], wg, L);
+            const float4 o = *reinterpret_cast<const float4*>(sp + col * kD + 4 * lane);
+            a.x = fmaf(o.x, wg, a.x); a.y = fmaf(o.y, wg, a.y); a.z = fmaf(o.z, wg, a.z); a.w = fmaf(o.w, wg, a.w);
+          }
+          if (exact) {
+            const float inv = 1.f / L;
+            uint2 r;
+            r.x = float_to_bf16_bits(a.x * inv) | (float_to_bf16_bits(a.y * inv) << 16);
+            r.y = float_to_bf16_bits(a.z * inv) | (float_to_bf16_bits(a.w * inv) << 16);
+            *reinterpret_cast<uint2*>(out_row + col * o_sh + 4 * lane) = r;
+          } else {
+            *reinterpret_cast<float4*>(po + col * kD + 4 * lane) = a;
+            if (lane == 0) { pml[col * 2] = M; pml[col * 2 + 1] = L; }
+          }
+        }
+        if (exact) deliver = false;
+      }
+    } else {
+      if constexpr (kScalar) scalar_end(st, whole, out, o_sb, o_sh, cc.b, cc.h, G, po, pml, lane);
+      else mma_end(st, whole, out, o_sb, o_sh, cc.b, cc.h, G, po, pml, lane);
+    }
+#ifdef B200KV_STAMPS
+    if (done + seg >= ntiles) STAMP(10, dclk());
+#endif
+    if (fused && deliver) {
+      // Fused cross-split reduction: the warp that delivers the last piece of (entry, head) merges
+      // all of them.  Release: partial stores -> warp barrier -> counter; acquire: counter -> warp barrier -> loads.
+      const Pieces pieces(part, s0, s0 + cc.T);
+      __syncwarp();  // the lanes' partial stores are ordered before lane 0's release below
+      int arrived = 0;
+      if (lane == 0) arrived = atom_add_acq_rel(ws_count + cc.b * c.Hkv + cc.h, 1) + 1;
+      arrived = __shfl_sync(0xffffffffu, arrived, 0);
+      if (arrived == pieces.n) {  // the acquire half makes every earlier arriver's stores visible to this warp
+        __syncwarp();
+        STAMP(11, dclk());
+        merge_partials(ws_ml, ws_o, pieces, G, out_row, o_sh, lane);
+        if (lane == 0) ws_count[cc.b * c.Hkv + cc.h] = 0;  // leave the counter zero for the next call
+#ifdef B200KV_STAMPS
+        STAMP(7, (unsigned long long)pieces.n);
+        STAMP(12, dclk());
+#endif
+      }
+    }
+    done += seg;
+    if (done < ntiles) cc.next_segment(lens, c.Hkv);
   }
-  pdl_trigger();
   cp_async_wait<0>();
 #ifdef B200KV_STAMPS
   {
     unsigned sm;
     asm volatile("mov.u32 %0, %%smid;" : "=r"(sm));
-    STAMP(0, t_entry); STAMP(1, (unsigned long long)sm); STAMP(5, gtime());
+    STAMP(0, t_entry); STAMP(1, (unsigned long long)sm); STAMP(5, gtime()); STAMP(6, (unsigned long long)ntiles);
     STAMP(13, dclk());
   }
 #endif
@@ -1355,16 +1206,12 @@ decode_combine_kernel(const uint8_t* __restrict__ workspace, const int32_t* __re
   }
 }
 
-static size_t main_smem_bytes(int G, bool scalar) {
+static size_t main_smem_bytes(int B, bool scalar) {
   size_t s = (size_t)kWarps * kStages * kTileBytes;
   if (scalar) s += (size_t)kWarps * (kMaxG * kD + kMaxG * kTile) * 4;
-  s += (size_t)kWarps * (G * kD + G * 2) * 4;  // where a CTA's warps park their pieces for the CTA-level sum
   s += (size_t)(kWarps * 32 + 1 + kSmemLens + 1) * 4;
+  (void)B;
   return s;
-}
-
-static size_t workspace_bytes_for(int B, int Hkv, int G, int ranges) {
-  return ws_head_bytes(B, Hkv) + ws_ml_bytes(ranges, G) + (size_t)ranges * 2 * G * kD * 4;
 }
 
 }  // namespace b200kv
@@ -1373,12 +1220,9 @@ using namespace b200kv;
 
 extern "C" size_t b200kv_decode_attn_workspace_bytes(int32_t B, int32_t Hq, int32_t Hkv, int32_t D, int32_t sm_count) {
   if (B < 0 || Hq < 1 || Hkv < 1 || Hq % Hkv || D != kD || sm_count < 1) return 0;
-  return workspace_bytes_for(B, Hkv, Hq / Hkv, sm_count * kCtasPerSm * kWarps);
-}
-
-extern "C" size_t b200kv_decode_attn_planned_workspace_bytes(int32_t B, int32_t Hq, int32_t Hkv, int32_t D, int32_t sm_count) {
-  if (B < 0 || Hq < 1 || Hkv < 1 || Hq % Hkv || D != kD || sm_count < 1) return 0;
-  return workspace_bytes_for(B, Hkv, Hq / Hkv, sm_count * kCtasPerSm * kWarps + kMaxPool);
+  const int G = Hq / Hkv;
+  const int W = sm_count * kCtasPerSm * kWarps;
+  return ws_head_bytes(B, Hkv) + ws_ml_bytes(W, G) + (size_t)W * 2 * G * kD * 4;
 }
 
 // Argument checks shared by the three decode-attention entry points; nothing is enqueued before they pass.
@@ -1417,7 +1261,7 @@ static int launch_decode(const void* q, int64_t q_sb, int64_t q_sh, const b200kv
   const bool scalar = (variant & 1) != 0;
   const int fused = (variant & 2) ? 0 : 1;
   const int early = ((variant & 4) && fused) ? 1 : 0;  // the separate reduction kernel's prefix array is written before the wait
-  const size_t smem = main_smem_bytes(G, scalar);
+  const size_t smem = main_smem_bytes(B, scalar);
   // the opt-in to more than 48 KB of dynamic shared memory is per function AND per device: set on every call
   cudaError_t e = scalar ? cudaFuncSetAttribute(decode_attn_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
                          : cudaFuncSetAttribute(decode_attn_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -1474,8 +1318,7 @@ extern "C" int b200kv_decode_plan(const b200kv_table* table, const int32_t* cach
   if (!aligned(plan, 16)) return B200KV_E_ALIGN;
   if (plan_bytes_given < b200kv_decode_plan_bytes(sm_count)) return B200KV_E_WORKSPACE;
   const int W = sm_count * kCtasPerSm * kWarps;
-  // a few CTAs share the ranges (each repeats the cheap length scan); none of them releases a chained successor early
-  decode_plan_kernel<<<kPlanCtas, kPlanThreads, 0, (cudaStream_t)stream>>>(cached_lens, num_decoding, table->ids, table->stride,
+  decode_plan_kernel<<<1, kPlanThreads, 0, (cudaStream_t)stream>>>(cached_lens, num_decoding, table->ids, table->stride,
                                                                    table->max_pages, page_size, B, Hkv, W, (int*)plan);
   return cudaGetLastError() == cudaSuccess ? B200KV_OK : B200KV_E_LAUNCH;
 }
@@ -1493,7 +1336,6 @@ extern "C" int b200kv_decode_attn_planned(const void* q, int64_t q_sb, int64_t q
   if (rc) return rc;
   if (variant & 2) return B200KV_E_SHAPE;  // the two-kernel reduction reads a prefix array only the unplanned kernel writes
   if (!aligned(plan, 16)) return B200KV_E_ALIGN;
-  if (workspace_bytes < b200kv_decode_attn_planned_workspace_bytes(B, Hq, cache->num_kv_heads, kD, sm_count)) return B200KV_E_WORKSPACE;
   if (plan_bytes_given < b200kv_decode_plan_bytes(sm_count)) return B200KV_E_WORKSPACE;
   return launch_decode(q, q_sb, q_sh, cache, table, cached_lens, num_decoding, scale, out, o_sb, o_sh, workspace, 0, B, Hq,
                        sm_count, variant, plan, status, stream);

@@ -238,8 +238,7 @@ def decode_attention(
         out = torch.empty(B, Hq, D, device=q.device, dtype=q.dtype)
     assert out.shape[0] >= B and out.shape[1:] == (Hq, D) and out.stride(-1) == 1
     sms = num_sms(q.device)
-    size_fn = lib.b200kv_decode_attn_workspace_bytes if plan is None else lib.b200kv_decode_attn_planned_workspace_bytes
-    nbytes = size_fn(B, Hq, Hkv, D, sms)
+    nbytes = lib.b200kv_decode_attn_workspace_bytes(B, Hq, Hkv, D, sms)
     if nbytes == 0:
         raise ValueError("decode_attention: unsupported geometry")
     workspace = decode_workspace(q.device, B, Hq, Hkv, nbytes)

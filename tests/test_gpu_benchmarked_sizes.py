@@ -79,10 +79,8 @@ def test_sweep_cells_at_ctx_4096(K, B):
         assert K.check_status() == 0
         check(H.to_f32(out), want)
         outs.append(out)
-    # At this size the plan holds back a pool of pieces that warps claim at run time: which warp takes which piece
-    # varies from call to call, the result must not.  (The unplanned call cuts the sequences elsewhere, so it agrees
-    # with the planned one to the last bf16 bit only.)
-    assert torch.equal(outs[2], outs[3]), "planned calls must be reproducible bit for bit"
+    assert torch.equal(outs[2], outs[3]), "calls must be reproducible bit for bit"
+    assert torch.equal(outs[0], outs[2]), "planned and unplanned calls share one work split"
 
 
 def test_one_shard_of_the_sequence_sharded_decode(K):
@@ -126,9 +124,7 @@ def test_one_shard_of_the_sequence_sharded_decode(K):
     torch.cuda.synchronize()
     assert K.check_status() == 0
     check(H.to_f32(plain), want)
-    check(H.to_f32(planned), want)
-    again = K.decode_attention(got_q, cache, cached, tab, nd, SCALE, plan=K.plan_decode_step(cached, tab, nd, cache))
-    assert torch.equal(planned, again), "planned calls must be reproducible bit for bit"
+    assert torch.equal(plain, planned), "planned and unplanned calls share one work split"
 
 
 @pytest.mark.parametrize("prior", [3072])

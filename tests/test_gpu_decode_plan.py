@@ -77,38 +77,6 @@ def test_planned_equals_unplanned_and_oracle(K, name, page_size):
             assert mx <= 8e-3 and mean <= 4e-4, (mx, mean)
 
 
-@pytest.mark.parametrize("page_size", [16, 64])
-def test_pool_pieces_on_a_ragged_batch(K, page_size):
-    """A batch large enough for the plan to hold back a pool (every warp has more than 24 tiles) and ragged enough
-    that pool pieces start and end inside sequences, hold several short sequences whole, and that sequences straddle
-    the border between the static ranges and the pool: against the oracle, and bit-reproducible across calls although
-    the pieces go to whichever warp asks first."""
-    from oracle import c_oracle as C
-
-    rng = np.random.default_rng(41 + page_size)
-    lens = [int(x) for x in rng.integers(1, 1300, 150)] + [int(x) for x in rng.integers(1, 140, 250)] + [4096, 3000, 17]
-    rng.shuffle(lens)
-    q, cache, cached, table = make_case(rng, lens, page_size, gauss=False)
-    B = len(lens)
-    tq, tc, tcl, ttab, tnd = H.bf16_tensor(q), H.cache_to_torch(cache), H.i32(cached), H.i32(table), H.i32([B])
-    plan = K.plan_decode_step(tcl, ttab, tnd, tc)
-    hdr = plan[:64].view(torch.int32).cpu().numpy()
-    assert hdr[9] + hdr[11] > 0 and hdr[8] < hdr[4], "this batch was meant to get a pool"
-    outs = [K.decode_attention(tq, tc, tcl, ttab, tnd, SCALE, plan=plan).clone() for _ in range(3)]
-    plain = K.decode_attention(tq, tc, tcl, ttab, tnd, SCALE)
-    torch.cuda.synchronize()
-    assert K.check_status() == 0
-    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
-    want = C.decode_attention(q, cache, cached, table, B, SCALE)
-    for got in (outs[0], plain):
-        mx, mean = H.attn_errors(H.to_f32(got), want)
-        assert mx <= 8e-3 and mean <= 4e-4, (mx, mean)
-    # the pool's claim counter is back at zero, like the arrival counters
-    ws = K.decode_workspace(tq.device, B, HQ, HKV, 1)
-    head = ws[: (B + 1 + 63) // 64 * 256 + (B * HKV + 63) // 64 * 256 + 256].view(torch.int32)
-    assert int(head[(B + 1 + 63) // 64 * 64 :].abs().sum()) == 0
-
-
 def test_plan_of_another_step_is_reported_and_writes_nothing(K):
     rng = np.random.default_rng(31)
     lens = [700, 33, 1500, 16, 257]
