@@ -79,17 +79,18 @@ __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
   __half2 h = __floats2half2_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&h);
 }
-__device__ __forceinline__ uint32_t hsub2_u32(uint32_t a, uint32_t b) {
-  __half2 r = __hsub2(*reinterpret_cast<__half2*>(&a), *reinterpret_cast<__half2*>(&b));
-  return *reinterpret_cast<uint32_t*>(&r);
-}
 template <int kOff>
 __device__ __forceinline__ void cp_async16_imm(uint32_t dst, const void* src) {  // both addresses + kOff bytes
   asm volatile("cp.async.cg.shared.global [%0+%2], [%1+%2], 16;\n" ::"r"(dst), "l"(src), "n"(kOff) : "memory");
 }
 // D += A(16x32, row, s8) * B(32x8, col, s8), s32 accumulate.
+#ifdef B200KV_MMA_VOLATILE
+#define MMA_ASM asm volatile
+#else
+#define MMA_ASM asm
+#endif
 __device__ __forceinline__ void imma16832(int (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-  asm(
+  MMA_ASM(
       "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
       : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
@@ -97,7 +98,7 @@ __device__ __forceinline__ void imma16832(int (&d)[4], const uint32_t (&a)[4], u
 // D += A(16x16, row) * B(16x8, col), fp16 inputs, fp32 accumulate.
 __device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                          uint32_t b1) {
-  asm(
+  MMA_ASM(
       "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
       : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
@@ -331,6 +332,7 @@ struct MmaState {
   uint32_t qa[4][4];  // A fragments of q for the 4 k-steps: {hi, lo, hi', lo'} words (see mma_begin)
   float sfac;         // head g: softmax_scale * log2(e) * s1 / 128
   float m, l;         // head g: running max (log2 domain, uniform over t) and this lane's share of the sum
+  float lv;           // head g: this lane's share of the sum of P' = p * v_scale (as rounded to fp16), see mma_pv
   float o[8][4];      // O^T accumulators: m-tile j, rows d = 16g+2j (+1), columns 2t, 2t+1
   uint32_t k_off[2], v_off;  // lane-constant shared-memory offsets of the fragment reads
 };
@@ -386,6 +388,7 @@ __device__ __forceinline__ void mma_begin(MmaState& st, const uint16_t* __restri
   st.sfac = g < G ? scale_log2 * s1 * (1.f / 128.f) : 0.f;
   st.m = -INFINITY;
   st.l = 0.f;
+  st.lv = 0.f;
 #pragma unroll
   for (int j = 0; j < 8; ++j)
 #pragma unroll
@@ -448,8 +451,12 @@ __device__ __forceinline__ Scored mma_score(MmaState& st, const uint8_t* stage, 
   const float p2 = fast_exp2(a[2] - m_new), p3 = fast_exp2(a[3] - m_new);
   st.l = st.l * r.alpha + ((p0 + p1) + (p2 + p3));
   st.m = m_new;
-  r.pb0 = pack_half2(p0 * vs_a.x, p1 * vs_a.y);
-  r.pb1 = pack_half2(p2 * vs_b.x, p3 * vs_b.y);
+  const __half2 h0 = __floats2half2_rn(p0 * vs_a.x, p1 * vs_a.y), h1 = __floats2half2_rn(p2 * vs_b.x, p3 * vs_b.y);
+  r.pb0 = *reinterpret_cast<const uint32_t*>(&h0);
+  r.pb1 = *reinterpret_cast<const uint32_t*>(&h1);
+  // the sum of the fp16 values the tensor core will see: what the +1152 offset of the widened codes adds per channel
+  const float2 f0 = __half22float2(h0), f1 = __half22float2(h1);
+  st.lv = st.lv * r.alpha + ((f0.x + f0.y) + (f1.x + f1.y));
   return r;
 }
 
@@ -467,7 +474,11 @@ __device__ __forceinline__ void mma_rescale(MmaState& st, float alpha, int lane)
   }
 }
 
-// O^T += V^T . P' : lane reads channels 16g..16g+15 of tokens 2t, 2t+1, 2t+8, 2t+9; codes widened exactly to fp16.
+// O'^T += (V + 1152)^T . P' : lane reads channels 16g..16g+15 of tokens 2t, 2t+1, 2t+8, 2t+9.  A code is widened to
+// fp16 by a byte permute alone: 0x6400 | (code ^ 0x80) is the half 1152 + code, exactly.  The offset is not
+// subtracted per element (a third of this function's instructions): every channel of head g collects
+// 1152 * sum(P'), and mma_end takes 1152 * lv away once.  The accumulation is fp32, so the offset costs about
+// five of its 24 bits, far below the bf16 result's eight.
 __device__ __forceinline__ void mma_pv(MmaState& st, const uint8_t* stage, uint32_t pb0, uint32_t pb1) {
   constexpr uint32_t kMagic = 0x64646464u, kFlip = 0x80808080u;
   uint32_t vw[4][4];
@@ -476,14 +487,13 @@ __device__ __forceinline__ void mma_pv(MmaState& st, const uint8_t* stage, uint3
     const uint4 raw = *reinterpret_cast<const uint4*>(stage + st.v_off + (i & 1) * kD + (i >> 1) * 8 * kD);
     vw[i][0] = raw.x ^ kFlip; vw[i][1] = raw.y ^ kFlip; vw[i][2] = raw.z ^ kFlip; vw[i][3] = raw.w ^ kFlip;
   }
-  constexpr uint32_t kBias = 0x64806480u;  // half2(1152, 1152)
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
     const uint32_t sel = (j & 1) ? 0x7362u : 0x5140u;
     const uint32_t xa = prmt(vw[0][j >> 1], vw[1][j >> 1], sel);  // tokens 2t, 2t+1: (d0,d0',d1,d1')
     const uint32_t xb = prmt(vw[2][j >> 1], vw[3][j >> 1], sel);  // tokens 2t+8, 2t+9
-    mma16816(st.o[j], hsub2_u32(prmt(xa, kMagic, 0x5140u), kBias), hsub2_u32(prmt(xa, kMagic, 0x7362u), kBias),
-             hsub2_u32(prmt(xb, kMagic, 0x5140u), kBias), hsub2_u32(prmt(xb, kMagic, 0x7362u), kBias), pb0, pb1);
+    mma16816(st.o[j], prmt(xa, kMagic, 0x5140u), prmt(xa, kMagic, 0x7362u), prmt(xb, kMagic, 0x5140u),
+             prmt(xb, kMagic, 0x7362u), pb0, pb1);
   }
 }
 
@@ -493,13 +503,18 @@ __device__ __forceinline__ void mma_end(MmaState& st, bool whole, uint16_t* __re
                                         long long o_sh, int b, int h, int G, float* __restrict__ part_o,
                                         float* __restrict__ part_ml, int lane) {
   const int g = lane >> 2, t = lane & 3;
-  float l = st.l;
+  float l = st.l, lv = st.lv;
   l += __shfl_xor_sync(0xffffffffu, l, 1);
   l += __shfl_xor_sync(0xffffffffu, l, 2);
+  lv += __shfl_xor_sync(0xffffffffu, lv, 1);
+  lv += __shfl_xor_sync(0xffffffffu, lv, 2);
 #pragma unroll
   for (int j = 0; j < 2; ++j) {
     const int col = 2 * t + j;  // this lane's output column; its softmax state lives in lanes 4*col..
     const float l_c = __shfl_sync(0xffffffffu, l, 4 * col), m_c = __shfl_sync(0xffffffffu, st.m, 4 * col);
+    const float off = 1152.f * __shfl_sync(0xffffffffu, lv, 4 * col);  // what the widened codes' offset added
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { st.o[i][j] -= off; st.o[i][2 + j] -= off; }
     if (col >= G) continue;
     if (whole) {
       const float inv = 1.f / l_c;
@@ -1002,7 +1017,6 @@ decode_attn_kernel(const uint16_t* __restrict__ q, long long q_sb, long long q_s
       if (p_left > 0) {
         issue_tile(c, pc, window_page(c, pc, win, lane), lc, my_ring_s + stage_p * kTileBytes, lane, status);
         if (--p_left > 0) pc.next(lens, c.Hkv, c.page_size);
-        else pdl_trigger();  // this warp has nothing left to fetch
       }
       cp_async_commit();
       cp_async_wait<kStages - 2>();
@@ -1018,9 +1032,17 @@ decode_attn_kernel(const uint16_t* __restrict__ q, long long q_sb, long long q_s
         // scores of the next tile of this segment side by side with this tile's product
         Scored next_s = cur_s;
         const bool more = k + 1 < seg;
+#ifdef B200KV_NO_PIPELINE
+        mma_pv(st, stage, cur_s.pb0, cur_s.pb1);
+        if (more) {
+          next_s = mma_score(st, my_ring + stage_n * kTileBytes, remaining - kTile, lane);
+          mma_rescale(st, next_s.alpha, lane);
+        }
+#else
         if (more) next_s = mma_score(st, my_ring + stage_n * kTileBytes, remaining - kTile, lane);
         mma_pv(st, stage, cur_s.pb0, cur_s.pb1);
         if (more) mma_rescale(st, next_s.alpha, lane);
+#endif
         cur_s = next_s;
       }
       __syncwarp();
@@ -1119,6 +1141,9 @@ decode_attn_kernel(const uint16_t* __restrict__ q, long long q_sb, long long q_s
     done += seg;
     if (done < ntiles) cc.next_segment(lens, c.Hkv);
   }
+  // The successor is released only now: its CTAs, brought up while this kernel still streams, would sit on the SMs
+  // waiting for it and slow it down (measured: 14-16 us per call with an earlier trigger).
+  pdl_trigger();
   cp_async_wait<0>();
 #ifdef B200KV_STAMPS
   {
