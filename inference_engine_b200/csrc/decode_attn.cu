@@ -332,7 +332,8 @@ struct MmaState {
   uint32_t qa[4][4];  // A fragments of q for the 4 k-steps: {hi, lo, hi', lo'} words (see mma_begin)
   float sfac;         // head g: softmax_scale * log2(e) * s1 / 128
   float m, l;         // head g: running max (log2 domain, uniform over t) and this lane's share of the sum
-  float lv;           // head g: this lane's share of the sum of P' = p * v_scale (as rounded to fp16), see mma_pv
+  float lv;           // head g: this lane's share of the sum of P' = p * v_scale (as rounded to fp16) since the last
+                      // mma_debias, see mma_pv
   float o[8][4];      // O^T accumulators: m-tile j, rows d = 16g+2j (+1), columns 2t, 2t+1
   uint32_t k_off[2], v_off;  // lane-constant shared-memory offsets of the fragment reads
 };
@@ -409,6 +410,7 @@ __device__ __forceinline__ void mma_init_lane(MmaState& st, int lane) {
 struct Scored {
   uint32_t pb0, pb1;  // P' = p * v_scale as the B fragment of the second contraction: k = 2t, 2t+1 | 2t+8, 2t+9, n = head g
   float alpha;        // exp2(old max - new max): what O has to be multiplied by before this tile's product is added
+  float lv;           // this lane's share of the sum of the tile's P' (as rounded to fp16)
 };
 
 // S = q . K^T on the int8 tensor cores, running max / sum update, P'.
@@ -456,7 +458,7 @@ __device__ __forceinline__ Scored mma_score(MmaState& st, const uint8_t* stage, 
   r.pb1 = *reinterpret_cast<const uint32_t*>(&h1);
   // the sum of the fp16 values the tensor core will see: what the +1152 offset of the widened codes adds per channel
   const float2 f0 = __half22float2(h0), f1 = __half22float2(h1);
-  st.lv = st.lv * r.alpha + ((f0.x + f0.y) + (f1.x + f1.y));
+  r.lv = (f0.x + f0.y) + (f1.x + f1.y);
   return r;
 }
 
@@ -471,16 +473,18 @@ __device__ __forceinline__ void mma_rescale(MmaState& st, float alpha, int lane)
       st.o[j][0] *= al0; st.o[j][1] *= al1;
       st.o[j][2] *= al0; st.o[j][3] *= al1;
     }
+    st.lv *= alpha;  // the offset that O carries is scaled with it
   }
 }
 
 // O'^T += (V + 1152)^T . P' : lane reads channels 16g..16g+15 of tokens 2t, 2t+1, 2t+8, 2t+9.  A code is widened to
 // fp16 by a byte permute alone: 0x6400 | (code ^ 0x80) is the half 1152 + code, exactly.  The offset is not
 // subtracted per element (a third of this function's instructions): every channel of head g collects
-// 1152 * sum(P'), and mma_end takes 1152 * lv away once.  The accumulation is fp32, so the offset costs about
-// five of its 24 bits, far below the bf16 result's eight.
-__device__ __forceinline__ void mma_pv(MmaState& st, const uint8_t* stage, uint32_t pb0, uint32_t pb1) {
+// 1152 * sum(P'), which mma_debias takes away again every few tiles.
+__device__ __forceinline__ void mma_pv(MmaState& st, const uint8_t* stage, const Scored& s) {
   constexpr uint32_t kMagic = 0x64646464u, kFlip = 0x80808080u;
+  const uint32_t pb0 = s.pb0, pb1 = s.pb1;
+  st.lv += s.lv;
   uint32_t vw[4][4];
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
@@ -497,24 +501,38 @@ __device__ __forceinline__ void mma_pv(MmaState& st, const uint8_t* stage, uint3
   }
 }
 
+// Take the offset of the widened codes out of O: every channel of head `col` has collected 1152 * (sum of P' of that
+// head since the last call).  Done every kDebiasTiles tiles, so that the offset never grows far beyond the products
+// it rides on and the fp32 accumulation keeps its precision however long the sequence is.
+constexpr int kDebiasTiles = 8;
+__device__ __forceinline__ void mma_debias(MmaState& st, int lane) {
+  const int t = lane & 3;
+  float lv = st.lv;
+  lv += __shfl_xor_sync(0xffffffffu, lv, 1);
+  lv += __shfl_xor_sync(0xffffffffu, lv, 2);
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    const float off = 1152.f * __shfl_sync(0xffffffffu, lv, 4 * (2 * t + j));
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { st.o[i][j] -= off; st.o[i][2 + j] -= off; }
+  }
+  st.lv = 0.f;
+}
+
 // Finish an (entry, head) segment: final bf16 rows when the warp saw every tile, otherwise an
 // fp32 partial (acc[G][128], m[G], l[G]) in the given workspace slot.
 __device__ __forceinline__ void mma_end(MmaState& st, bool whole, uint16_t* __restrict__ out, long long o_sb,
                                         long long o_sh, int b, int h, int G, float* __restrict__ part_o,
                                         float* __restrict__ part_ml, int lane) {
   const int g = lane >> 2, t = lane & 3;
-  float l = st.l, lv = st.lv;
+  mma_debias(st, lane);
+  float l = st.l;
   l += __shfl_xor_sync(0xffffffffu, l, 1);
   l += __shfl_xor_sync(0xffffffffu, l, 2);
-  lv += __shfl_xor_sync(0xffffffffu, lv, 1);
-  lv += __shfl_xor_sync(0xffffffffu, lv, 2);
 #pragma unroll
   for (int j = 0; j < 2; ++j) {
     const int col = 2 * t + j;  // this lane's output column; its softmax state lives in lanes 4*col..
     const float l_c = __shfl_sync(0xffffffffu, l, 4 * col), m_c = __shfl_sync(0xffffffffu, st.m, 4 * col);
-    const float off = 1152.f * __shfl_sync(0xffffffffu, lv, 4 * col);  // what the widened codes' offset added
-#pragma unroll
-    for (int i = 0; i < 8; ++i) { st.o[i][j] -= off; st.o[i][2 + j] -= off; }
     if (col >= G) continue;
     if (whole) {
       const float inv = 1.f / l_c;
@@ -1033,14 +1051,15 @@ decode_attn_kernel(const uint16_t* __restrict__ q, long long q_sb, long long q_s
         Scored next_s = cur_s;
         const bool more = k + 1 < seg;
 #ifdef B200KV_NO_PIPELINE
-        mma_pv(st, stage, cur_s.pb0, cur_s.pb1);
+        mma_pv(st, stage, cur_s);
         if (more) {
           next_s = mma_score(st, my_ring + stage_n * kTileBytes, remaining - kTile, lane);
           mma_rescale(st, next_s.alpha, lane);
         }
 #else
         if (more) next_s = mma_score(st, my_ring + stage_n * kTileBytes, remaining - kTile, lane);
-        mma_pv(st, stage, cur_s.pb0, cur_s.pb1);
+        mma_pv(st, stage, cur_s);
+        if ((k & (kDebiasTiles - 1)) == kDebiasTiles - 1) mma_debias(st, lane);
         if (more) mma_rescale(st, next_s.alpha, lane);
 #endif
         cur_s = next_s;
