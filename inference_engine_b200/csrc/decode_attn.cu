@@ -84,13 +84,8 @@ __device__ __forceinline__ void cp_async16_imm(uint32_t dst, const void* src) { 
   asm volatile("cp.async.cg.shared.global [%0+%2], [%1+%2], 16;\n" ::"r"(dst), "l"(src), "n"(kOff) : "memory");
 }
 // D += A(16x32, row, s8) * B(32x8, col, s8), s32 accumulate.
-#ifdef B200KV_MMA_VOLATILE
-#define MMA_ASM asm volatile
-#else
-#define MMA_ASM asm
-#endif
 __device__ __forceinline__ void imma16832(int (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-  MMA_ASM(
+  asm(
       "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
       : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
@@ -98,7 +93,7 @@ __device__ __forceinline__ void imma16832(int (&d)[4], const uint32_t (&a)[4], u
 // D += A(16x16, row) * B(16x8, col), fp16 inputs, fp32 accumulate.
 __device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                          uint32_t b1) {
-  MMA_ASM(
+  asm(
       "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
       : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
@@ -403,10 +398,10 @@ __device__ __forceinline__ void mma_init_lane(MmaState& st, int lane) {
   st.v_off = kTile * kD + 2 * t * kD + ((g ^ (2 * t)) << 4);
 }
 
-// One tile is processed in three steps that the main loop overlaps across tiles: the scores of tile k+1 (int8
-// tensor cores, softmax bookkeeping) are independent of the P.V product of tile k (fp16 tensor cores), so the two
-// are issued side by side and hide each other's latencies; the rescaling of O by tile k+1's correction comes after
-// tile k's product, which is the order the plain online softmax has.
+// One tile is processed in three steps: scores and softmax bookkeeping (int8 tensor cores), the rescaling of O by
+// the tile's correction, and the P.V product (fp16 tensor cores).  (Taking the scores of tile k+1 ahead of tile k's
+// product, to overlap the two dependency chains, was measured: no gain at 64 sequences x 4096 tokens, and the ring
+// slot it ties up costs 3-7 % on larger batches.)
 struct Scored {
   uint32_t pb0, pb1;  // P' = p * v_scale as the B fragment of the second contraction: k = 2t, 2t+1 | 2t+8, 2t+9, n = head g
   float alpha;        // exp2(old max - new max): what O has to be multiplied by before this tile's product is added
@@ -1016,8 +1011,6 @@ decode_attn_kernel(const uint16_t* __restrict__ q, long long q_sb, long long q_s
   if constexpr (!kScalar) mma_init_lane(st, lane);
   int stage_c = 0, stage_p = kStages - 1;  // ring slots of the tile consumed / issued next
   int done = 0;
-  cp_async_wait<kStages - 2>();  // the first tile of the range has landed (the scores of a tile are taken one step ahead)
-  __syncwarp();
   while (done < ntiles) {
     // one segment: the tiles [cc.tile, cc.tile + seg) of (entry cc.b, head cc.h)
     const int seg = min(cc.T - cc.tile, ntiles - done);
@@ -1027,46 +1020,29 @@ decode_attn_kernel(const uint16_t* __restrict__ q, long long q_sb, long long q_s
     if (done == 0) STAMP(9, dclk());
 #endif
     int remaining = cc.n - cc.tile * kTile;  // tokens from this tile to the end of the sequence
-    // The ring invariant: when the consumer is at tile k of its range, tiles k and k+1 have landed and tiles k+2,
-    // k+3 are in flight (one commit group per loop iteration, at most kStages-2 of them pending after the wait).
-    [[maybe_unused]] Scored cur_s;
-    if constexpr (!kScalar) cur_s = mma_score(st, my_ring + stage_c * kTileBytes, remaining, lane);
     for (int k = 0; k < seg; ++k) {
       if (p_left > 0) {
         issue_tile(c, pc, window_page(c, pc, win, lane), lc, my_ring_s + stage_p * kTileBytes, lane, status);
         if (--p_left > 0) pc.next(lens, c.Hkv, c.page_size);
       }
       cp_async_commit();
-      cp_async_wait<kStages - 2>();
+      cp_async_wait<kStages - 1>();
       __syncwarp();
 #ifdef B200KV_STAMPS
       if (done == 0 && k == 0) STAMP(3, dclk());
 #endif
       const uint8_t* stage = my_ring + stage_c * kTileBytes;
-      const int stage_n = (stage_c + 1) & (kStages - 1);
       if constexpr (kScalar) {
         scalar_tile(st, my_q, my_q + kMaxG * kD, stage, min(remaining, kTile), G, lane);
       } else {
-        // scores of the next tile of this segment side by side with this tile's product
-        Scored next_s = cur_s;
-        const bool more = k + 1 < seg;
-#ifdef B200KV_NO_PIPELINE
-        mma_pv(st, stage, cur_s);
-        if (more) {
-          next_s = mma_score(st, my_ring + stage_n * kTileBytes, remaining - kTile, lane);
-          mma_rescale(st, next_s.alpha, lane);
-        }
-#else
-        if (more) next_s = mma_score(st, my_ring + stage_n * kTileBytes, remaining - kTile, lane);
-        mma_pv(st, stage, cur_s);
+        const Scored s = mma_score(st, stage, remaining, lane);
+        mma_rescale(st, s.alpha, lane);
+        mma_pv(st, stage, s);
         if ((k & (kDebiasTiles - 1)) == kDebiasTiles - 1) mma_debias(st, lane);
-        if (more) mma_rescale(st, next_s.alpha, lane);
-#endif
-        cur_s = next_s;
       }
       __syncwarp();
       remaining -= kTile;
-      stage_c = stage_n;
+      stage_c = (stage_c + 1) & (kStages - 1);
       stage_p = (stage_p + 1) & (kStages - 1);
     }
 #ifdef B200KV_STAMPS
