@@ -84,6 +84,11 @@ inline int check_cache(const b200kv_cache* c, const b200kv_table* t) {
     return B200KV_E_ALIGN;
   if (c->stride_tok < kD || (c->stride_tok % 16) || (c->stride_head % 16) || (c->stride_page % 16)) return B200KV_E_ALIGN;
   if ((c->sstride_head % 4) || (c->sstride_page % 4) || (c->cstride_head % 4) || (c->cstride_page % 4)) return B200KV_E_ALIGN;
+  // the kernels multiply ids by strides in 32 x 32 -> 64 bit arithmetic
+  const int64_t strides[] = {c->stride_page, c->stride_head, c->stride_tok, c->sstride_page, c->sstride_head,
+                             c->cstride_page, c->cstride_head};
+  for (int64_t s : strides)
+    if (s < 0 || s > 0x7fffffffLL) return B200KV_E_RANGE;
   return B200KV_OK;
 }
 

@@ -287,10 +287,13 @@ __device__ __forceinline__ void issue_tile(const CacheView& c, const Cursor& cur
     if (lane == 0 && status) atomicOr(status, page == -2 ? B200KV_S_BAD_POSITION : B200KV_S_BAD_PAGE);
     page = 0;
   }
-  const long long code_off = page * c.stride_page + cur.h * c.stride_head + cur.row0 * c.stride_tok + lc.g_off;
+  // strides fit 32 bits (checked on the host): each product is one widening multiply-add
+  const long long code_off = (long long)page * (int)c.stride_page + (long long)cur.h * (int)c.stride_head +
+                             (cur.row0 * (int)c.stride_tok + (int)lc.g_off);
   const int8_t* ksrc = c.k + code_off;
   const int8_t* vsrc = c.v + code_off;
-  const float* ssrc = (lane < 16 ? c.k_scale : c.v_scale) + page * c.sstride_page + cur.h * c.sstride_head + cur.row0;
+  const float* ssrc = (lane < 16 ? c.k_scale : c.v_scale) +
+                      ((long long)page * (int)c.sstride_page + (long long)cur.h * (int)c.sstride_head + cur.row0);
   if (ok && nvalid >= kTile) {  // the common case: a full tile, no predicates
     if (c.stride_tok == kD) {   // rows are contiguous: 4 rows further is +512 bytes on both sides
       cp_async16_imm<0>(sbase + lc.k_dst, ksrc);
