@@ -249,6 +249,10 @@ int b200kv_get_chained_launch(void);
  * HEAD COUNTS (the counters' place depends on them; zero-fill again before changing shape).  Two
  * calls that overlap on the GPU must not share a workspace. */
 size_t b200kv_decode_attn_workspace_bytes(int32_t B, int32_t Hq, int32_t Hkv, int32_t D, int32_t sm_count);
+/* The part of that workspace that has to be zero: its first b200kv_decode_attn_workspace_zero_bytes(B, Hkv) bytes
+ * (the arrival counters).  What lies behind them (the split partials) is written before it is read in every call
+ * and may hold anything, NaNs included. */
+size_t b200kv_decode_attn_workspace_zero_bytes(int32_t B, int32_t Hkv);
 
 /* Replaces decode_attention (kernels.py:272-361): split-K GQA decode attention over the int8
  * cache with in-kernel dequantization, one new token per entry, followed by the cross-split

@@ -70,6 +70,7 @@ SIGNATURES = {
     "b200kv_set_chained_launch": (None, [c_int32]),
     "b200kv_get_chained_launch": (c_int32, []),
     "b200kv_decode_attn_workspace_bytes": (c_size_t, [c_int32, c_int32, c_int32, c_int32, c_int32]),
+    "b200kv_decode_attn_workspace_zero_bytes": (c_size_t, [c_int32, c_int32]),
     "b200kv_decode_attn": (c_int32, [c_void_p, c_int64, c_int64, P_CACHE, P_TABLE, c_void_p, c_void_p, c_float, c_void_p,
                                      c_int64, c_int64, c_void_p, c_size_t, c_int32, c_int32, c_int32, c_int32, c_void_p,
                                      c_void_p]),

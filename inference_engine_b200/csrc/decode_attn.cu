@@ -1254,6 +1254,11 @@ extern "C" size_t b200kv_decode_attn_workspace_bytes(int32_t B, int32_t Hq, int3
   return ws_head_bytes(B, Hkv) + ws_ml_bytes(W, G) + (size_t)W * 2 * G * kD * 4;
 }
 
+extern "C" size_t b200kv_decode_attn_workspace_zero_bytes(int32_t B, int32_t Hkv) {
+  if (B < 0 || Hkv < 1) return 0;
+  return ws_head_bytes(B, Hkv);
+}
+
 // Argument checks shared by the three decode-attention entry points; nothing is enqueued before they pass.
 static int check_decode_args(const void* q, int64_t q_sb, int64_t q_sh, const b200kv_cache* cache,
                              const b200kv_table* table, const int32_t* cached_lens, const int32_t* num_decoding,
