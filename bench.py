@@ -1541,10 +1541,20 @@ def run_sweep(args):
                 times.append(e0.elapsed_time(e1) * 1e3 / L)
             us = statistics.median(times)
             gbs = nbytes / us / 1e3
+            parity = None
+            if not args.no_parity:
+                # the graph's last call left `out` = attention over the last cache: up to four of its sequences
+                # are recomputed by the CPU oracle
+                sample = sorted({0, B // 3, (2 * B) // 3, B - 1})
+                res = oracle_sample_check(K, caches[-1], table.cpu().numpy(), np.full(B, n), sample,
+                                          out[sample].cpu().reshape(-1, HQ, D), q_rot=q[sample].float().cpu().numpy())
+                parity = {k: (round(v, 6) if isinstance(v, float) else v) for k, v in res.items() if k != "sequences"}
+                if not res["within_gate"]:
+                    raise SystemExit(f"sweep cell B={B} ctx={n}: output differs from the oracle: {res}")
             print(json.dumps({"B": B, "ctx": n, "layers_in_graph": L, "us_per_call": round(us, 2),
                               "us_min": round(min(times), 2), "gbs": round(gbs, 1), "pct_of_8TBs": round(gbs / 80.0, 2),
                               "frac_of_measured": round(gbs / peak, 4), "in_sweep_config": (B, n) not in dropped,
-                              "bytes": nbytes}), flush=True)
+                              "planned": not args.no_plan, "bytes": nbytes, "parity": parity}), flush=True)
             del caches, graph
             torch.cuda.empty_cache()
 

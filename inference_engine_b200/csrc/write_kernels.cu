@@ -96,16 +96,18 @@ __device__ __forceinline__ void norm_rope_regs(const HeadRow& row, float eps, fl
   unpack4(row.c, c);
   unpack4(row.s, s);
   float ss = sum_squares_ordered(x, sq, lane);
-  float rstd = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)kD), eps)));
+  // ss / 128 as a product with 2^-7: both are the correctly rounded value of the same real number
+  static_assert(kD == 128, "the mean is taken with a power-of-two factor");
+  float rstd = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fmul_rn(ss, 0.0078125f), eps)));
+  // First half: y1*c - y2*s with y1 = mine, y2 = the partner's; second half: y1*s + y2*c with y1 = the partner's,
+  // y2 = mine.  Both are mine*c + partner*(-+s): subtracting is adding the negated product and the sum commutes,
+  // so one expression with a signed sine gives the same bits as the two of the reference.
   const bool first_half = lane < 16;
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     float y = __fmul_rn(__fmul_rn(x[i], rstd), wv[i]);
     float other = __shfl_xor_sync(0xffffffffu, y, 16);
-    float y1 = first_half ? y : other;
-    float y2 = first_half ? other : y;
-    out[i] = first_half ? __fsub_rn(__fmul_rn(y1, c[i]), __fmul_rn(y2, s[i]))
-                        : __fadd_rn(__fmul_rn(y1, s[i]), __fmul_rn(y2, c[i]));
+    out[i] = __fadd_rn(__fmul_rn(y, c[i]), __fmul_rn(other, first_half ? -s[i] : s[i]));
   }
 }
 
@@ -116,15 +118,24 @@ __device__ __forceinline__ float warp_max(float v) {
 }
 
 // Per-row absmax int8 quantizer (kernels.py:460-470, 475-480, 798-811): writes the 128 codes
-// of one head row (4 per lane) and its scale.
+// of one head row (4 per lane) and its scale.  code = rint(x / scale) with the IEEE quotient: the quotient is
+// first estimated as x * (127 / amax) with an approximate reciprocal (2 ulp), which is within 6e-5 of it for
+// |x / scale| <= 127.5 (the rounding of scale itself, the approximate division, the product); only when that
+// estimate lies within 2e-4 of a rounding boundary (k + 0.5) can the two round to different integers, and only
+// then is the division carried out.  The estimate does not wait for the division that produces the stored scale.
 __device__ __forceinline__ void quantize_store(const float (&x)[4], int8_t* code_row, float* scale_ptr, int lane) {
   float amax = fmaxf(fmaxf(fabsf(x[0]), fabsf(x[1])), fmaxf(fabsf(x[2]), fabsf(x[3])));
   amax = warp_max(amax);
-  float scale = __fdiv_rn(fmaxf(amax, 1e-6f), 127.0f);
+  const float floor_max = fmaxf(amax, 1e-6f);
+  const float scale = __fdiv_rn(floor_max, 127.0f);
+  // (the approximate division returns 0 for divisors above 2^126: such rows take the exact reciprocal)
+  const float inv = amax < 1e30f ? __fdividef(127.0f, floor_max) : __frcp_rn(scale);
   uint32_t packed = 0;
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    float r = rintf(__fdiv_rn(x[i], scale));
+    const float est = __fmul_rn(x[i], inv);
+    float r = rintf(est);
+    if (fabsf(fabsf(__fsub_rn(est, r)) - 0.5f) < 2e-4f) r = rintf(__fdiv_rn(x[i], scale));
     r = fminf(fmaxf(r, -127.0f), 127.0f);
     packed |= (static_cast<uint32_t>(static_cast<int>(r)) & 0xFFu) << (8 * i);
   }
