@@ -43,6 +43,7 @@ constexpr int kCtasPerSm = 3;
 constexpr int kStages = 4;                // tiles in flight per warp
 constexpr int kTileBytes = 2 * kTile * kD + 2 * kTile * 4;  // K, V codes + K, V scales = 4224
 constexpr int kDeepTiles = 224;           // tiles per warp from which the full look-ahead of the ring pays
+constexpr int kShallowFloor = 8;          // ... and up to which a warp's few tiles are all requested at once
 constexpr int kMaxG = 8;                  // query heads per kv head the MMA n-dimension can hold
 constexpr int kMaxB = 1 << 20;
 static_assert((kStages & (kStages - 1)) == 0, "ring indices are masked");
@@ -171,16 +172,26 @@ __device__ void scan_tiles(const int32_t* __restrict__ cached_lens, int B, const
 }
 
 // `per` = tiles per warp.  Never below the even share; the floor below it trades parallelism against
-// hand-offs: a piece that goes through the workspace costs about as much as 8 tiles of work, so
-// short sequences (<= 32 tiles: a whole one fits a warp, or exactly a CTA of 4 x 8) use pieces of
-// 8 tiles, longer ones pieces of 4 (64 tokens, the reference's MIN_PIECE, kernels.py:295).
+// hand-offs: a piece that goes through the workspace costs about as much as 8 tiles of work, but the four pieces
+// of a CTA that covers exactly one (entry, head) meet in shared memory and cost nothing of the kind.  So short
+// sequences (32 tiles or fewer on average) are cut into quarters of the average length (2..8 tiles) when the grid
+// has warps to spare for that: in a batch of equal lengths every CTA then owns exactly one (entry, head), and its
+// four warps fetch the few tiles side by side instead of one warp streaming all of them (5.8 instead of 10.3 us
+// for one 128-token sequence).  When the quarters would not fit the grid, short sequences use pieces of 8 tiles
+// (a whole sequence per warp, or exactly a CTA of 4 x 8); longer ones pieces of 4 (64 tokens, the reference's
+// MIN_PIECE, kernels.py:295).
 __host__ __device__ __forceinline__ Partition make_partition(int total_tiles_one_head, int Hkv, int W, int num_entries) {
   Partition p;
   p.U = total_tiles_one_head * Hkv;
   p.W = W;
-  const int min_tiles = (num_entries > 0 && total_tiles_one_head <= 32 * num_entries) ? 8 : 4;
-  int per = (p.U + W - 1) / W;
-  p.per = per > min_tiles ? per : min_tiles;
+  const int share = (p.U + W - 1) / W;
+  int min_tiles = 4;
+  if (num_entries > 0 && total_tiles_one_head <= 32 * num_entries) {
+    int quarter = (total_tiles_one_head + 4 * num_entries - 1) / (4 * num_entries);  // <= 8
+    if (quarter < 2) quarter = 2;
+    min_tiles = share <= quarter ? quarter : 8;
+  }
+  p.per = share > min_tiles ? share : min_tiles;
   return p;
 }
 
@@ -1015,7 +1026,9 @@ decode_attn_kernel(const uint16_t* __restrict__ q, long long q_sb, long long q_s
   if constexpr (!kScalar) mma_init_lane(st, lane);
   int stage_c = 0, stage_p = kStages - 1;  // ring slots of the tile consumed / issued next
   int done = 0;
-  const bool deep = part.per > kDeepTiles;
+  // ... and a warp with only a handful of tiles has nothing to gain from holding one back: the grid is far from
+  // loading the memory system and its time is the latency of its few tiles
+  const bool deep = part.per > kDeepTiles || part.per <= kShallowFloor;
   while (done < ntiles) {
     // one segment: the tiles [cc.tile, cc.tile + seg) of (entry cc.b, head cc.h)
     const int seg = min(cc.T - cc.tile, ntiles - done);
@@ -1285,10 +1298,10 @@ static int launch_decode(const void* q, int64_t q_sb, int64_t q_sh, const b200kv
   const int Hkv = cache->num_kv_heads;
   const int G = Hq / Hkv;
   const int W = sm_count * kCtasPerSm * kWarps;
-  // Only CTAs that can have work are launched: a warp never takes fewer than 4 tiles, and no entry has
+  // Only CTAs that can have work are launched: a warp never takes fewer than 2 tiles, and no entry has
   // more tiles than its table row can address.
   const long long max_tiles = (long long)B * Hkv * (((long long)table->max_pages * cache->page_size + kTile - 1) / kTile);
-  const long long want = (max_tiles + 4 * kWarps - 1) / (4 * kWarps);
+  const long long want = (max_tiles + 2 * kWarps - 1) / (2 * kWarps);
   const int grid = (int)std::max<long long>(1, std::min<long long>(sm_count * kCtasPerSm, want));
   const float scale_log2 = scale * 1.4426950408889634f;
   cudaStream_t s = (cudaStream_t)stream;
