@@ -719,6 +719,13 @@ def run_decode_model(args):
             ts.append(e0.elapsed_time(e1))
         return statistics.median(ts), res
 
+    tuned = None
+    if args.tune:
+        # what the reference's Engine does before capturing its graphs (engine.py:91-103): each weight shape is timed
+        # with both matmuls at this step's row count and the faster is kept
+        L0 = model.layers[0]
+        K.tune_linear([L0["qkv"], L0["o"], L0["gate_up"], L0["down"], model.embed], [B])
+        tuned = {f"{N}x{Kd}": s for (N, Kd, M), s in sorted(K.use_skinny.items()) if M == B}
     step_ms, toks = graph_ms(step)
     path_ms, _ = graph_ms(path_only)
     kv_bytes = S.LAYERS * (B * n * 2112 + B * WRITE_BYTES_PER_TOKEN)
@@ -726,6 +733,7 @@ def run_decode_model(args):
         "case": "pure decode step of the random-init decoder", "batch": B, "ctx": n, "layers": S.LAYERS,
         "step_ms": round(step_ms, 3), "tokens_per_s": round(B / step_ms * 1e3), "attention_path_ms": round(path_ms, 3),
         "attention_path_share": round(path_ms / step_ms, 3), "attention_path_gbs": round(kv_bytes / path_ms / 1e6, 1),
+        "matmul_cluster_size_by_weight (0 = cuBLAS)": tuned,
         "status": K.check_status(dev), "sampled_head": toks[:4].tolist(), "data": "synthetic ids, random-init weights"}), flush=True)
 
 
@@ -1580,6 +1588,7 @@ def main():
     ap.add_argument("--seqs", type=int, default=2048, help="--sharded: concurrent sequences over all GPUs")
     ap.add_argument("--serve", action="store_true", help="offline serving run of the step loop on the random-init decoder")
     ap.add_argument("--decode-model", action="store_true", help="pure decode step of the random-init decoder (B, ctx)")
+    ap.add_argument("--tune", action="store_true", help="--decode-model: let tune_linear pick the matmul per weight shape first")
     ap.add_argument("--path", action="store_true", help="each op of the mixed step's attention path timed alone")
     ap.add_argument("--prefill", action="store_true", help="chunked-prefill attention kernel alone, both kernels")
     ap.add_argument("--mixed", action="store_true", help="chunked-prefill + decode step inside the decoder scaffold")

@@ -33,7 +33,7 @@ namespace b200kv {
 
 constexpr int kSkRows = 128;     // weight rows per CTA
 constexpr int kSkStep = 64;      // channels per pipeline slot (128 bytes: one swizzle atom)
-constexpr int kSkStages = 6;
+constexpr int kSkStages = 4;
 constexpr int kSkThreads = 192;  // producer warp, issuing warp, four epilogue warps
 constexpr uint32_t kSkWBytes = kSkRows * kSkStep * 2;  // 16 KB
 constexpr uint32_t kSkSpin = 1u << 20;
@@ -102,7 +102,7 @@ __device__ __forceinline__ void sk_tmem_ld<16>(uint32_t taddr, uint32_t (&u)[16]
 
 // kT = token columns of the accumulator (M rounded up to 16, 32 or 64).
 template <int kT>
-__global__ void __launch_bounds__(kSkThreads, 1)
+__global__ void __launch_bounds__(kSkThreads, 2)
 skinny_linear_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
                      uint16_t* __restrict__ y, long long ldy, int M, int K, int S, int32_t* status) {
   extern __shared__ uint8_t sk_raw[];

@@ -6,8 +6,9 @@ qwen3-1.7b/kernels.py (LayerKVCache :11-17, decode_attention :272-361, fused_rop
 dequantize_kv_prefix :935-970, prefill_attention :1129-1175, silu_mul :1204-1212,
 add_rms_norm :1261-1285, sample :1341-1370), backed by hand-written sm_100a CUDA kernels
 reached through the C ABI in include/b200kv.h.  There is no Triton, no other backend and no
-CPU fallback: without a CUDA device and the built library every op raises.  `linear` and
-`tune_linear` (:1465-1485) stay plain PyTorch (cuBLAS through F.linear).
+CPU fallback: without a CUDA device and the built library every op raises.  `linear`
+(:1430-1463) is cuBLAS through F.linear unless `tune_linear` (:1465-1485) measured the library's
+weight-streaming matmul (`skinny_matmul`, :1373-1428) faster for that weight and row count.
 
 One generalisation: wherever the reference takes `slot_ids [B]` (one contiguous cache row per
 sequence), a 2-D int32 block table `[B, max_pages]` is accepted as well, in which case the
