@@ -1298,10 +1298,13 @@ static int launch_decode(const void* q, int64_t q_sb, int64_t q_sh, const b200kv
   const int Hkv = cache->num_kv_heads;
   const int G = Hq / Hkv;
   const int W = sm_count * kCtasPerSm * kWarps;
-  // Only CTAs that can have work are launched: a warp never takes fewer than 2 tiles, and no entry has
-  // more tiles than its table row can address.
+  // Only CTAs that can have work are launched.  No entry has more tiles than its table row can address; a warp takes
+  // at least 4 tiles, except in a batch of short sequences (32 tiles or fewer on average, make_partition), where it
+  // takes at least 2 - and such a batch has at most 32 B Hkv tiles, i.e. 4 B Hkv CTAs.
   const long long max_tiles = (long long)B * Hkv * (((long long)table->max_pages * cache->page_size + kTile - 1) / kTile);
-  const long long want = (max_tiles + 2 * kWarps - 1) / (2 * kWarps);
+  const long long want_long = (max_tiles + 4 * kWarps - 1) / (4 * kWarps);
+  const long long want_short = std::min<long long>((max_tiles + 2 * kWarps - 1) / (2 * kWarps), 4LL * B * Hkv);
+  const long long want = std::max(want_long, want_short);
   const int grid = (int)std::max<long long>(1, std::min<long long>(sm_count * kCtasPerSm, want));
   const float scale_log2 = scale * 1.4426950408889634f;
   cudaStream_t s = (cudaStream_t)stream;
