@@ -23,6 +23,7 @@ struct CacheView {
   long long sstride_page, sstride_head;
   long long cstride_page, cstride_head;
   int num_pages, Hkv, page_size;
+  int page_shift;  // log2(page_size) when that is a power of two, else -1 (split_pos divides)
   const int32_t* table;
   int table_stride, max_pages;
 };
@@ -34,6 +35,9 @@ inline CacheView make_view(const b200kv_cache* c, const b200kv_table* t) {
   w.sstride_page = c->sstride_page; w.sstride_head = c->sstride_head;
   w.cstride_page = c->cstride_page; w.cstride_head = c->cstride_head;
   w.num_pages = c->num_pages; w.Hkv = c->num_kv_heads; w.page_size = c->page_size;
+  w.page_shift = -1;
+  for (int sft = 0; sft < 31; ++sft)
+    if (c->page_size == (1 << sft)) w.page_shift = sft;
   w.table = t->ids; w.table_stride = t->stride; w.max_pages = t->max_pages;
   return w;
 }
@@ -92,6 +96,32 @@ inline int check_cache(const b200kv_cache* c, const b200kv_table* t) {
   return B200KV_OK;
 }
 
+// Token position -> (table column, row inside the page).
+__device__ __forceinline__ void split_pos(const CacheView& c, int pos, int& slot, int& prow) {
+  if (c.page_shift >= 0) {
+    slot = pos >> c.page_shift;
+    prow = pos & (c.page_size - 1);
+  } else {
+    slot = pos / c.page_size;
+    prow = pos - slot * c.page_size;
+  }
+}
+// Element offsets into the cache tensors.  Every stride is below 2^31 (check_cache), so each product is one
+// 32 x 32 -> 64 bit multiply-add, and the part inside a page fits 32 bits.
+__device__ __forceinline__ long long code_offset(const CacheView& c, int page, int head, int prow) {
+  return (long long)page * (int)c.stride_page + (head * (int)c.stride_head + prow * (int)c.stride_tok);
+}
+__device__ __forceinline__ long long scale_offset(const CacheView& c, int page, int head, int prow) {
+  return (long long)page * (int)c.sstride_page + (head * (int)c.sstride_head + prow);
+}
+__device__ __forceinline__ long long cal_offset(const CacheView& c, int page, int head) {
+  return (long long)page * (int)c.cstride_page + head * (int)c.cstride_head;
+}
+// Row r, head j of a packed activation tensor whose strides (elements) are below 2^31 (checked on the host).
+__device__ __forceinline__ long long act_offset(int r, long long s_row, int j, long long s_head) {
+  return (long long)r * (int)s_row + j * (int)s_head;
+}
+
 __device__ __forceinline__ float bf16_bits_to_float(uint32_t bits16) { return __uint_as_float(bits16 << 16); }
 
 __device__ __forceinline__ uint32_t float_to_bf16_bits(float x) {
@@ -100,7 +130,8 @@ __device__ __forceinline__ uint32_t float_to_bf16_bits(float x) {
 
 // Page id of token position `pos` of entry b, or -1 (and a status bit) when out of range.
 __device__ __forceinline__ int lookup_page(const CacheView& c, int b, int pos, int32_t* status) {
-  int slot = pos / c.page_size;
+  int slot, prow;
+  split_pos(c, pos, slot, prow);
   if (pos < 0 || slot >= c.max_pages) {
     if (status) atomicOr(status, B200KV_S_BAD_POSITION);
     return -1;

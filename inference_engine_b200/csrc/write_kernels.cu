@@ -128,14 +128,15 @@ __device__ __forceinline__ void quantize_store(const float (&x)[4], int8_t* code
   amax = warp_max(amax);
   const float floor_max = fmaxf(amax, 1e-6f);
   const float scale = __fdiv_rn(floor_max, 127.0f);
-  // (the approximate division returns 0 for divisors above 2^126: such rows take the exact reciprocal)
-  const float inv = amax < 1e30f ? __fdividef(127.0f, floor_max) : __frcp_rn(scale);
+  // (the approximate division returns 0 for divisors above 2^126: rows with such values divide every element)
+  const float inv = __fdividef(127.0f, floor_max);
+  const float band = amax < 1e30f ? 2e-4f : __int_as_float(0x7f800000);
   uint32_t packed = 0;
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     const float est = __fmul_rn(x[i], inv);
     float r = rintf(est);
-    if (fabsf(fabsf(__fsub_rn(est, r)) - 0.5f) < 2e-4f) r = rintf(__fdiv_rn(x[i], scale));
+    if (fabsf(fabsf(__fsub_rn(est, r)) - 0.5f) < band) r = rintf(__fdiv_rn(x[i], scale));
     r = fminf(fmaxf(r, -127.0f), 127.0f);
     packed |= (static_cast<uint32_t>(static_cast<int>(r)) & 0xFFu) << (8 * i);
   }
@@ -174,17 +175,18 @@ write_decode_kernel(const uint16_t* __restrict__ q, long long q_sb, long long q_
   const bool is_q = job < Hq, is_k = !is_q && job < Hq + Hkv;
   const int j = is_q ? job : (is_k ? job - Hq : job - Hq - Hkv);
   HeadRow row;
-  if (is_q) row = load_head_row(q + b * q_sb + j * q_sh, qw, cosp + b * cos_sb, sinp + b * sin_sb, lane);
-  else if (is_k) row = load_head_row(k + b * k_sb + j * k_sh, kw, cosp + b * cos_sb, sinp + b * sin_sb, lane);
-  else row.x = *reinterpret_cast<const uint2*>(v + b * v_sb + j * v_sh + 4 * lane);
+  if (is_q) row = load_head_row(q + act_offset(b, q_sb, j, q_sh), qw, cosp + (long long)b * (int)cos_sb, sinp + (long long)b * (int)sin_sb, lane);
+  else if (is_k) row = load_head_row(k + act_offset(b, k_sb, j, k_sh), kw, cosp + (long long)b * (int)cos_sb, sinp + (long long)b * (int)sin_sb, lane);
+  else row.x = *reinterpret_cast<const uint2*>(v + act_offset(b, v_sb, j, v_sh) + 4 * lane);
   // Round two, issued as soon as round one's metadata is there: the page of the new token and the calibration.
-  const int slot = pos / c.page_size;
+  int slot, prow;
+  split_pos(c, pos, slot, prow);
   const bool pos_ok = pos >= 0 && slot < c.max_pages;
   int page = (!is_q && pos_ok) ? trow[slot] : 0;
   const bool page0_ok = page0 >= 0 && page0 < c.num_pages;
   float cal[4] = {1.f, 1.f, 1.f, 1.f};
   if ((is_q || is_k) && page0_ok)
-    load4_f32(c.k_cal + page0 * c.cstride_page + (is_q ? j / (Hq / Hkv) : j) * c.cstride_head, lane, cal);
+    load4_f32(c.k_cal + cal_offset(c, page0, is_q ? j / (Hq / Hkv) : j), lane, cal);
   if ((is_q || is_k) && !page0_ok) {
     if (lane == 0 && status) atomicOr(status, B200KV_S_BAD_PAGE);
     return;
@@ -199,23 +201,20 @@ write_decode_kernel(const uint16_t* __restrict__ q, long long q_sb, long long q_
       return;
     }
   }
-  const int prow = pos % c.page_size;
   float r[4];
   if (is_q) {
     norm_rope_regs(row, eps, sq, lane, r);
 #pragma unroll
     for (int i = 0; i < 4; ++i) r[i] = __fmul_rn(r[i], cal[i]);
-    store4_bf16(q_out + b * o_sb + j * o_sh, lane, r);
+    store4_bf16(q_out + act_offset(b, o_sb, j, o_sh), lane, r);
   } else if (is_k) {
     norm_rope_regs(row, eps, sq, lane, r);
 #pragma unroll
     for (int i = 0; i < 4; ++i) r[i] = __fdiv_rn(r[i], cal[i]);
-    quantize_store(r, c.k + page * c.stride_page + j * c.stride_head + prow * c.stride_tok,
-                   c.k_scale + page * c.sstride_page + j * c.sstride_head + prow, lane);
+    quantize_store(r, c.k + code_offset(c, page, j, prow), c.k_scale + scale_offset(c, page, j, prow), lane);
   } else {
     unpack4(row.x, r);
-    quantize_store(r, c.v + page * c.stride_page + j * c.stride_head + prow * c.stride_tok,
-                   c.v_scale + page * c.sstride_page + j * c.sstride_head + prow, lane);
+    quantize_store(r, c.v + code_offset(c, page, j, prow), c.v_scale + scale_offset(c, page, j, prow), lane);
   }
 }
 
@@ -239,12 +238,12 @@ norm_rope_prefill_kernel(const uint16_t* __restrict__ q, long long q_sn, long lo
   pdl_wait();  // q and k come from the kernel before this one
   float r[4];
   if (job < Hq) {
-    norm_rope_head(q + n * q_sn + job * q_sh, qw, cosp + n * cos_sn, sinp + n * sin_sn, eps, sq_all[warp], lane, r);
-    store4_bf16(q_out + n * qo_sn + job * qo_sh, lane, r);
+    norm_rope_head(q + act_offset(n, q_sn, job, q_sh), qw, cosp + (long long)n * (int)cos_sn, sinp + (long long)n * (int)sin_sn, eps, sq_all[warp], lane, r);
+    store4_bf16(q_out + act_offset(n, qo_sn, job, qo_sh), lane, r);
   } else {
     const int j = job - Hq;
-    norm_rope_head(k + n * k_sn + j * k_sh, kw, cosp + n * cos_sn, sinp + n * sin_sn, eps, sq_all[warp], lane, r);
-    store4_bf16(k_out + n * ko_sn + j * ko_sh, lane, r);
+    norm_rope_head(k + act_offset(n, k_sn, j, k_sh), kw, cosp + (long long)n * (int)cos_sn, sinp + (long long)n * (int)sin_sn, eps, sq_all[warp], lane, r);
+    store4_bf16(k_out + act_offset(n, ko_sn, j, ko_sh), lane, r);
   }
 }
 
@@ -294,7 +293,8 @@ __device__ __forceinline__ RowEntry find_row_entry(const int32_t* __restrict__ c
 
 // The cache row of token position `pos` of entry b: page id from the table (bounds-checked, status bit on failure).
 __device__ __forceinline__ int page_of(const CacheView& c, int b, int pos, int32_t* status, int lane) {
-  const int slot = pos / c.page_size;
+  int slot, prow;
+  split_pos(c, pos, slot, prow);
   if (pos < 0 || slot >= c.max_pages) {
     if (lane == 0 && status) atomicOr(status, B200KV_S_BAD_POSITION);
     return -1;
@@ -340,9 +340,9 @@ prefill_rows_kernel(const uint16_t* __restrict__ q, long long q_sn, long long q_
   if (kFusedNorm && !is_q && !is_k && !prefilling) return;
   pdl_wait();  // q, k, v come from the kernel before this one
   HeadRow row;
-  if (kFusedNorm && is_q) row = load_head_row(q + r * q_sn + j * q_sh, qw, cosp + r * cos_sn, sinp + r * sin_sn, lane);
-  else if (kFusedNorm && is_k) row = load_head_row(k + r * k_sn + j * k_sh, kw, cosp + r * cos_sn, sinp + r * sin_sn, lane);
-  else row.x = *reinterpret_cast<const uint2*>((is_k ? k + r * k_sn + j * k_sh : v + r * v_sn + j * v_sh) + 4 * lane);
+  if (kFusedNorm && is_q) row = load_head_row(q + act_offset(r, q_sn, j, q_sh), qw, cosp + (long long)r * (int)cos_sn, sinp + (long long)r * (int)sin_sn, lane);
+  else if (kFusedNorm && is_k) row = load_head_row(k + act_offset(r, k_sn, j, k_sh), kw, cosp + (long long)r * (int)cos_sn, sinp + (long long)r * (int)sin_sn, lane);
+  else row.x = *reinterpret_cast<const uint2*>((is_k ? k + act_offset(r, k_sn, j, k_sh) : v + act_offset(r, v_sn, j, v_sh)) + 4 * lane);
   // round two: the page of this row's token and the entry's calibration
   const bool quantizes = prefilling && !is_q && !(is_k && first_chunk);
   const int pos = re.cached + (r - re.start);
@@ -355,7 +355,7 @@ prefill_rows_kernel(const uint16_t* __restrict__ q, long long q_sn, long long q_
         if (lane == 0 && status) atomicOr(status, B200KV_S_BAD_PAGE);
         page = -1;
       } else {
-        load4_f32(c.k_cal + re.page0 * c.cstride_page + j * c.cstride_head, lane, cal);
+        load4_f32(c.k_cal + cal_offset(c, re.page0, j), lane, cal);
       }
     }
   }
@@ -363,25 +363,24 @@ prefill_rows_kernel(const uint16_t* __restrict__ q, long long q_sn, long long q_
   if (kFusedNorm && (is_q || is_k)) {
     norm_rope_regs(row, eps, sq_all[kFusedNorm ? warp : 0], lane, x);
     if (is_q) {
-      store4_bf16(q_out + r * qo_sn + j * qo_sh, lane, x);
+      store4_bf16(q_out + act_offset(r, qo_sn, j, qo_sh), lane, x);
       return;
     }
-    store4_bf16(k_out + r * ko_sn + j * ko_sh, lane, x);
+    store4_bf16(k_out + act_offset(r, ko_sn, j, ko_sh), lane, x);
 #pragma unroll
     for (int i = 0; i < 4; ++i) x[i] = bf16_bits_to_float(float_to_bf16_bits(x[i]));  // the quantizer reads the stored bf16
   } else {
     unpack4(row.x, x);
   }
   if (!quantizes || page < 0) return;
-  const int prow = pos % c.page_size;
+  int slot_unused, prow;
+  split_pos(c, pos, slot_unused, prow);
   if (is_k) {
 #pragma unroll
     for (int i = 0; i < 4; ++i) x[i] = __fdiv_rn(x[i], cal[i]);
-    quantize_store(x, c.k + page * c.stride_page + j * c.stride_head + prow * c.stride_tok,
-                   c.k_scale + page * c.sstride_page + j * c.sstride_head + prow, lane);
+    quantize_store(x, c.k + code_offset(c, page, j, prow), c.k_scale + scale_offset(c, page, j, prow), lane);
   } else {
-    quantize_store(x, c.v + page * c.stride_page + j * c.stride_head + prow * c.stride_tok,
-                   c.v_scale + page * c.sstride_page + j * c.sstride_head + prow, lane);
+    quantize_store(x, c.v + code_offset(c, page, j, prow), c.v_scale + scale_offset(c, page, j, prow), lane);
   }
 }
 
@@ -428,8 +427,9 @@ first_chunk_k_kernel(const uint16_t* __restrict__ k, long long k_sn, long long k
 #pragma unroll
       for (int i = 0; i < kKeepRows; ++i) {  // independent loads: all in flight together
         const int t = s0 + wid + i * nw;
-        keep[i] = t < s1 ? *reinterpret_cast<const uint2*>(kcol + t * k_sn) : make_uint2(0u, 0u);
-        const int slot = (t - s0) / c.page_size;
+        keep[i] = t < s1 ? *reinterpret_cast<const uint2*>(kcol + (long long)t * (int)k_sn) : make_uint2(0u, 0u);
+        int slot, prow_unused;
+        split_pos(c, t - s0, slot, prow_unused);
         keep_page[i] = (t < s1 && slot < c.max_pages) ? c.table[(long long)b * c.table_stride + slot] : -2;
       }
 #pragma unroll
@@ -441,7 +441,7 @@ first_chunk_k_kernel(const uint16_t* __restrict__ k, long long k_sn, long long k
       }
       for (int t = s0 + wid + kKeepRows * nw; t < s1; t += nw) {  // chunks beyond kKeepRows * 128 rows
         float x[4];
-        unpack4(*reinterpret_cast<const uint2*>(kcol + t * k_sn), x);
+        unpack4(*reinterpret_cast<const uint2*>(kcol + (long long)t * (int)k_sn), x);
 #pragma unroll
         for (int j = 0; j < 4; ++j) m[j] = fmaxf(m[j], fabsf(x[j]));
       }
@@ -474,7 +474,7 @@ first_chunk_k_kernel(const uint16_t* __restrict__ k, long long k_sn, long long k
       const bool page0_ok = page0 >= 0 && page0 < c.num_pages;
       if (!page0_ok && crank == 0 && threadIdx.x == 0 && status) atomicOr(status, B200KV_S_BAD_PAGE);
       if (crank == 0 && threadIdx.x < kD && page0_ok)
-        c.k_cal[page0 * c.cstride_page + h * c.cstride_head + threadIdx.x] = cal_s[threadIdx.x];
+        c.k_cal[cal_offset(c, page0, h) + threadIdx.x] = cal_s[threadIdx.x];
       float cal[4];
       load4_f32(cal_s, lane, cal);
       auto quantize_row = [&](int t, uint2 raw, int page) {
@@ -487,9 +487,9 @@ first_chunk_k_kernel(const uint16_t* __restrict__ k, long long k_sn, long long k
           if (lane == 0 && status) atomicOr(status, page == -2 ? B200KV_S_BAD_POSITION : B200KV_S_BAD_PAGE);
           return;
         }
-        const int prow = pos % c.page_size;
-        quantize_store(x, c.k + page * c.stride_page + h * c.stride_head + prow * c.stride_tok,
-                       c.k_scale + page * c.sstride_page + h * c.sstride_head + prow, lane);
+        int slot_unused, prow;
+        split_pos(c, pos, slot_unused, prow);
+        quantize_store(x, c.k + code_offset(c, page, h, prow), c.k_scale + scale_offset(c, page, h, prow), lane);
       };
 #pragma unroll
       for (int i = 0; i < kKeepRows; ++i) {
@@ -497,8 +497,9 @@ first_chunk_k_kernel(const uint16_t* __restrict__ k, long long k_sn, long long k
         if (t < s1) quantize_row(t, keep[i], keep_page[i]);
       }
       for (int t = s0 + wid + kKeepRows * nw; t < s1; t += nw) {
-        const int slot = (t - s0) / c.page_size;
-        quantize_row(t, *reinterpret_cast<const uint2*>(kcol + t * k_sn),
+        int slot, prow_unused;
+        split_pos(c, t - s0, slot, prow_unused);
+        quantize_row(t, *reinterpret_cast<const uint2*>(kcol + (long long)t * (int)k_sn),
                      slot < c.max_pages ? c.table[(long long)b * c.table_stride + slot] : -2);
       }
       __syncthreads();  // part / cal_s are reused by the next entry
@@ -535,7 +536,8 @@ dequant_prefix_kernel(CacheView c, const int32_t* __restrict__ cu_cached, int nu
   const int page0 = lookup_page(c, b, 0, status);
   const int page = lookup_page(c, b, t, status);
   if (page0 < 0 || page < 0) return;
-  const int row = t % c.page_size;
+  int slot_unused, row;
+  split_pos(c, t, slot_unused, row);
   pdl_wait();  // the cache is written by the kernels before this one
   constexpr int kHeadsAtOnce = 4;
   for (int h0 = 0; h0 < c.Hkv; h0 += kHeadsAtOnce) {
@@ -544,13 +546,13 @@ dequant_prefix_kernel(CacheView c, const int32_t* __restrict__ cu_cached, int nu
 #pragma unroll
     for (int i = 0; i < kHeadsAtOnce; ++i) {
       const int h = min(h0 + i, c.Hkv - 1);
-      const long long coff = page * c.stride_page + h * c.stride_head + row * c.stride_tok + 4 * lane;
-      const long long soff = page * c.sstride_page + h * c.sstride_head + row;
+      const long long coff = code_offset(c, page, h, row) + 4 * lane;
+      const long long soff = scale_offset(c, page, h, row);
       kc[i] = *reinterpret_cast<const uint32_t*>(c.k + coff);
       vc[i] = *reinterpret_cast<const uint32_t*>(c.v + coff);
       ks[i] = c.k_scale[soff];
       vs[i] = c.v_scale[soff];
-      load4_f32(c.k_cal + page0 * c.cstride_page + h * c.cstride_head, lane, cal[i]);
+      load4_f32(c.k_cal + cal_offset(c, page0, h), lane, cal[i]);
     }
 #pragma unroll
     for (int i = 0; i < kHeadsAtOnce; ++i) {
@@ -572,7 +574,8 @@ dequant_prefix_kernel(CacheView c, const int32_t* __restrict__ cu_cached, int nu
 }
 
 static inline int launch_status() { return cudaGetLastError() == cudaSuccess ? B200KV_OK : B200KV_E_LAUNCH; }
-static inline bool stride_ok4(long long s) { return (s % 4) == 0; }
+// strides of bf16 tensors: whole 8-byte groups, and below 2^31 elements (the kernels multiply them in 32 bits)
+static inline bool stride_ok4(long long s) { return (s % 4) == 0 && s >= 0 && s <= 0x7fffffffLL; }
 
 }  // namespace b200kv
 
