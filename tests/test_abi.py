@@ -61,6 +61,24 @@ def test_invalid_arguments_launch_nothing():
     assert rc == -1  # cache pointers are NULL
 
 
+def test_cache_strides_must_fit_32_bits():
+    """The kernels form offsets from 32 x 32 -> 64 bit products: a stride of 2^31 or more is refused on the host
+    (made-up aligned addresses: validation never dereferences them and nothing is launched)."""
+    from inference_engine_b200 import _lib
+
+    lib = _lib.load()
+    fake = 0x10000
+    cache = _lib.Cache(fake, fake, fake, fake, fake, 8 * 16 * 128, 16 * 128, 128, 8 * 16, 16, 8 * 128, 128, 4, 8, 16, 128)
+    table = _lib.Table(fake, 4, 4)
+    args = (ctypes.byref(cache), ctypes.byref(table), fake, 1, fake, fake, 128, 1024, 4, None, None)
+    # in range: validation passes and the call goes on to launch, which is not done without a GPU here
+    cache.stride_page = 1 << 31
+    assert lib.b200kv_dequant_prefix(*args) == -6
+    cache.stride_page = 8 * 16 * 128
+    cache.sstride_page = -4
+    assert lib.b200kv_dequant_prefix(*args) == -6
+
+
 def test_dropin_module_exports_reference_names():
     from inference_engine_b200 import kernels
 
