@@ -10,8 +10,13 @@
 //     kWarps warps).  Every warp therefore streams the same number of bytes (+-1 tile);
 //   * a warp walks its range; whenever it finishes its part of an (entry, head) it either
 //     writes the final bf16 output (it saw the whole sequence) or an fp32 partial
-//     (acc, m, l) into one of its two workspace slots;
-//   * a second small kernel merges the partials of every split (entry, head).
+//     (acc, m, l) into one of its two workspace slots; the four warps of a CTA that hold pieces
+//     of the same (entry, head) add them in shared memory first;
+//   * the warp that delivers the last piece of an (entry, head) merges all of them (an arrival
+//     counter per (entry, head) in the workspace); `variant` bit 1 leaves the merge to a second
+//     small kernel instead, as the reference does;
+//   * the split can be read from a per-step plan (decode_plan_kernel) instead of being
+//     re-derived by every CTA of every layer's call.
 //
 // Data movement: every warp owns a private ring of kStages tiles in shared memory, filled
 // with 16-byte cp.async copies (K tile 2 KB, V tile 2 KB, 2 x 16 scales) that complete in the
@@ -26,8 +31,9 @@
 //                    the scores of head g for tokens 2t, 2t+1, 2t+8, 2t+9 - exactly the P' fragment
 //                    the second contraction wants, so no shuffles sit between the two.
 //     O^T[d, head] += V^T[d, tok] . P'[tok, head]   fp16 x fp16 -> fp32, mma.m16n8k16.  Codes are
-//                    widened exactly with byte permutes (0x6400 | (code ^ 0x80) == 1152 + code, then
-//                    minus 1152); P' = p * v_scale.
+//                    widened exactly with byte permutes (0x6400 | (code ^ 0x80) == 1152 + code); the
+//                    offset is taken out of O every kDebiasTiles tiles as 1152 x the sum of P'
+//                    (mma_debias); P' = p * v_scale.
 // Softmax state is fp32 in registers; scores use exp2 with log2(e) folded into the scale.
 // Variant 1 does the same with fp32 FMAs on the CUDA cores and exists for cross-checking.
 #include <algorithm>
