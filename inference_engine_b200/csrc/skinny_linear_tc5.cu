@@ -57,7 +57,7 @@ __device__ __forceinline__ bool sk_mbar_wait(uint32_t bar, uint32_t parity, uint
 __device__ __forceinline__ void sk_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1;\n\t}\n" ::"r"(bar), "r"(bytes) : "memory");
 }
-// Tensor-map tile load (no multicast: every CTA fetches its own boxes of this GPU's memory).  c0 is a multiple of
+// Tensor-map tile load into this CTA alone (every CTA fetches its own boxes of this GPU's memory).  c0 is a multiple of
 // 64 bf16 = 128 bytes, so the 16-byte rule of the innermost coordinate holds.
 __device__ __forceinline__ void sk_tma_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
   asm volatile(
