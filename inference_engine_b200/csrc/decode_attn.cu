@@ -1035,14 +1035,6 @@ decode_attn_kernel(const uint16_t* __restrict__ q, long long q_sb, long long q_s
   // ... and a warp with only a handful of tiles has nothing to gain from holding one back: the grid is far from
   // loading the memory system and its time is the latency of its few tiles
   const bool deep = part.per > kDeepTiles || part.per <= kShallowFloor;
-  // With the shallow wait the tile after the current one has landed too, so its scores (int8 product, softmax) can
-  // be taken while the current tile's P.V product is in the tensor pipe: the two dependent chains of a tile overlap
-  // (97.9 instead of 99.3 us per call at B = 64 x 4096, 2.75 instead of 2.86 ms per step, same GPU).
-  [[maybe_unused]] const bool pipelined = !kScalar && !deep;
-  if (pipelined) {
-    cp_async_wait<kStages - 2>();  // the first tile of the range has landed
-    __syncwarp();
-  }
   while (done < ntiles) {
     // one segment: the tiles [cc.tile, cc.tile + seg) of (entry cc.b, head cc.h)
     const int seg = min(cc.T - cc.tile, ntiles - done);
@@ -1052,39 +1044,7 @@ decode_attn_kernel(const uint16_t* __restrict__ q, long long q_sb, long long q_s
     if (done == 0) STAMP(9, dclk());
 #endif
     int remaining = cc.n - cc.tile * kTile;  // tokens from this tile to the end of the sequence
-    if constexpr (!kScalar) {
-      if (pipelined) {
-        // Ring invariant: when the consumer is at tile k of its range, tiles k and k+1 have landed and tiles k+2,
-        // k+3 are in flight (one commit group per iteration, at most kStages-2 of them pending after the wait).
-        Scored cur_s = mma_score(st, my_ring + stage_c * kTileBytes, remaining, lane);
-        for (int k = 0; k < seg; ++k) {
-          if (p_left > 0) {
-            issue_tile(c, pc, window_page(c, pc, win, lane), lc, my_ring_s + stage_p * kTileBytes, lane, status);
-            if (--p_left > 0) pc.next(lens, c.Hkv, c.page_size);
-          }
-          cp_async_commit();
-          cp_async_wait<kStages - 2>();
-          __syncwarp();
-#ifdef B200KV_STAMPS
-          if (done == 0 && k == 0) STAMP(3, dclk());
-#endif
-          const uint8_t* stage = my_ring + stage_c * kTileBytes;
-          const int stage_n = (stage_c + 1) & (kStages - 1);
-          Scored next_s = cur_s;
-          const bool more = k + 1 < seg;
-          if (more) next_s = mma_score(st, my_ring + stage_n * kTileBytes, remaining - kTile, lane);
-          mma_pv(st, stage, cur_s);
-          if ((k & (kDebiasTiles - 1)) == kDebiasTiles - 1) mma_debias(st, lane);
-          if (more) mma_rescale(st, next_s.alpha, lane);
-          cur_s = next_s;
-          __syncwarp();
-          remaining -= kTile;
-          stage_c = stage_n;
-          stage_p = (stage_p + 1) & (kStages - 1);
-        }
-      }
-    }
-    for (int k = 0; k < (pipelined ? 0 : seg); ++k) {
+    for (int k = 0; k < seg; ++k) {
       if (p_left > 0) {
         issue_tile(c, pc, window_page(c, pc, win, lane), lc, my_ring_s + stage_p * kTileBytes, lane, status);
         if (--p_left > 0) pc.next(lens, c.Hkv, c.page_size);
