@@ -358,6 +358,10 @@ class Engine:
             self.fill_mixed(Step([], 0), n)
             self.mixed_graphs[n] = self.capture_graph(lambda n=n: self.forward_mixed(n))
         self.torch.cuda.synchronize()
+        # the warm-up steps ran on all-idle inputs: a status bit here is a fault of the path, not of the data
+        bits = self.K.check_status(self.device)
+        if bits:
+            raise RuntimeError(f"device status word {bits:#x} set while the step graphs were captured")
 
     def run_decode(self, step: Step) -> list[int]:
         torch = self.torch

@@ -62,7 +62,9 @@ def status_word(device: torch.device) -> torch.Tensor:
     idx = device.index if device.index is not None else torch.cuda.current_device()
     t = _status.get(idx)
     if t is None:
-        t = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
+        # a normal tensor even when the first op runs under torch.inference_mode(): check_status clears it in place
+        with torch.inference_mode(False):
+            t = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
         _status[idx] = t
     return t
 
@@ -239,6 +241,11 @@ def decode_attention(
         out = torch.empty(B, Hq, D, device=q.device, dtype=q.dtype)
     assert out.shape[0] >= B and out.shape[1:] == (Hq, D) and out.stride(-1) == 1
     sms = num_sms(q.device)
+    if plan is not None:
+        # The plan was made for all entries of cached_lens (plan_decode_step), and the kernel checks that.  q and out
+        # need only hold the rows of the decoding entries, which come first: a caller that packs tokens (a mixed
+        # step with fewer tokens than entries) may pass fewer rows than entries.
+        B = cached_lens.shape[0]
     nbytes = lib.b200kv_decode_attn_workspace_bytes(B, Hq, Hkv, D, sms)
     if nbytes == 0:
         raise ValueError("decode_attention: unsupported geometry")

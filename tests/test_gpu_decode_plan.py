@@ -77,6 +77,30 @@ def test_planned_equals_unplanned_and_oracle(K, name, page_size):
             assert mx <= 8e-3 and mean <= 4e-4, (mx, mean)
 
 
+def test_planned_call_with_fewer_query_rows_than_entries(K):
+    """A mixed step packs tokens: its decoding entries come first with one row each, and a step with fewer tokens
+    than entries passes q / out with fewer rows than cached_lens has entries.  The plan covers all entries; the
+    planned call must accept that and give the unplanned result (it once compared q's row count with the plan's
+    entry count and refused the plan)."""
+    rng = np.random.default_rng(77)
+    lens = [300, 17, 2049, 64] + [1] * 9  # 13 entries, the first 4 decoding
+    q, cache, cached, table = make_case(rng, lens, 16)
+    nd, rows = 4, 6  # six packed token rows, thirteen entries
+    tq, tc, tcl, ttab, tnd = H.bf16_tensor(q[:rows]), H.cache_to_torch(cache), H.i32(cached), H.i32(table), H.i32([nd])
+    plain = torch.full((rows, HQ, D), 7.0, dtype=torch.bfloat16, device="cuda")
+    planned = plain.clone()
+    K.decode_attention(tq, tc, tcl, ttab, tnd, SCALE, out=plain)
+    plan = K.plan_decode_step(tcl, ttab, tnd, tc)
+    K.decode_attention(tq, tc, tcl, ttab, tnd, SCALE, out=planned, plan=plan)
+    torch.cuda.synchronize()
+    assert K.check_status() == 0
+    assert torch.equal(plain, planned)
+    assert np.all(H.to_f32(planned)[nd:] == 7.0)
+    want = O.decode_attention(q, cache, cached, table, nd, SCALE)
+    mx, mean = H.attn_errors(H.to_f32(planned)[:nd], want[:nd])
+    assert mx <= 8e-3 and mean <= 4e-4, (mx, mean)
+
+
 def test_plan_of_another_step_is_reported_and_writes_nothing(K):
     rng = np.random.default_rng(31)
     lens = [700, 33, 1500, 16, 257]
