@@ -286,7 +286,9 @@ int b200kv_decode_attn(const void* q, int64_t q_stride_b, int64_t q_stride_h,
  * b200kv_decode_attn reading that plan: same arguments, same result bit for bit, but each CTA starts its copies
  * after one round of loads instead of a length scan, a search and a dependent page-table read.
  * Contract: between b200kv_decode_plan and the last planned call that uses the plan, cached_lens, *num_decoding
- * and the table must not change, and B, Hkv, page_size and sm_count must be the ones the plan was made with.  A
+ * and the table must not change, and B, Hkv, page_size and sm_count must be the ones the plan was made with (B counts
+ * the entries of cached_lens; q and out are only touched in the rows of decoding entries, so a caller that packs
+ * tokens may hold fewer rows than B there).  A
  * plan that does not fit (checked per warp against the header and the lengths) sets B200KV_S_BAD_PLAN in the
  * status word and the warps that saw it write nothing; zero-fill the workspace again after that.
  * `variant` as for b200kv_decode_attn, except bit 1 (the two-kernel reduction), which is refused.  With bit 2
